@@ -1,0 +1,414 @@
+#!/usr/bin/env python
+"""MemSolve layer forward+backward throughput on B200 (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c5]
+
+Workload (default, "c3"): BASELINE configuration 3 -- one MemSolve layer, dim 768, 12 heads
+(head dim 64), rank 32, rotary on, BF16, x = [1, 32768, 768] ~ N(0,1), upstream gradient
+~ N(0,1), seeded random-init weights (core_base_raw ~ N(0, 0.1^2) so the core is exercised),
+recompute_readout=False.  With N > 1 GPUs every rank holds 32768 local tokens of one
+sequence of 32768*N tokens (sequence parallel, weak scaling).  "c5" is BASELINE configuration 5:
+rank 64, one sequence of 262144 tokens split evenly over the ranks (strong scaling).
+
+A step is layer forward + backward (+ the sequence-parallel gradient SUM when N > 1).
+`value` is tokens/s of the whole job with inputs resident in HBM; `e2e` repeats the step
+through the same public call with the inputs in pinned host memory (copied in every step) and
+a scalar result read back.  `roofline` is measured live: each mixer kernel is timed alone with
+CUDA events on the launching stream after an L2 flush.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    "c3": dict(dim=768, heads=12, rank=32, local_tokens=32768, strong=False),
+    "c5": dict(dim=768, heads=12, rank=64, global_tokens=262144, strong=True),
+}
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "measured"
+    return 6650.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def build_layer(cfg, device, seed=0):
+    from memsolve_b200 import MemSolve, MemSolveConfig
+    torch.manual_seed(seed)
+    layer = MemSolve(MemSolveConfig(dim=cfg["dim"], num_heads=cfg["heads"], rank=cfg["rank"], rotary=True,
+                                    recompute_readout=False))
+    with torch.no_grad():
+        layer.core_base_raw.normal_(std=0.1)
+    return layer.to(device)
+
+
+# ---------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle port of the reference's pure-PyTorch CPU path
+# ---------------------------------------------------------------------------------------
+def cpu_layer_step(cfg, tokens, seed=0):
+    """Returns a closure running one oracle layer forward+backward on `tokens` tokens."""
+    from oracle import memsolve_oracle as O
+    from memsolve_b200 import MemSolve, MemSolveConfig
+    torch.manual_seed(seed)
+    layer = MemSolve(MemSolveConfig(dim=cfg["dim"], num_heads=cfg["heads"], rank=cfg["rank"], rotary=True))
+    with torch.no_grad():
+        layer.core_base_raw.normal_(std=0.1)
+    params = O.LayerParams(layer.w_bc.weight.detach().clone(), layer.w_o.weight.detach().clone(),
+                           layer.core_base_raw.detach().clone(), layer.eta_raw.detach().clone(),
+                           heads=cfg["heads"], rank=cfg["rank"])
+    for t in params.tensors():
+        t.requires_grad_()
+    x = torch.randn(1, tokens, cfg["dim"]).bfloat16().requires_grad_()
+    dout = torch.randn(1, tokens, cfg["dim"]).bfloat16()
+    d = cfg["dim"] // cfg["heads"]
+    cos, sin = O.rotary_tables(torch.arange(tokens)[None], head_dim=d, train_length=128, context_length=tokens)
+
+    def step():
+        for t in params.tensors():
+            t.grad = None
+        x.grad = None
+        y = O.layer_forward(params, x, None, cos, sin)
+        y.backward(dout)
+        return y
+
+    return step
+
+
+def time_cpu(cfg, tokens, steps, warmup):
+    step = cpu_layer_step(cfg, tokens)
+    for _ in range(warmup):
+        step()
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    return sum(times) / len(times)
+
+
+def run_reference(args, cfg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    full = cfg.get("local_tokens", cfg.get("global_tokens"))
+    # bounded sample: pick the largest token count whose (steps+warmup) run stays near two minutes
+    probe = time_cpu(cfg, 2048, 1, 1)
+    budget = 120.0 / max(1, args.steps + args.warmup)
+    tokens = full
+    while tokens > 2048 and probe * (tokens / 2048.0) > budget:
+        tokens //= 2
+    dt = time_cpu(cfg, tokens, args.steps, args.warmup)
+    value = tokens / dt
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": "layer_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong" if cfg["strong"] else "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args, cfg, 1),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"{tokens} of {full} tokens per step, oracle port of the reference CPU path"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(args, cfg, world):
+    if cfg["strong"]:
+        glob = cfg["global_tokens"]
+    else:
+        glob = cfg["local_tokens"] * world
+    return {"workload": f"MemSolve layer fwd+bwd, config {args.workload}: dim {cfg['dim']}, {cfg['heads']} heads, "
+                        f"rank {cfg['rank']}, rotary, B=1, N={glob} tokens"
+                        + (f" sequence-parallel over {world} GPUs" if world > 1 else ""),
+            "global_tokens": glob, "tokens_per_gpu": glob // world, "recompute_readout": False,
+            "parallelism": f"sp{world}", "l2": "working set per step exceeds the 126 MB L2 (inputs larger than L2)"}
+
+
+# ---------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------
+def time_kernels(layer, cfg, tokens, device, reps=10):
+    """Each mixer kernel alone, CUDA events on the launching stream, L2 flushed before each launch."""
+    import ctypes
+    from memsolve_b200.ball import cuda as C
+    lib = C._LIB
+    heads, rank, dim = cfg["heads"], cfg["rank"], cfg["dim"]
+    d = dim // heads
+    width = heads * rank + dim
+    g = torch.Generator(device="cpu").manual_seed(1)
+    proj = (torch.randn(1, tokens, width, generator=g) * 0.5).bfloat16().to(device)
+    dy = torch.randn(1, tokens, dim, generator=g).bfloat16().to(device)
+    pos = torch.arange(tokens, device=device)[None]
+    from memsolve_b200.ball.rotary import rotary_position_factors
+    cos, sin = rotary_position_factors(pos, head_dim=d, base=10000.0, train_length=128, context_length=tokens,
+                                       scaling="yarn")
+    base, raw = layer.core_base_raw.detach(), layer.eta_raw.detach()
+    shape, dims = C._make_shape(proj, base, cos)
+    tape = C._alloc_tape(dims, device)
+    tc = tape.as_struct()
+    ws = C._workspace(shape, device)
+    dpad = lib.ms_padded_head_dim(d)
+    mixed = torch.empty(1, tokens, dim, device=device, dtype=torch.bfloat16)
+    gg = torch.empty(1, heads, 2, rank, rank, device=device, dtype=torch.bfloat16)
+    cg = torch.empty(1, heads, 2, rank, dpad, device=device, dtype=torch.bfloat16)
+    dproj = torch.empty_like(proj)
+    dbase = torch.empty_like(base)
+    draw = torch.empty_like(raw)
+    st = torch.cuda.current_stream(device).cuda_stream
+    S = ctypes.byref(shape)
+    T = ctypes.byref(tc)
+    calls = {
+        "core_forward": lambda: lib.ms_core_forward(S, base.data_ptr(), raw.data_ptr(), T, st),
+        "stats_forward": lambda: lib.ms_stats_forward(S, proj.data_ptr(), cos.data_ptr(), sin.data_ptr(), None,
+                                                      ws.data_ptr(), ws.numel(), None, st),
+        "compact_forward": lambda: lib.ms_compact_forward(S, None, ws.data_ptr(), ws.numel(), None, T, st),
+        "readout": lambda: lib.ms_readout(S, proj.data_ptr(), cos.data_ptr(), sin.data_ptr(), None, T,
+                                          mixed.data_ptr(), st),
+        "stats_backward": lambda: lib.ms_stats_backward(S, proj.data_ptr(), dy.data_ptr(), cos.data_ptr(),
+                                                        sin.data_ptr(), None, ws.data_ptr(), ws.numel(), None, st),
+        "compact_backward": lambda: lib.ms_compact_backward(S, None, ws.data_ptr(), ws.numel(), None, T,
+                                                            base.data_ptr(), raw.data_ptr(), 1.0, gg.data_ptr(),
+                                                            cg.data_ptr(), dbase.data_ptr(), draw.data_ptr(), st),
+        "token_backward": lambda: lib.ms_token_backward(S, proj.data_ptr(), dy.data_ptr(), cos.data_ptr(),
+                                                        sin.data_ptr(), None, T, gg.data_ptr(), cg.data_ptr(),
+                                                        dproj.data_ptr(), st),
+    }
+    bpt = {  # algorithmic bytes per token (BF16): packed row = 2*width, mixed row = 2*dim
+        "stats_forward": 2 * width, "readout": 2 * width + 2 * dim,
+        "stats_backward": 2 * width + 2 * dim, "token_backward": 4 * width + 2 * dim,
+    }
+    flush = torch.empty(256 * 1024 * 1024, device=device, dtype=torch.uint8)
+    out = {}
+    for name, fn in calls.items():
+        for _ in range(3):
+            assert fn() == 0
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            assert fn() == 0
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e-3)
+        out[name] = {"s": sum(ts) / len(ts), "bytes": bpt.get(name, 0) * tokens}
+    return out
+
+
+def run_ours(args, cfg):
+    import torch.distributed as dist
+    from memsolve_b200.ball import cuda as C
+    from memsolve_b200.integrations.distributed import SequenceParallel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    C.load(device=device)
+
+    tokens = cfg["global_tokens"] // world if cfg["strong"] else cfg["local_tokens"]
+    global_tokens = tokens * world
+    layer = build_layer(cfg, device)
+    gen = torch.Generator().manual_seed(1234 + rank)
+    x_host = torch.randn(1, tokens, cfg["dim"], generator=gen).bfloat16().pin_memory()
+    d_host = torch.randn(1, tokens, cfg["dim"], generator=gen).bfloat16().pin_memory()
+    x = x_host.to(device).requires_grad_()
+    dout = d_host.to(device)
+    sp = counts = None
+    if world > 1:
+        sp = SequenceParallel.create(tokens)
+        counts = sp.valid_counts(None, batch_size=1, device=device)
+
+    def step(xin, grad_out):
+        layer.zero_grad(set_to_none=True)
+        xin.grad = None
+        if sp is None:
+            y = layer(xin, implementation="cuda")
+        else:
+            y = layer(xin, implementation="cuda", sequence_parallel=sp, valid_counts=counts)
+        y.backward(grad_out)
+        if sp is not None:
+            sp.reduce_gradients_(layer)
+        return y
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e-3], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step(x, dout)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    total = timed(lambda: step(x, dout), args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # end to end: inputs start in pinned host memory every step, a scalar result comes back
+    x_dev = torch.empty_like(x_host, device=device).requires_grad_()
+    d_dev = torch.empty_like(d_host, device=device)
+    result = torch.zeros(1, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        with torch.no_grad():
+            x_dev.copy_(x_host, non_blocking=True)
+            d_dev.copy_(d_host, non_blocking=True)
+        y = step(x_dev, d_dev)
+        with torch.no_grad():
+            result.copy_((y[0, :8].float().sum() + x_dev.grad[0, :8].float().sum()).reshape(1), non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    e2e_total = timed(e2e_step, args.steps)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    hbm, tc, which = _peaks()
+    kern = time_kernels(layer, cfg, tokens, device)
+    name = max((k for k in kern if kern[k]["bytes"]), key=lambda k: kern[k]["s"])
+    achieved = kern[name]["bytes"] / kern[name]["s"] / 1e9
+    mixer_time = sum(v["s"] for v in kern.values())
+    width = cfg["heads"] * cfg["rank"] + cfg["dim"]
+    core_bytes = 2 * (5 * width + 3 * cfg["dim"]) * tokens
+    dt = total / args.steps
+    value = global_tokens / dt
+    layer_bytes_per_tok = 2 * (5 * width + 3 * cfg["dim"]) + 2 * (5 * cfg["dim"] + 2 * width + 3 * cfg["dim"])
+    layer_flops_per_tok = 6 * cfg["dim"] * (width + cfg["dim"])
+    tok_rate_gpu = tokens / dt
+    bound = max(layer_bytes_per_tok * tok_rate_gpu / (hbm * 1e9), layer_flops_per_tok * tok_rate_gpu / (tc * 1e12))
+    line = {
+        "metric": "layer_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong" if cfg["strong"] else "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(args, cfg, world), "clocks": clocks,
+        "e2e": {"value": global_tokens / (e2e_total / args.steps), "unit": "tokens/s",
+                "h2d_bytes_per_step": (x_host.numel() + d_host.numel()) * 2 * world, "d2h_bytes_per_step": 4 * world},
+        "gpu_launches": 8 * args.steps,
+        "roofline": {
+            "bound": "hbm", "kernel": name, "achieved": achieved, "peak": hbm, "unit": "GB/s",
+            "frac": achieved / hbm, "traffic": None, "peak_source": f"of {which}",
+            "per_kernel_us": {k: round(v["s"] * 1e6, 2) for k, v in kern.items()},
+            "per_kernel_gbs": {k: round(v["bytes"] / v["s"] / 1e9, 1) for k, v in kern.items() if v["bytes"]},
+            "mix_core": {"bytes_per_token": 2 * (5 * width + 3 * cfg["dim"]), "us": round(mixer_time * 1e6, 2),
+                         "achieved": core_bytes / mixer_time / 1e9, "frac": core_bytes / mixer_time / 1e9 / hbm},
+            "layer": {"frac_of_max_hbm_tensor_bound": bound},
+        },
+    }
+    if world == 1 and not args.no_cpu:
+        n_cpu = 8192
+        t_cpu = time_cpu(cfg, n_cpu, 2, 1)
+        line["cpu_baseline"] = {"value": n_cpu / t_cpu, "unit": "tokens/s", "cores": torch.get_num_threads(),
+                                "kind": "port",
+                                "sample": f"{n_cpu}-token slice of the workload, 2 timed steps, oracle port of the "
+                                          "reference's pure-PyTorch CPU layer forward+backward"}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=tuple(CONFIGS), default="c3")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    cfg = CONFIGS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, cfg)
+    else:
+        run_ours(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

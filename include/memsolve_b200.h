@@ -1,0 +1,188 @@
+/*
+ * memsolve_b200.h -- C ABI of the B200 (sm_100a) MemSolve mixer kernels.
+ *
+ * One shared library, `memsolve_equilibrium_sm100.so`, exports exactly the symbols
+ * declared here.  Signatures use plain pointers and integers only (no torch types).
+ * Every pointer named `d_*`/documented as "device" is a device pointer owned by the
+ * caller; nothing here allocates or frees device memory, synchronises the host, or
+ * keeps a pointer after returning, so calls may be captured into a CUDA graph.
+ * `stream` is a `cudaStream_t` passed as `void*`.
+ *
+ * All functions returning `int` return an `ms_status` (0 on success).
+ *
+ * Reference interfaces replaced (paths inside the reference project):
+ *   - csrc/ball/binding.cpp:314-321  TORCH_LIBRARY(memsolve_equilibrium) op set
+ *   - memsolve/ball/cuda.py:2121-2247 `_no_frame_statistics`      -> ms_stats_forward / ms_stats_backward
+ *   - memsolve/ball/cuda.py:2798-2880 core forward + `_no_frame_compact` -> ms_core_forward, ms_compact_forward
+ *   - memsolve/ball/cuda.py:2990-3050 `_run_readout`              -> ms_readout
+ *   - memsolve/ball/cuda.py:2883-2987 `_no_frame_compact_backward` -> ms_compact_backward, ms_core_backward
+ *   - memsolve/ball/cuda.py:3053-3109 `_run_token_backward`       -> ms_token_backward
+ *   - memsolve/ball/cuda.py:3112-3227 `_no_frame_forward` / `_NoFrameMix` -> ms_mix_forward / ms_mix_backward
+ *
+ * Tensor layouts (row-major, innermost last):
+ *   projected   bf16 [B, N, H*r + H*d]   head h: relation cols [h*r,(h+1)*r), content cols [H*r+h*d, H*r+(h+1)*d)
+ *   mixed, dy   bf16 [B, N, H*d]
+ *   cos, sin    f32  [rotary_rows, N, d/2]  (rotary_rows = 1 or B; adjacent-pair layout)
+ *   counts      f32  [B]                  max(valid tokens, 1); NULL means N
+ *   base_raw    f32  [H, r, r]            ignored when shape.complement != 0
+ *   eta_raw     f32  [H]
+ *   tape tensors: see ms_tape below.
+ */
+#ifndef MEMSOLVE_B200_H_
+#define MEMSOLVE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MS_ABI_VERSION 1
+
+typedef enum ms_status {
+  MS_OK = 0,
+  MS_ERR_INVALID_ARGUMENT = 1, /* null pointer, non-positive size, bad rotary_rows ...          */
+  MS_ERR_UNSUPPORTED_RANK = 2, /* rank not in {16, 32, 48, 64}                                  */
+  MS_ERR_WORKSPACE = 3,        /* workspace pointer null or smaller than ms_workspace_bytes()   */
+  MS_ERR_LAUNCH = 4,           /* a kernel launch reported a CUDA error                         */
+  MS_ERR_DEVICE = 5,           /* current device is not sm_100-class                            */
+  MS_ERR_ODD_HEAD_DIM = 6      /* rotary tables given with an odd head dimension                */
+} ms_status;
+
+/* Problem shape shared by every call. */
+typedef struct ms_shape {
+  int32_t batch;       /* B */
+  int32_t tokens;      /* N (local tokens of this rank under sequence parallelism)  */
+  int32_t heads;       /* H */
+  int32_t rank;        /* r in {16,32,48,64} */
+  int32_t head_dim;    /* d >= 1 */
+  int32_t complement;  /* nonzero: complement mode (F = 0, no base_raw)             */
+  int32_t rotary_rows; /* 0: no rotary; 1: one table for all samples; B: per sample */
+  int32_t reserved;    /* must be 0 */
+} ms_shape;
+
+/*
+ * Compact tape written by the forward and read by the backward.  All device
+ * pointers, caller-allocated (sizes in elements):
+ *   eta        f32  [H]            (1 - 2^-23) * tanh(eta_raw)
+ *   eta_slope  f32  [H]            d eta / d eta_raw (exponential form)
+ *   core_map   f32  [H, r, r]      F = (I+J)^-1 (I-J); untouched in complement mode
+ *   core_info  i32  [H]            0, or k+1 if LU pivot k was exactly zero
+ *   inverse    f32  [B, H, r, r]   T = chol(I+G)^-1, lower triangular
+ *   state      f32  [B, H, r, d]   Z = T Q
+ *   coeff      bf16 [B, H, 2, r, dp] readout coefficients W = T^T (F - eta I) Z split into a
+ *                                  high BF16 word ([..,0,..]) and the BF16 residual ([..,1,..]);
+ *                                  dp = ms_padded_head_dim(d), padding columns are zero
+ */
+typedef struct ms_tape {
+  float* eta;
+  float* eta_slope;
+  float* core_map;
+  int32_t* core_info;
+  float* inverse;
+  float* state;
+  void* coeff;
+} ms_tape;
+
+/* Replaces torch.ops.memsolve_equilibrium.contract_version (csrc/ball/binding.cpp:315). */
+int ms_abi_version(void);
+
+/* Replaces supported_architectures (csrc/ball/binding.cpp:316): writes up to `capacity`
+ * SM numbers (e.g. 100) compiled into this library, returns how many exist. */
+int ms_supported_architectures(int32_t* out, int capacity);
+
+/* Human-readable text for a status code (static storage). */
+const char* ms_status_string(int status);
+
+/* Row pitch, in elements, of the split coefficient tensors: d rounded up to a multiple of 8. */
+int ms_padded_head_dim(int head_dim);
+
+/* Bytes of scratch the stats/compact calls need for this shape (partials of the token
+ * reduction and backward intermediates).  Same workspace serves forward and backward. */
+size_t ms_workspace_bytes(const ms_shape* shape);
+
+/* Number of floats in the packed, reduced forward statistics (per rank):
+ * B*H*(r*r + r*d).  Backward: B*H*(r*d + 1).  Used for the sequence-parallel all-reduce. */
+size_t ms_packed_stats_floats(const ms_shape* shape, int backward);
+
+/*
+ * Per-head core: eta, eta_slope, F.  Replaces `complement`, `core_forward`, `compact_lu`,
+ * `compact_getrs` (memsolve/ball/cuda.py:2798-2814; csrc/ball/solvers.cuh:227-560).
+ * Only tape->eta, eta_slope, core_map, core_info are written.
+ */
+int ms_core_forward(const ms_shape* shape, const float* base_raw, const float* eta_raw,
+                    const ms_tape* tape, void* stream);
+
+/*
+ * Token reduction G = A^T A / n, Q = A^T rot(C) / sqrt(n).
+ * Writes per-chunk partial sums into `workspace`.  If `packed` is non-null the partials are
+ * also summed (fixed order) and scaled into packed[B*H][r*r + r*d] (G then Q per system) --
+ * the buffer a sequence-parallel caller all-reduces before ms_compact_forward.
+ */
+int ms_stats_forward(const ms_shape* shape, const void* projected, const float* cos,
+                     const float* sin, const float* counts, void* workspace,
+                     size_t workspace_bytes, float* packed, void* stream);
+
+/*
+ * Per (b,h): T, Z, W from the statistics.  `packed` null: read the partials left in
+ * `workspace` by ms_stats_forward (reduced here, fixed order).  `packed` non-null: read the
+ * already reduced + scaled statistics from it.  Needs tape->eta and tape->core_map
+ * (ms_core_forward).  Writes tape->inverse, state, coeff.
+ */
+int ms_compact_forward(const ms_shape* shape, const float* counts, const void* workspace,
+                       size_t workspace_bytes, const float* packed, const ms_tape* tape,
+                       void* stream);
+
+/* mixed = eta*C + rot^-1(A_raw W)/sqrt(n).  Reads tape->eta, tape->coeff. */
+int ms_readout(const ms_shape* shape, const void* projected, const float* cos, const float* sin,
+               const float* counts, const ms_tape* tape, void* mixed, void* stream);
+
+/* Whole forward on one rank: core + stats + compact + readout (no collective). */
+int ms_mix_forward(const ms_shape* shape, const void* projected, const float* base_raw,
+                   const float* eta_raw, const float* cos, const float* sin, const float* counts,
+                   void* workspace, size_t workspace_bytes, const ms_tape* tape, void* mixed,
+                   void* stream);
+
+/*
+ * Adjoint token reduction E = A^T rot(dy)/sqrt(n), de = <dy, C> per (b,h).
+ * Same partial / packed convention as ms_stats_forward; packed[B*H][r*d] then [B*H] de.
+ */
+int ms_stats_backward(const ms_shape* shape, const void* projected, const void* dy,
+                      const float* cos, const float* sin, const float* counts, void* workspace,
+                      size_t workspace_bytes, float* packed, void* stream);
+
+/*
+ * Compact adjoint per (b,h) and per head.  Inputs: E/de (workspace partials or `packed`),
+ * the forward tape, base_raw, eta_raw.  Outputs (device, caller-allocated):
+ *   gram_grad  bf16 [B,H,2,r,r]   dG + dG^T, split high/residual
+ *   cross_grad bf16 [B,H,2,r,dp]  dQ, split high/residual
+ *   d_base_raw f32  [H,r,r]       (not written in complement mode)
+ *   d_eta_raw  f32  [H]
+ * `grad_scale` multiplies d_base_raw and d_eta_raw (1/world_size under sequence parallelism,
+ * memsolve/ball/cuda.py:3221-3226).
+ */
+int ms_compact_backward(const ms_shape* shape, const float* counts, void* workspace,
+                        size_t workspace_bytes, const float* packed, const ms_tape* tape,
+                        const float* base_raw, const float* eta_raw, float grad_scale,
+                        void* gram_grad, void* cross_grad, float* d_base_raw, float* d_eta_raw,
+                        void* stream);
+
+/* dprojected from the token pass (dA_raw | dC), same packed layout as `projected`. */
+int ms_token_backward(const ms_shape* shape, const void* projected, const void* dy,
+                      const float* cos, const float* sin, const float* counts,
+                      const ms_tape* tape, const void* gram_grad, const void* cross_grad,
+                      void* dprojected, void* stream);
+
+/* Whole backward on one rank: adjoint stats + compact adjoint + token pass (no collective). */
+int ms_mix_backward(const ms_shape* shape, const void* projected, const void* dy,
+                    const float* base_raw, const float* eta_raw, const float* cos,
+                    const float* sin, const float* counts, void* workspace,
+                    size_t workspace_bytes, const ms_tape* tape, void* gram_grad,
+                    void* cross_grad, void* dprojected, float* d_base_raw, float* d_eta_raw,
+                    void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MEMSOLVE_B200_H_ */

@@ -1,0 +1,652 @@
+"""Loader and autograd boundary of the B200 MemSolve mixer kernels.
+
+Mirrors the public surface of the reference's ``memsolve.ball.cuda``
+(memsolve/ball/cuda.py): ``load``, ``is_available``, ``require_available``,
+``fast_mix`` and the private hooks the layer module uses (``_recompute_scope``,
+``_recompute_output_linear``, ``_is_default_fast_mix``, ``_TensorCoreLinear``).
+
+Instead of a ``torch.ops`` namespace the native code is a C-ABI shared library
+(``memsolve_equilibrium_sm100.so``, declared in ``include/memsolve_b200.h``) opened
+with :mod:`ctypes`; tensors cross the boundary as raw device pointers plus the
+current CUDA stream.  There is no CPU or PyTorch fallback for the mixer: when
+the library is missing every entry point raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+from contextlib import contextmanager
+from pathlib import Path
+from threading import Lock, local
+from typing import Literal, NamedTuple
+
+import torch
+from torch.autograd.function import once_differentiable
+
+from .config import _validate_recompute_readout
+
+_LOAD_LOCK = Lock()
+_RECOMPUTE_LOCAL = local()
+_SUPPORTED_ARCHITECTURES = frozenset((100,))
+_NATIVE_CONTRACT_VERSION = 1
+_LIBRARY_ENV = "MEMSOLVE_CUDA_LIBRARY"
+_LIBRARY_PATTERN = re.compile(r"^memsolve_equilibrium(_sm(\d+))?\.so$")
+
+_LIB: ctypes.CDLL | None = None
+_LIB_PATH: str | None = None
+_LOADED_ARCHITECTURE: frozenset[int] | None = None
+
+
+# --------------------------------------------------------------------------------------
+# C structures (include/memsolve_b200.h)
+# --------------------------------------------------------------------------------------
+class _Shape(ctypes.Structure):
+    _fields_ = [(name, ctypes.c_int32) for name in (
+        "batch", "tokens", "heads", "rank", "head_dim", "complement", "rotary_rows", "reserved")]
+
+
+class _Tape(ctypes.Structure):
+    _fields_ = [(name, ctypes.c_void_p) for name in (
+        "eta", "eta_slope", "core_map", "core_info", "inverse", "state", "coeff")]
+
+
+_P = ctypes.c_void_p
+_SIGNATURES = {
+    "ms_abi_version": (ctypes.c_int, []),
+    "ms_supported_architectures": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int32), ctypes.c_int]),
+    "ms_status_string": (ctypes.c_char_p, [ctypes.c_int]),
+    "ms_padded_head_dim": (ctypes.c_int, [ctypes.c_int]),
+    "ms_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(_Shape)]),
+    "ms_packed_stats_floats": (ctypes.c_size_t, [ctypes.POINTER(_Shape), ctypes.c_int]),
+    "ms_core_forward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, ctypes.POINTER(_Tape), _P]),
+    "ms_stats_forward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, ctypes.c_size_t, _P, _P]),
+    "ms_compact_forward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, ctypes.c_size_t, _P,
+                                          ctypes.POINTER(_Tape), _P]),
+    "ms_readout": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, ctypes.POINTER(_Tape), _P, _P]),
+    "ms_mix_forward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t,
+                                      ctypes.POINTER(_Tape), _P, _P]),
+    "ms_stats_backward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, _P, ctypes.c_size_t, _P, _P]),
+    "ms_compact_backward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, ctypes.c_size_t, _P,
+                                           ctypes.POINTER(_Tape), _P, _P, ctypes.c_float, _P, _P, _P, _P, _P]),
+    "ms_token_backward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, ctypes.POINTER(_Tape),
+                                         _P, _P, _P, _P]),
+    "ms_mix_backward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t,
+                                       ctypes.POINTER(_Tape), _P, _P, _P, _P, _P, _P]),
+}
+EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+
+
+# --------------------------------------------------------------------------------------
+# loading
+# --------------------------------------------------------------------------------------
+def default_library_path() -> Path:
+    """In-tree build product (``python -m memsolve_b200.csrc.build``)."""
+    return Path(__file__).resolve().parent.parent / "lib" / "memsolve_equilibrium_sm100.so"
+
+
+def _open_library(path: str | os.PathLike) -> ctypes.CDLL:
+    """dlopen + bind every symbol of the header; needs no GPU."""
+    lib = ctypes.CDLL(os.fspath(path))
+    for name, (restype, argtypes) in _SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as error:
+            raise RuntimeError(
+                f"{path} does not export {name}; it is not a MemSolve sm_100 library"
+            ) from error
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+def _check_native_contract(lib: ctypes.CDLL) -> None:
+    version = lib.ms_abi_version()
+    if version != _NATIVE_CONTRACT_VERSION:
+        raise RuntimeError(
+            "the loaded MemSolve CUDA extension has native contract version "
+            f"{version}, but this package requires {_NATIVE_CONTRACT_VERSION}; "
+            "rebuild it with `python -m memsolve_b200.csrc.build` and restart the process"
+        )
+
+
+def _library_architectures(lib: ctypes.CDLL) -> frozenset[int]:
+    buf = (ctypes.c_int32 * 8)()
+    count = lib.ms_supported_architectures(buf, 8)
+    return frozenset(int(buf[i]) for i in range(min(count, 8)))
+
+
+def _device_architecture(device: torch.device | int | None = None) -> int:
+    """SM number of ``device`` normalised the way the reference does
+    (memsolve/ball/cuda.py:183-211): 10.3 and 11.0 count as 100."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("the MemSolve CUDA fast path requires an available CUDA device")
+    if device is None:
+        resolved = torch.device("cuda", torch.cuda.current_device())
+    elif isinstance(device, int):
+        resolved = torch.device("cuda", device)
+    else:
+        resolved = torch.device(device)
+    if resolved.type != "cuda":
+        raise ValueError(f"the MemSolve CUDA fast path requires a CUDA device, got {resolved}")
+    if resolved.index is None:
+        resolved = torch.device("cuda", torch.cuda.current_device())
+    major, minor = torch.cuda.get_device_capability(resolved)
+    architecture = major * 10 + minor
+    if architecture in (103, 110):
+        architecture = 100
+    if architecture not in _SUPPORTED_ARCHITECTURES:
+        raise RuntimeError(
+            f"this build of the MemSolve CUDA fast path supports SM100 (B200) only; got SM{major}{minor}"
+        )
+    return architecture
+
+
+def _resolve_library_path(path: str | os.PathLike | None) -> Path:
+    if path is None:
+        env = os.environ.get(_LIBRARY_ENV)
+        path = env if env else default_library_path()
+    resolved = Path(path)
+    if not _LIBRARY_PATTERN.match(resolved.name):
+        raise RuntimeError(
+            "the MemSolve CUDA library must be named memsolve_equilibrium.so or "
+            f"memsolve_equilibrium_sm<arch>.so, got {resolved.name!r}"
+        )
+    if not resolved.exists():
+        raise RuntimeError(
+            f"the MemSolve CUDA extension is not built: {resolved} does not exist; "
+            "run `python -m memsolve_b200.csrc.build`"
+        )
+    return resolved
+
+
+def load(path: str | os.PathLike | None = None, *, device: torch.device | int | None = None) -> None:
+    """Open the native library and check it against ``device``.
+
+    Same call shape as the reference loader (memsolve/ball/cuda.py:334-339).
+    Idempotent and serialised by a lock; a later call for a device whose SM is
+    not in the loaded library raises ``"targets SM..., not requested SM..."``.
+    """
+    global _LIB, _LIB_PATH, _LOADED_ARCHITECTURE
+    requested = _device_architecture(device)
+    with _LOAD_LOCK:
+        if _LIB is not None:
+            if requested not in _LOADED_ARCHITECTURE:
+                built = ", ".join(f"SM{a}" for a in sorted(_LOADED_ARCHITECTURE))
+                raise RuntimeError(
+                    f"the loaded MemSolve CUDA extension targets {built}, not requested SM{requested}"
+                )
+            return
+        resolved = _resolve_library_path(path)
+        lib = _open_library(resolved)
+        _check_native_contract(lib)
+        architectures = _library_architectures(lib)
+        if requested not in architectures:
+            built = ", ".join(f"SM{a}" for a in sorted(architectures))
+            raise RuntimeError(f"{resolved} targets {built}, not requested SM{requested}")
+        _LIB, _LIB_PATH, _LOADED_ARCHITECTURE = lib, str(resolved), architectures
+
+
+def is_available() -> bool:
+    """Whether the native library has been loaded and verified."""
+    return _LIB is not None
+
+
+def require_available() -> None:
+    """Reject a CUDA request until the extension is loaded (memsolve/ball/cuda.py:164-180)."""
+    if _LIB is None:
+        raise RuntimeError(
+            "the MemSolve accretive-equilibrium CUDA extension is not loaded; build it with "
+            "`python -m memsolve_b200.csrc.build`, then call memsolve_b200.ball.cuda.load(); "
+            f"native contract version {_NATIVE_CONTRACT_VERSION} is required"
+        )
+
+
+def loaded_library_path() -> str | None:
+    return _LIB_PATH
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        text = _LIB.ms_status_string(status).decode() if _LIB is not None else str(status)
+        raise RuntimeError(f"MemSolve CUDA {what} failed: {text} (status {status})")
+
+
+# --------------------------------------------------------------------------------------
+# recompute-readout scope (memsolve/ball/cuda.py:26-59)
+# --------------------------------------------------------------------------------------
+class _RecomputeSpec(NamedTuple):
+    projected: torch.Tensor
+    tape: "_TapeTensors"
+    counts: torch.Tensor | None
+    rotary_cos: torch.Tensor | None
+    rotary_sin: torch.Tensor | None
+    shape: tuple
+
+
+class _RecomputeScopeState:
+    __slots__ = ("policy", "spec")
+
+    def __init__(self, policy: Literal["auto"] | bool) -> None:
+        self.policy = _validate_recompute_readout(policy)
+        self.spec: _RecomputeSpec | None = None
+
+    @property
+    def enabled(self) -> bool:
+        return self.policy is not False
+
+
+@contextmanager
+def _recompute_scope(policy: Literal["auto"] | bool = "auto"):
+    previous = getattr(_RECOMPUTE_LOCAL, "active", None)
+    state = _RecomputeScopeState(policy)
+    _RECOMPUTE_LOCAL.active = state
+    try:
+        yield state
+    finally:
+        _RECOMPUTE_LOCAL.active = previous
+
+
+# --------------------------------------------------------------------------------------
+# native call helpers
+# --------------------------------------------------------------------------------------
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+class _TapeTensors(NamedTuple):
+    eta: torch.Tensor
+    eta_slope: torch.Tensor
+    core_map: torch.Tensor
+    core_info: torch.Tensor
+    inverse: torch.Tensor
+    state: torch.Tensor
+    coeff: torch.Tensor
+
+    def as_struct(self) -> _Tape:
+        return _Tape(*(t.data_ptr() for t in self))
+
+
+def _make_shape(projected, base, cos) -> tuple[_Shape, tuple]:
+    batch, length, width = projected.shape
+    heads, rank, columns = base.shape
+    head_dim = (width - heads * rank) // heads
+    rows = 0 if cos is None else int(cos.shape[0])
+    dims = (batch, length, heads, rank, head_dim, int(columns == 0), rows)
+    return _Shape(*dims, 0), dims
+
+
+def _alloc_tape(dims, device) -> _TapeTensors:
+    batch, _length, heads, rank, head_dim, _comp, _rows = dims
+    f32 = dict(device=device, dtype=torch.float32)
+    dpad = _LIB.ms_padded_head_dim(head_dim)
+    return _TapeTensors(
+        eta=torch.empty(heads, **f32),
+        eta_slope=torch.empty(heads, **f32),
+        core_map=torch.empty(heads, rank, rank, **f32),
+        core_info=torch.empty(heads, device=device, dtype=torch.int32),
+        inverse=torch.empty(batch, heads, rank, rank, **f32),
+        state=torch.empty(batch, heads, rank, head_dim, **f32),
+        coeff=torch.empty(batch, heads, 2, rank, dpad, device=device, dtype=torch.bfloat16),
+    )
+
+
+def _workspace(shape: _Shape, device) -> torch.Tensor:
+    nbytes = _LIB.ms_workspace_bytes(ctypes.byref(shape))
+    return torch.empty(max(int(nbytes), 16), device=device, dtype=torch.uint8)
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _sp_active(sequence_parallel) -> bool:
+    return sequence_parallel is not None and getattr(sequence_parallel, "world_size", 2) > 1
+
+
+def _mix_forward(projected, base, raw, counts, sequence_parallel, cos, sin):
+    """Launch the forward kernels; returns (mixed, tape, dims)."""
+    shape, dims = _make_shape(projected, base, cos)
+    device = projected.device
+    batch, length, heads, rank, head_dim = dims[:5]
+    with torch.cuda.device(device):
+        tape = _alloc_tape(dims, device)
+        tape_c = tape.as_struct()
+        ws = _workspace(shape, device)
+        mixed = torch.empty(batch, length, heads * head_dim, device=device, dtype=torch.bfloat16)
+        stream = _stream(device)
+        base_ptr = None if dims[5] else base.data_ptr()
+        if not _sp_active(sequence_parallel):
+            _check(_LIB.ms_mix_forward(
+                ctypes.byref(shape), projected.data_ptr(), base_ptr, raw.data_ptr(), _ptr(cos), _ptr(sin),
+                _ptr(counts), ws.data_ptr(), ws.numel(), ctypes.byref(tape_c), mixed.data_ptr(), stream),
+                "forward")
+        else:
+            _check(_LIB.ms_core_forward(ctypes.byref(shape), base_ptr, raw.data_ptr(), ctypes.byref(tape_c),
+                                        stream), "core forward")
+            packed = torch.empty(_LIB.ms_packed_stats_floats(ctypes.byref(shape), 0), device=device,
+                                 dtype=torch.float32)
+            _check(_LIB.ms_stats_forward(ctypes.byref(shape), projected.data_ptr(), _ptr(cos), _ptr(sin),
+                                         _ptr(counts), ws.data_ptr(), ws.numel(), packed.data_ptr(), stream),
+                   "statistics")
+            # the only cross-GPU step of the forward: SUM of the packed (G, Q) statistics
+            (packed,) = sequence_parallel.sum_tensors(packed)
+            _check(_LIB.ms_compact_forward(ctypes.byref(shape), _ptr(counts), None, 0, packed.data_ptr(),
+                                           ctypes.byref(tape_c), stream), "compact forward")
+            _check(_LIB.ms_readout(ctypes.byref(shape), projected.data_ptr(), _ptr(cos), _ptr(sin),
+                                   _ptr(counts), ctypes.byref(tape_c), mixed.data_ptr(), stream), "readout")
+    return mixed, tape, dims
+
+
+def _readout(projected, tape: _TapeTensors, dims, counts, cos, sin) -> torch.Tensor:
+    batch, length, heads, rank, head_dim, comp, rows = dims
+    shape = _Shape(*dims, 0)
+    device = projected.device
+    with torch.cuda.device(device):
+        mixed = torch.empty(batch, length, heads * head_dim, device=device, dtype=torch.bfloat16)
+        tape_c = tape.as_struct()
+        _check(_LIB.ms_readout(ctypes.byref(shape), projected.data_ptr(), _ptr(cos), _ptr(sin), _ptr(counts),
+                               ctypes.byref(tape_c), mixed.data_ptr(), _stream(device)), "readout")
+    return mixed
+
+
+def _mix_backward(projected, gradient, base, raw, counts, sequence_parallel, cos, sin, tape, dims):
+    batch, length, heads, rank, head_dim, comp, rows = dims
+    shape = _Shape(*dims, 0)
+    device = projected.device
+    with torch.cuda.device(device):
+        tape_c = tape.as_struct()
+        ws = _workspace(shape, device)
+        dpad = _LIB.ms_padded_head_dim(head_dim)
+        gram_grad = torch.empty(batch, heads, 2, rank, rank, device=device, dtype=torch.bfloat16)
+        cross_grad = torch.empty(batch, heads, 2, rank, dpad, device=device, dtype=torch.bfloat16)
+        d_projected = torch.empty_like(projected)
+        d_base = None if comp else torch.empty(heads, rank, rank, device=device, dtype=torch.float32)
+        d_raw = torch.empty(heads, device=device, dtype=torch.float32)
+        stream = _stream(device)
+        base_ptr = None if comp else base.data_ptr()
+        if not _sp_active(sequence_parallel):
+            _check(_LIB.ms_mix_backward(
+                ctypes.byref(shape), projected.data_ptr(), gradient.data_ptr(), base_ptr, raw.data_ptr(),
+                _ptr(cos), _ptr(sin), _ptr(counts), ws.data_ptr(), ws.numel(), ctypes.byref(tape_c),
+                gram_grad.data_ptr(), cross_grad.data_ptr(), d_projected.data_ptr(), _ptr(d_base),
+                d_raw.data_ptr(), stream), "backward")
+        else:
+            packed = torch.empty(_LIB.ms_packed_stats_floats(ctypes.byref(shape), 1), device=device,
+                                 dtype=torch.float32)
+            _check(_LIB.ms_stats_backward(ctypes.byref(shape), projected.data_ptr(), gradient.data_ptr(),
+                                          _ptr(cos), _ptr(sin), _ptr(counts), ws.data_ptr(), ws.numel(),
+                                          packed.data_ptr(), stream), "adjoint statistics")
+            (packed,) = sequence_parallel.sum_tensors(packed)
+            # replicated parameters: every rank holds the full adjoint, a later SUM must count it once
+            scale = 1.0 / float(sequence_parallel.world_size)
+            _check(_LIB.ms_compact_backward(
+                ctypes.byref(shape), _ptr(counts), ws.data_ptr(), ws.numel(), packed.data_ptr(),
+                ctypes.byref(tape_c), base_ptr, raw.data_ptr(), scale, gram_grad.data_ptr(),
+                cross_grad.data_ptr(), _ptr(d_base), d_raw.data_ptr(), stream), "compact backward")
+            _check(_LIB.ms_token_backward(
+                ctypes.byref(shape), projected.data_ptr(), gradient.data_ptr(), _ptr(cos), _ptr(sin),
+                _ptr(counts), ctypes.byref(tape_c), gram_grad.data_ptr(), cross_grad.data_ptr(),
+                d_projected.data_ptr(), stream), "token backward")
+    return d_projected, d_base, d_raw
+
+
+# --------------------------------------------------------------------------------------
+# autograd boundary (memsolve/ball/cuda.py:3146-3227)
+# --------------------------------------------------------------------------------------
+class _NoFrameMix(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, projected, base, raw, counts, sequence_parallel, rotary_cos, rotary_sin):
+        mixed, tape, dims = _mix_forward(projected, base, raw, counts, sequence_parallel, rotary_cos, rotary_sin)
+        ctx.sequence_parallel = sequence_parallel
+        ctx.dims = dims
+        ctx.has_counts = counts is not None
+        ctx.has_rotary = rotary_cos is not None
+        saved = [projected, base, raw, *tape]
+        if counts is not None:
+            saved.append(counts)
+        if rotary_cos is not None:
+            saved += [rotary_cos, rotary_sin]
+        ctx.save_for_backward(*saved)
+        scope = getattr(_RECOMPUTE_LOCAL, "active", None)
+        if scope is not None and (scope.policy is True or (scope.policy == "auto" and projected.shape[1] > 512)):
+            scope.spec = _RecomputeSpec(
+                projected.detach(), _TapeTensors(*(t.detach() for t in tape)), counts, rotary_cos, rotary_sin, dims)
+        return mixed
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, gradient):
+        saved = list(ctx.saved_tensors)
+        projected, base, raw = saved[:3]
+        tape = _TapeTensors(*saved[3:10])
+        rest = saved[10:]
+        counts = rest.pop(0) if ctx.has_counts else None
+        cos, sin = (rest[0], rest[1]) if ctx.has_rotary else (None, None)
+        gradient = gradient.contiguous()
+        if gradient.dtype != torch.bfloat16:
+            gradient = gradient.to(torch.bfloat16)
+        d_projected, d_base, d_raw = _mix_backward(
+            projected, gradient, base, raw, counts, ctx.sequence_parallel, cos, sin, tape, ctx.dims)
+        if d_base is None:
+            d_base = torch.zeros_like(base)
+        return d_projected, d_base, d_raw, None, None, None, None
+
+
+# --------------------------------------------------------------------------------------
+# public mixer entry (memsolve/ball/cuda.py:5175-5278)
+# --------------------------------------------------------------------------------------
+def _validate_no_frame_inputs(projected, base, raw, counts) -> None:
+    def require(condition, message):
+        if not condition:
+            raise RuntimeError(message)
+
+    require(projected.is_cuda, "projected must be a CUDA tensor")
+    require(projected.ndim == 3 and projected.is_contiguous(), "projected must be contiguous [B, N, H*R + D]")
+    require(projected.dtype == torch.bfloat16,
+            "projected must use bfloat16 under the mixed precision CUDA contract")
+    for name, value in (("core_base_raw", base), ("eta_raw", raw)):
+        require(value.device == projected.device and value.is_contiguous(),
+                f"{name} must be contiguous on the same CUDA device")
+        require(value.dtype == torch.float32, f"{name} must use float32")
+    require(base.ndim == 3, "core_base_raw must have shape [H,R,R] or [H,R,0]")
+    batch, length, width = projected.shape
+    heads, rank, columns = base.shape
+    require(batch > 0 and length > 0 and heads > 0, "B, N, and H must be positive")
+    require(rank in (16, 32, 48, 64), "the CUDA fast path supports rank in {16,32,48,64}")
+    require(columns in (0, rank), "core_base_raw must have shape [H,R,R] or [H,R,0]")
+    content = width - heads * rank
+    require(content > 0 and content % heads == 0, "projected content width must be positive and divisible by H")
+    require(raw.ndim == 1 and raw.shape[0] == heads, "eta_raw must have shape [H]")
+    if counts is not None:
+        require(counts.device == projected.device and counts.dtype == torch.float32 and counts.is_contiguous(),
+                "valid_counts must be contiguous float32 on the same CUDA device")
+        require(counts.ndim == 1 and counts.shape[0] == batch, "valid_counts must have shape [B]")
+
+
+def fast_mix(
+    projected: torch.Tensor,
+    core_base_raw: torch.Tensor,
+    eta_raw: torch.Tensor,
+    valid_counts: torch.Tensor | None = None,
+    *, sequence_parallel=None, rotary_cos=None, rotary_sin=None,
+) -> torch.Tensor:
+    """Mix pre-projected BF16 tokens ``[B, N, H*r + D]`` -> ``[B, N, D]`` (BF16).
+
+    Same arguments, checks and messages as the reference entry point
+    (memsolve/ball/cuda.py:5222-5278).  ``core_base_raw`` with a zero last
+    dimension selects complement mode.  All sequence lengths, including
+    ``N <= r``, take the rank-space kernels.
+    """
+    if valid_counts is not None and valid_counts.requires_grad:
+        raise ValueError("the MemSolve CUDA fast path does not support gradients for valid_counts")
+    require_available()
+    _validate_no_frame_inputs(projected, core_base_raw, eta_raw, valid_counts)
+    if (rotary_cos is None) != (rotary_sin is None):
+        raise ValueError("rotary_cos and rotary_sin must be supplied together")
+    if rotary_cos is not None:
+        batch, length, width = projected.shape
+        heads, rank = core_base_raw.shape[:2]
+        head_dim = (width - heads * rank) // heads
+        if head_dim % 2:
+            raise ValueError("rotary content requires an even head dimension")
+        for name, table in (("rotary_cos", rotary_cos), ("rotary_sin", rotary_sin)):
+            if (table.device != projected.device or table.dtype != torch.float32
+                    or not table.is_contiguous() or table.requires_grad):
+                raise ValueError(f"{name} must be non-differentiable contiguous FP32 on the input device")
+            if (table.ndim != 3 or table.shape[1] != length or table.shape[2] != head_dim // 2
+                    or table.shape[0] not in (1, batch)):
+                raise ValueError(f"{name} must have shape [1 or B,N,Dhead/2]")
+        if rotary_cos.shape != rotary_sin.shape:
+            raise ValueError("rotary_cos and rotary_sin must share their shape")
+    record = torch.is_grad_enabled() and any(
+        value.requires_grad for value in (projected, core_base_raw, eta_raw))
+    if sequence_parallel is not None:
+        sequence_parallel.validate(projected.shape[1], core_base_raw.shape[1])
+        if valid_counts is None:
+            raise ValueError("sequence parallelism requires global valid_counts")
+    if record:
+        return _NoFrameMix.apply(projected, core_base_raw, eta_raw, valid_counts, sequence_parallel,
+                                 rotary_cos, rotary_sin)
+    with torch.no_grad():
+        return _mix_forward(projected, core_base_raw, eta_raw, valid_counts, sequence_parallel,
+                            rotary_cos, rotary_sin)[0]
+
+
+_ORIGINAL_FAST_MIX = fast_mix
+
+
+def _is_default_fast_mix() -> bool:
+    return fast_mix is _ORIGINAL_FAST_MIX
+
+
+# --------------------------------------------------------------------------------------
+# projections around the mixer (memsolve/ball/cuda.py:933-1041, 1307-1342)
+# --------------------------------------------------------------------------------------
+_MM_OUT_DTYPE = True
+
+
+def _mm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """BF16 x BF16 GEMM whose FP32 accumulator is returned without a BF16 rounding."""
+    global _MM_OUT_DTYPE
+    if _MM_OUT_DTYPE:
+        try:
+            return torch.mm(a, b, out_dtype=torch.float32)
+        except (TypeError, RuntimeError):
+            _MM_OUT_DTYPE = False
+    return torch.mm(a.float(), b.float())
+
+
+def _masked_rows(value: torch.Tensor, mask: torch.Tensor | None) -> torch.Tensor:
+    if mask is None:
+        return value
+    return torch.where(mask.reshape(-1, 1), value, torch.zeros((), dtype=value.dtype, device=value.device))
+
+
+def _linear_forward(value, weight_bf16, bias, output_dtype, output_mask, input_mask):
+    """BF16 x BF16 with FP32 accumulation, FP32 bias, row masks, one rounding."""
+    flat = value.reshape(-1, value.shape[-1])
+    flat = _masked_rows(flat, None if input_mask is None else input_mask.reshape(-1))
+    flat = flat.to(torch.bfloat16)
+    target = output_dtype if output_dtype is not None else torch.float32
+    if bias is None and output_mask is None and target == torch.bfloat16:
+        out = flat @ weight_bf16.mT
+    else:
+        out = _mm_f32(flat, weight_bf16.mT)
+        if bias is not None:
+            out = out + bias.to(torch.float32)
+        out = _masked_rows(out, None if output_mask is None else output_mask.reshape(-1))
+        out = out.to(target)
+    return out.reshape(value.shape[:-1] + (weight_bf16.shape[0],))
+
+
+def _linear_backward(grad_output, value, weight_bf16, output_mask, input_mask, needs, value_dtype,
+                     weight_dtype, bias):
+    need_dx, need_dw, need_db = needs
+    out_features = weight_bf16.shape[0]
+    flat_g = grad_output.reshape(-1, out_features)
+    flat_g = _masked_rows(flat_g, None if output_mask is None else output_mask.reshape(-1))
+    g_bf16 = flat_g if flat_g.dtype == torch.bfloat16 else flat_g.to(torch.bfloat16)
+    grad_value = grad_weight = grad_bias = None
+    if need_dw:
+        flat_v = value.reshape(-1, value.shape[-1])
+        flat_v = _masked_rows(flat_v, None if input_mask is None else input_mask.reshape(-1)).to(torch.bfloat16)
+        grad_weight = _mm_f32(g_bf16.mT, flat_v).to(weight_dtype)
+    if need_db:
+        grad_bias = flat_g.sum(dim=0, dtype=torch.float32).to(device=bias.device, dtype=bias.dtype)
+    if need_dx:
+        if value_dtype == torch.bfloat16:
+            dx = g_bf16 @ weight_bf16
+        else:
+            dx = _mm_f32(g_bf16, weight_bf16)
+        dx = _masked_rows(dx, None if input_mask is None else input_mask.reshape(-1))
+        grad_value = dx.reshape(grad_output.shape[:-1] + (weight_bf16.shape[1],)).to(value_dtype)
+    return grad_value, grad_weight, grad_bias
+
+
+class _TensorCoreLinear(torch.autograd.Function):
+    """Projection with BF16 multiplicands, FP32 accumulation and dtype-aware stores."""
+
+    @staticmethod
+    def forward(ctx, value, weight, bias, output_dtype, fuse_weight_bias_grad, output_mask, input_mask):
+        weight_bf16 = weight.to(torch.bfloat16)
+        ctx.save_for_backward(value, weight_bf16, output_mask, input_mask, bias)
+        ctx.value_dtype, ctx.weight_dtype = value.dtype, weight.dtype
+        return _linear_forward(value, weight_bf16, bias, output_dtype, output_mask, input_mask)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output):
+        value, weight_bf16, output_mask, input_mask, bias = ctx.saved_tensors
+        needs = (ctx.needs_input_grad[0], ctx.needs_input_grad[1], bias is not None and ctx.needs_input_grad[2])
+        gv, gw, gb = _linear_backward(grad_output, value, weight_bf16, output_mask, input_mask, needs,
+                                      ctx.value_dtype, ctx.weight_dtype, bias)
+        return gv, gw, gb, None, None, None, None
+
+
+def tensor_core_linear(value, weight, bias=None, *, output_dtype=None, fuse_weight_bias_grad=False,
+                       output_mask=None, input_mask=None):
+    """CUDA branch of the reference's ``tensor_core_linear`` (memsolve/ball/reference.py:191-269)."""
+    if value.shape[-1] != weight.shape[-1]:
+        raise ValueError(
+            f"tensor_core_linear input and weight features must agree, got {value.shape[-1]} and {weight.shape[-1]}")
+    return _TensorCoreLinear.apply(value, weight, bias, output_dtype, fuse_weight_bias_grad, output_mask, input_mask)
+
+
+class _RecomputeOutputLinear(torch.autograd.Function):
+    """Output projection that rebuilds its ``mixed`` operand in backward from the compact tape
+    (memsolve/ball/cuda.py:1345-1457) instead of keeping the [B,N,D] readout alive."""
+
+    @staticmethod
+    def forward(ctx, mixed, weight, bias, spec, output_dtype, output_mask):
+        weight_bf16 = weight.to(torch.bfloat16)
+        extra = [t for t in (spec.counts, spec.rotary_cos, spec.rotary_sin) if t is not None]
+        ctx.save_for_backward(weight_bf16, output_mask, bias, spec.projected, *spec.tape, *extra)
+        ctx.flags = (spec.counts is not None, spec.rotary_cos is not None)
+        ctx.dims = spec.shape
+        ctx.value_dtype, ctx.weight_dtype = mixed.dtype, weight.dtype
+        return _linear_forward(mixed, weight_bf16, bias, output_dtype, output_mask, None)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output):
+        saved = list(ctx.saved_tensors)
+        weight_bf16, output_mask, bias, projected = saved[:4]
+        tape = _TapeTensors(*saved[4:11])
+        rest = saved[11:]
+        counts = rest.pop(0) if ctx.flags[0] else None
+        cos, sin = (rest[0], rest[1]) if ctx.flags[1] else (None, None)
+        need_dw = ctx.needs_input_grad[1]
+        mixed = _readout(projected, tape, ctx.dims, counts, cos, sin) if need_dw else None
+        needs = (ctx.needs_input_grad[0], need_dw, bias is not None and ctx.needs_input_grad[2])
+        gv, gw, gb = _linear_backward(grad_output, mixed, weight_bf16, output_mask, None, needs,
+                                      ctx.value_dtype, ctx.weight_dtype, bias)
+        return gv, gw, gb, None, None, None
+
+
+def _recompute_output_linear(mixed, spec, weight, bias, *, output_dtype, fuse_weight_bias_grad=True,
+                             output_mask=None):
+    return _RecomputeOutputLinear.apply(mixed, weight, bias, spec, output_dtype, output_mask)
+
+
+__all__ = ["fast_mix", "is_available", "load", "require_available", "tensor_core_linear"]

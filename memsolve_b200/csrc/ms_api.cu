@@ -1,0 +1,288 @@
+// extern "C" entry points of memsolve_equilibrium_sm100.so (declared in include/memsolve_b200.h):
+// argument checking, launch planning and the order of kernel launches.  No allocation, no
+// host synchronisation; every launch goes to the caller's stream.
+#include <atomic>
+
+#include "ms_common.cuh"
+
+namespace ms {
+
+int launch_stats(const ms_shape&, const Plan&, bool grad, const void* projected, const void* dy,
+                 const float* cos, const float* sin, float* partials, float* de_partials, cudaStream_t);
+int launch_pack_stats(const ms_shape&, const Plan&, bool grad, const float* partials, const float* de_partials,
+                      const float* counts, float* packed, cudaStream_t);
+int launch_core_forward(const ms_shape&, const float* base_raw, const float* eta_raw, const ms_tape&, cudaStream_t);
+int launch_compact_forward(const ms_shape&, const Plan&, const float* counts, const float* partials, bool packed,
+                           const ms_tape&, cudaStream_t);
+int launch_compact_backward(const ms_shape&, const Plan&, const float* counts, const float* partials,
+                            const float* de_partials, bool packed, const ms_tape&, float* hmat, float* de_sys,
+                            void* gram_grad, void* cross_grad, cudaStream_t);
+int launch_core_backward(const ms_shape&, const float* base_raw, const float* hmat, const float* de_sys,
+                         const ms_tape&, float grad_scale, float* d_base, float* d_eta_raw, cudaStream_t);
+int launch_readout(const ms_shape&, const Plan&, const void* projected, const float* cos, const float* sin,
+                   const float* counts, const ms_tape&, void* mixed, cudaStream_t);
+int launch_token_backward(const ms_shape&, const Plan&, const void* projected, const void* dy, const float* cos,
+                          const float* sin, const float* counts, const ms_tape&, const void* gram_grad,
+                          const void* cross_grad, void* dprojected, cudaStream_t);
+
+static std::atomic<int> g_sm_count[64];
+
+int sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int v = g_sm_count[dev].load(std::memory_order_relaxed);
+  if (v > 0) return v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+    cudaGetLastError();
+    return 148;
+  }
+  g_sm_count[dev].store(v, std::memory_order_relaxed);
+  return v;
+}
+
+static int device_status() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MS_ERR_DEVICE;
+  int v = cached[dev].load(std::memory_order_relaxed);
+  if (v == 1) return MS_OK;
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return MS_ERR_DEVICE;
+  if (major != 10 && major != 11) return MS_ERR_DEVICE;
+  cached[dev].store(1, std::memory_order_relaxed);
+  return MS_OK;
+}
+
+int check_shape(const ms_shape* s) {
+  if (!s) return MS_ERR_INVALID_ARGUMENT;
+  if (s->batch <= 0 || s->tokens <= 0 || s->heads <= 0 || s->head_dim <= 0) return MS_ERR_INVALID_ARGUMENT;
+  if (s->rank != 16 && s->rank != 32 && s->rank != 48 && s->rank != 64) return MS_ERR_UNSUPPORTED_RANK;
+  if (s->rotary_rows != 0 && s->rotary_rows != 1 && s->rotary_rows != s->batch) return MS_ERR_INVALID_ARGUMENT;
+  if (s->rotary_rows != 0 && (s->head_dim & 1)) return MS_ERR_ODD_HEAD_DIM;
+  if (s->reserved != 0) return MS_ERR_INVALID_ARGUMENT;
+  if ((long long)s->batch * s->heads > 0x3fffffffLL) return MS_ERR_INVALID_ARGUMENT;
+  return MS_OK;
+}
+
+static size_t round64(size_t v) { return (v + 63) & ~size_t(63); }
+
+Plan make_plan(const ms_shape& s) {
+  Plan p;
+  p.systems = s.batch * s.heads;
+  p.dblocks = (s.head_dim + kChanBlock - 1) / kChanBlock;
+  p.dpad = (s.head_dim + 7) & ~7;
+  const int tiles = (s.tokens + kTileTokens - 1) / kTileTokens;
+  const long want = 2L * sm_count();
+  long per = (long)p.systems * p.dblocks;
+  long chunks = (want + per - 1) / per;
+  if (chunks < 1) chunks = 1;
+  if (chunks > tiles) chunks = tiles;
+  const int tiles_per_chunk = (int)((tiles + chunks - 1) / chunks);
+  p.chunk_tokens = tiles_per_chunk * kTileTokens;
+  p.chunks = (s.tokens + p.chunk_tokens - 1) / p.chunk_tokens;
+  p.aligned = (s.head_dim % 8) == 0;
+  p.fwd_partial_floats = (size_t)s.rank * s.rank + (size_t)s.rank * s.head_dim;
+  p.bwd_partial_floats = (size_t)s.rank * s.head_dim;
+  p.ws_partials = round64((size_t)p.systems * p.chunks * p.fwd_partial_floats);
+  p.ws_de = round64((size_t)p.systems * p.chunks * p.dblocks);
+  p.ws_hmat = round64((size_t)p.systems * s.rank * s.rank);
+  p.ws_de_sys = round64((size_t)p.systems);
+  p.ws_total_bytes = (p.ws_partials + p.ws_de + p.ws_hmat + p.ws_de_sys) * sizeof(float);
+  return p;
+}
+
+struct Workspace {
+  float* partials;
+  float* de_partials;
+  float* hmat;
+  float* de_sys;
+};
+
+static Workspace carve(void* ws, const Plan& p) {
+  Workspace w;
+  w.partials = static_cast<float*>(ws);
+  w.de_partials = w.partials + p.ws_partials;
+  w.hmat = w.de_partials + p.ws_de;
+  w.de_sys = w.hmat + p.ws_hmat;
+  return w;
+}
+
+static bool is16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace ms
+
+using namespace ms;
+
+#define MS_TRY(expr)            \
+  do {                          \
+    int _st = (expr);           \
+    if (_st != MS_OK) return _st; \
+  } while (0)
+
+extern "C" {
+
+int ms_abi_version(void) { return MS_ABI_VERSION; }
+
+int ms_supported_architectures(int32_t* out, int capacity) {
+  if (out && capacity > 0) out[0] = 100;
+  return 1;
+}
+
+const char* ms_status_string(int status) {
+  switch (status) {
+    case MS_OK: return "ok";
+    case MS_ERR_INVALID_ARGUMENT: return "invalid argument (null pointer, non-positive size or bad rotary_rows)";
+    case MS_ERR_UNSUPPORTED_RANK: return "the CUDA fast path supports rank in {16,32,48,64}";
+    case MS_ERR_WORKSPACE: return "workspace is null or smaller than ms_workspace_bytes()";
+    case MS_ERR_LAUNCH: return "a CUDA kernel launch failed";
+    case MS_ERR_DEVICE: return "the current CUDA device is not an sm_100-class GPU";
+    case MS_ERR_ODD_HEAD_DIM: return "rotary content requires an even head dimension";
+  }
+  return "unknown status";
+}
+
+int ms_padded_head_dim(int head_dim) { return (head_dim + 7) & ~7; }
+
+size_t ms_workspace_bytes(const ms_shape* shape) {
+  if (check_shape(shape) != MS_OK) return 0;
+  return make_plan(*shape).ws_total_bytes;
+}
+
+size_t ms_packed_stats_floats(const ms_shape* shape, int backward) {
+  if (check_shape(shape) != MS_OK) return 0;
+  const size_t sys = (size_t)shape->batch * shape->heads;
+  const size_t rd = (size_t)shape->rank * shape->head_dim;
+  return backward ? sys * (rd + 1) : sys * ((size_t)shape->rank * shape->rank + rd);
+}
+
+int ms_core_forward(const ms_shape* shape, const float* base_raw, const float* eta_raw, const ms_tape* tape,
+                    void* stream) {
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  if (!eta_raw || !tape || !tape->eta || !tape->eta_slope || !tape->core_info) return MS_ERR_INVALID_ARGUMENT;
+  if (!shape->complement && (!base_raw || !tape->core_map)) return MS_ERR_INVALID_ARGUMENT;
+  return launch_core_forward(*shape, base_raw, eta_raw, *tape, static_cast<cudaStream_t>(stream));
+}
+
+int ms_stats_forward(const ms_shape* shape, const void* projected, const float* cos, const float* sin,
+                     const float* counts, void* workspace, size_t workspace_bytes, float* packed, void* stream) {
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  if (!projected) return MS_ERR_INVALID_ARGUMENT;
+  if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
+  Plan plan = make_plan(*shape);
+  if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+  plan.aligned = plan.aligned && is16(projected) && (!shape->rotary_rows || (is16(cos) && is16(sin)));
+  const Workspace w = carve(workspace, plan);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MS_TRY(launch_stats(*shape, plan, false, projected, nullptr, cos, sin, w.partials, nullptr, st));
+  if (packed) MS_TRY(launch_pack_stats(*shape, plan, false, w.partials, nullptr, counts, packed, st));
+  return MS_OK;
+}
+
+int ms_compact_forward(const ms_shape* shape, const float* counts, const void* workspace, size_t workspace_bytes,
+                       const float* packed, const ms_tape* tape, void* stream) {
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  if (!tape || !tape->eta || !tape->inverse || !tape->state || !tape->coeff) return MS_ERR_INVALID_ARGUMENT;
+  if (!shape->complement && !tape->core_map) return MS_ERR_INVALID_ARGUMENT;
+  const Plan plan = make_plan(*shape);
+  const float* src = packed;
+  if (!packed) {
+    if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+    src = static_cast<const float*>(workspace);
+  }
+  return launch_compact_forward(*shape, plan, counts, src, packed != nullptr, *tape,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int ms_readout(const ms_shape* shape, const void* projected, const float* cos, const float* sin,
+               const float* counts, const ms_tape* tape, void* mixed, void* stream) {
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  if (!projected || !mixed || !tape || !tape->eta || !tape->coeff) return MS_ERR_INVALID_ARGUMENT;
+  if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
+  Plan plan = make_plan(*shape);
+  plan.aligned = plan.aligned && is16(projected) && is16(mixed);
+  return launch_readout(*shape, plan, projected, cos, sin, counts, *tape, mixed, static_cast<cudaStream_t>(stream));
+}
+
+int ms_mix_forward(const ms_shape* shape, const void* projected, const float* base_raw, const float* eta_raw,
+                   const float* cos, const float* sin, const float* counts, void* workspace,
+                   size_t workspace_bytes, const ms_tape* tape, void* mixed, void* stream) {
+  MS_TRY(ms_core_forward(shape, base_raw, eta_raw, tape, stream));
+  MS_TRY(ms_stats_forward(shape, projected, cos, sin, counts, workspace, workspace_bytes, nullptr, stream));
+  MS_TRY(ms_compact_forward(shape, counts, workspace, workspace_bytes, nullptr, tape, stream));
+  return ms_readout(shape, projected, cos, sin, counts, tape, mixed, stream);
+}
+
+int ms_stats_backward(const ms_shape* shape, const void* projected, const void* dy, const float* cos,
+                      const float* sin, const float* counts, void* workspace, size_t workspace_bytes,
+                      float* packed, void* stream) {
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  if (!projected || !dy) return MS_ERR_INVALID_ARGUMENT;
+  if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
+  Plan plan = make_plan(*shape);
+  if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+  plan.aligned = plan.aligned && is16(projected) && is16(dy) && (!shape->rotary_rows || (is16(cos) && is16(sin)));
+  const Workspace w = carve(workspace, plan);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MS_TRY(launch_stats(*shape, plan, true, projected, dy, cos, sin, w.partials, w.de_partials, st));
+  if (packed) MS_TRY(launch_pack_stats(*shape, plan, true, w.partials, w.de_partials, counts, packed, st));
+  return MS_OK;
+}
+
+int ms_compact_backward(const ms_shape* shape, const float* counts, void* workspace, size_t workspace_bytes,
+                        const float* packed, const ms_tape* tape, const float* base_raw, const float* eta_raw,
+                        float grad_scale, void* gram_grad, void* cross_grad, float* d_base_raw,
+                        float* d_eta_raw, void* stream) {
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  (void)eta_raw;
+  if (!tape || !tape->eta || !tape->eta_slope || !tape->inverse || !tape->state) return MS_ERR_INVALID_ARGUMENT;
+  if (!gram_grad || !cross_grad || !d_eta_raw) return MS_ERR_INVALID_ARGUMENT;
+  if (!shape->complement && (!base_raw || !tape->core_map || !d_base_raw)) return MS_ERR_INVALID_ARGUMENT;
+  const Plan plan = make_plan(*shape);
+  if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+  const Workspace w = carve(workspace, plan);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MS_TRY(launch_compact_backward(*shape, plan, counts, packed ? packed : w.partials, w.de_partials,
+                                 packed != nullptr, *tape, w.hmat, w.de_sys, gram_grad, cross_grad, st));
+  return launch_core_backward(*shape, base_raw, w.hmat, w.de_sys, *tape, grad_scale, d_base_raw, d_eta_raw, st);
+}
+
+int ms_token_backward(const ms_shape* shape, const void* projected, const void* dy, const float* cos,
+                      const float* sin, const float* counts, const ms_tape* tape, const void* gram_grad,
+                      const void* cross_grad, void* dprojected, void* stream) {
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  if (!projected || !dy || !dprojected || !gram_grad || !cross_grad || !tape || !tape->eta || !tape->coeff)
+    return MS_ERR_INVALID_ARGUMENT;
+  if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
+  Plan plan = make_plan(*shape);
+  plan.aligned = plan.aligned && is16(projected) && is16(dy) && is16(dprojected);
+  return launch_token_backward(*shape, plan, projected, dy, cos, sin, counts, *tape, gram_grad, cross_grad,
+                               dprojected, static_cast<cudaStream_t>(stream));
+}
+
+int ms_mix_backward(const ms_shape* shape, const void* projected, const void* dy, const float* base_raw,
+                    const float* eta_raw, const float* cos, const float* sin, const float* counts,
+                    void* workspace, size_t workspace_bytes, const ms_tape* tape, void* gram_grad,
+                    void* cross_grad, void* dprojected, float* d_base_raw, float* d_eta_raw, void* stream) {
+  MS_TRY(ms_stats_backward(shape, projected, dy, cos, sin, counts, workspace, workspace_bytes, nullptr, stream));
+  (void)eta_raw;
+  if (!tape || !tape->eta || !tape->eta_slope || !tape->inverse || !tape->state) return MS_ERR_INVALID_ARGUMENT;
+  if (!gram_grad || !cross_grad || !d_eta_raw) return MS_ERR_INVALID_ARGUMENT;
+  if (!shape->complement && (!base_raw || !tape->core_map || !d_base_raw)) return MS_ERR_INVALID_ARGUMENT;
+  const Plan plan = make_plan(*shape);
+  const Workspace w = carve(workspace, plan);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MS_TRY(launch_compact_backward(*shape, plan, counts, w.partials, w.de_partials, false, *tape, w.hmat,
+                                 w.de_sys, gram_grad, cross_grad, st));
+  // the token pass needs only dG and dQ; the per-head core adjoint follows it
+  MS_TRY(ms_token_backward(shape, projected, dy, cos, sin, counts, tape, gram_grad, cross_grad, dprojected, stream));
+  return launch_core_backward(*shape, base_raw, w.hmat, w.de_sys, *tape, 1.0f, d_base_raw, d_eta_raw, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,293 @@
+"""GPU parity of the mixer kernels (called through the C-ABI library) against the CPU oracle
+and the committed golden vectors.  Metric: relative L2, as in the reference's own CUDA tests
+(tests/cuda/test_fast_path.py:85-99); limits follow those tests (forward 5e-3, gradients 3e-2,
+rotary dprojected 5e-3) and are written at each assertion."""
+from __future__ import annotations
+
+import ctypes
+
+import pytest
+import torch
+
+from conftest import load_golden, rel_l2
+from oracle import memsolve_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cuda_mod():
+    from memsolve_b200.ball import cuda
+    cuda.load()
+    assert cuda.is_available()
+    return cuda
+
+
+def _dev(t):
+    return None if t is None else t.cuda()
+
+
+def _run_fast(cuda_mod, proj, base, eta_raw, counts, cos, sin, dy):
+    ins = [proj.cuda().requires_grad_(), base.cuda().requires_grad_(), eta_raw.cuda().requires_grad_()]
+    y = cuda_mod.fast_mix(ins[0], ins[1], ins[2], _dev(counts), rotary_cos=_dev(cos), rotary_sin=_dev(sin))
+    grads = torch.autograd.grad((y.float() * dy.cuda().float()).sum(), ins, allow_unused=True)
+    torch.cuda.synchronize()
+    return y, grads
+
+
+def _run_oracle(proj, base, eta_raw, counts, cos, sin, dy):
+    ins = [proj.double().requires_grad_(), base.double().requires_grad_(), eta_raw.double().requires_grad_()]
+    y = O.fast_mix_frame(ins[0], ins[1], ins[2], counts, cos, sin)
+    wanted = [ins[0], ins[2]] if base.numel() == 0 else ins
+    g = torch.autograd.grad((y * dy.double()).sum(), wanted)
+    gp, ge = g[0], g[-1]
+    gb = g[1] if base.numel() else torch.zeros_like(base, dtype=torch.float64)
+    return y, (gp, gb, ge)
+
+
+def _assert_case(cuda_mod, proj, base, eta_raw, counts, cos, sin, dy, *, fwd=5e-3, gproj=3e-2, gpar=3e-2,
+                 expected=None, tag=""):
+    y, grads = _run_fast(cuda_mod, proj, base, eta_raw, counts, cos, sin, dy)
+    ey, eg = expected if expected is not None else _run_oracle(proj, base, eta_raw, counts, cos, sin, dy)
+    assert y.dtype == torch.bfloat16 and torch.isfinite(y.float()).all()
+    errs = {"y": rel_l2(y, ey), "dproj": rel_l2(grads[0], eg[0]), "deta": rel_l2(grads[2], eg[2])}
+    if base.numel():
+        errs["dbase"] = rel_l2(grads[1], eg[1])
+    print(tag, {k: f"{v:.2e}" for k, v in errs.items()})
+    assert errs["y"] <= fwd, errs
+    assert errs["dproj"] <= gproj, errs
+    assert errs["deta"] <= gpar, errs
+    if base.numel():
+        assert errs["dbase"] <= gpar, errs
+    return errs
+
+
+GOLDEN = ["mix_r16_plain", "mix_r32_rot", "mix_r16_comp_rot_mask", "mix_r48_strong", "mix_r64_rot_mask",
+          "mix_r16_short"]
+
+
+@pytest.mark.parametrize("name", GOLDEN)
+def test_golden_vectors(cuda_mod, name):
+    g = load_golden(name + ".npz")
+    expected = (g["y"], (g["d_projected"], g["d_base"], g["d_eta_raw"]))
+    _assert_case(cuda_mod, g["projected"].bfloat16(), g["base"], g["eta_raw"], g.get("counts"), g.get("cos"),
+                 g.get("sin"), g["dy"].bfloat16(), expected=expected, tag=name)
+
+
+def _random_case(seed, b, n, h, r, d, *, comp=False, rot=False, masked=False, base_scale=0.1, rel_scale=1.0,
+                 batched_table=False):
+    gen = torch.Generator().manual_seed(seed)
+    proj = torch.randn(b, n, h * r + h * d, generator=gen)
+    proj[..., : h * r] *= rel_scale
+    counts = None
+    if masked:
+        mask = torch.rand(b, n, generator=gen) > 0.3
+        mask[-1] = False if b > 1 else mask[-1]
+        proj = torch.where(mask[:, :, None], proj, torch.zeros_like(proj))
+        counts = mask.sum(-1).float().clamp_min(1.0)
+    proj = proj.bfloat16()
+    base = torch.randn(h, r, 0 if comp else r, generator=gen) * base_scale
+    eta_raw = torch.randn(h, generator=gen) * 0.5
+    dy = torch.randn(b, n, h * d, generator=gen).bfloat16()
+    if masked:
+        dy = torch.where(mask[:, :, None], dy, torch.zeros_like(dy))
+    cos = sin = None
+    if rot:
+        if batched_table:
+            pos = torch.stack([torch.arange(n) + 3 * i for i in range(b)])
+        else:
+            pos = torch.arange(n)[None]
+        cos, sin = O.rotary_tables(pos, head_dim=d, train_length=16, context_length=n)
+    return proj, base, eta_raw, counts, cos, sin, dy
+
+
+@pytest.mark.parametrize("length", (31, 33, 64, 65, 127, 128, 129, 257, 513))
+def test_lengths_around_tile_edges(cuda_mod, length):
+    """Shapes of tests/cuda/test_fast_path.py:692-743 (B=1, H=2, D=32, r=16)."""
+    case = _random_case(19 + length, 1, length, 2, 16, 16)
+    _assert_case(cuda_mod, *case, tag=f"N={length}")
+
+
+@pytest.mark.parametrize(
+    ("batch", "rank", "heads", "head_dim", "length"),
+    [(1, 16, 1, 1, 31), (1, 16, 1, 17, 31), (1, 16, 1, 33, 33), (1, 16, 1, 257, 33), (1, 32, 2, 48, 31),
+     (2, 32, 3, 17, 35), (1, 48, 2, 96, 33), (1, 64, 1, 33, 33), (1, 64, 1, 17, 2017), (1, 32, 8, 32, 4096),
+     (1, 16, 4, 32, 4776), (1, 32, 1, 17, 8193), (3, 32, 2, 64, 197), (2, 64, 2, 64, 300)],
+)
+def test_generic_shapes(cuda_mod, batch, rank, heads, head_dim, length):
+    """Head dims off the 8/16/64 grids, all ranks, multi-chunk lengths
+    (tests/cuda/test_fast_path.py:847-932)."""
+    case = _random_case(71 + batch + rank + head_dim, batch, length, heads, rank, head_dim, base_scale=0.05)
+    _assert_case(cuda_mod, *case, tag=f"B{batch} r{rank} H{heads} d{head_dim} N{length}")
+
+
+@pytest.mark.parametrize("comp", [False, True])
+@pytest.mark.parametrize("rank", [16, 32, 48, 64])
+@pytest.mark.parametrize("length,head_dim", [(7, 8), (129, 64), (200, 18)])
+def test_rotary_modes_ranks(cuda_mod, comp, rank, length, head_dim):
+    """RoVE on every rank and both core modes (tests/cuda/test_fast_path.py:1805-1866); the
+    reference bounds the rotary forward and dprojected at 5e-3."""
+    case = _random_case(500 + rank + length, 2, length, 2, rank, head_dim, comp=comp, rot=True,
+                        batched_table=(length == 129))
+    _assert_case(cuda_mod, *case, gproj=5e-3, gpar=5e-3, tag=f"rot comp={comp} r{rank} N{length} d{head_dim}")
+
+
+@pytest.mark.parametrize("rank,head_dim,length", [(16, 17, 35), (32, 64, 35), (64, 257, 35), (64, 17, 2017)])
+def test_masked_rows_and_empty_samples(cuda_mod, rank, head_dim, length):
+    """Gapped masks and a fully masked sample (tests/cuda/test_fast_path.py:936-1024)."""
+    case = _random_case(97 + rank + head_dim, 2, length, 2, rank, head_dim, masked=True, base_scale=0.05)
+    proj, base, eta_raw, counts, cos, sin, dy = case
+    _assert_case(cuda_mod, *case, tag=f"masked r{rank} d{head_dim} N{length}")
+    y = cuda_mod.fast_mix(proj.cuda(), base.cuda(), eta_raw.cuda(), counts.cuda())
+    assert torch.count_nonzero(y[1]) == 0  # all-masked sample: zero rows stay zero
+
+
+@pytest.mark.parametrize("rel_scale,eta_value,base_scale", [(64.0, 9.5, 4.0), (0.001, -9.5, 0.0), (8.0, 0.3, 1.0)])
+def test_numerical_boundaries(cuda_mod, rel_scale, eta_value, base_scale):
+    """Strong relations, saturated eta, large core (tests/cuda/test_fast_path.py:1385-1427)."""
+    proj, base, eta_raw, counts, cos, sin, dy = _random_case(7, 2, 150, 2, 32, 32, rel_scale=rel_scale,
+                                                             base_scale=base_scale)
+    eta_raw = torch.full_like(eta_raw, eta_value)
+    y, grads = _run_fast(cuda_mod, proj, base, eta_raw, counts, cos, sin, dy)
+    ey, eg = _run_oracle(proj, base, eta_raw, counts, cos, sin, dy)
+    assert all(torch.isfinite(g).all() for g in grads)
+    assert rel_l2(y, ey) <= 1.5e-2
+    assert rel_l2(grads[0], eg[0]) <= 3.5e-2
+
+
+def test_correction_term_alone(cuda_mod):
+    """mixed - eta*C isolates the compact path, which is only a few percent of `mixed`
+    at default initialisation."""
+    proj, base, eta_raw, counts, cos, sin, dy = _random_case(11, 1, 1024, 4, 32, 64, rot=True)
+    heads, rank, d = 4, 32, 64
+    y = cuda_mod.fast_mix(proj.cuda(), base.cuda(), eta_raw.cuda(), rotary_cos=cos.cuda(), rotary_sin=sin.cuda())
+    ey = O.fast_mix_frame(proj, base, eta_raw, None, cos, sin)
+    eta = O.bounded_eta(eta_raw.double())
+    content = proj[..., heads * rank:].double().reshape(1, 1024, heads, d) * eta.view(1, 1, heads, 1)
+    content = content.reshape(1, 1024, heads * d)
+    got = y.double().cpu() - content
+    want = ey - content
+    # the BF16 store of `mixed` dominates: its rounding is ~2^-9 of |mixed| ~ 20x the correction
+    assert rel_l2(got, want) <= 8e-2
+
+
+def test_bitwise_repeatability(cuda_mod):
+    """Two evaluations give identical bits (fixed-order reductions, no atomics)."""
+    proj, base, eta_raw, counts, cos, sin, dy = _random_case(5, 2, 3000, 3, 32, 64, rot=True)
+    a = _run_fast(cuda_mod, proj, base, eta_raw, counts, cos, sin, dy)
+    b = _run_fast(cuda_mod, proj, base, eta_raw, counts, cos, sin, dy)
+    assert torch.equal(a[0], b[0])
+    for ga, gb in zip(a[1], b[1]):
+        assert torch.equal(ga, gb)
+
+
+def test_inputs_are_not_mutated(cuda_mod):
+    proj, base, eta_raw, counts, cos, sin, dy = _random_case(3, 1, 200, 2, 16, 32, rot=True)
+    dev = [t.cuda() for t in (proj, base, eta_raw, cos, sin)]
+    keep = [t.clone() for t in dev]
+    p = dev[0].requires_grad_()
+    y = cuda_mod.fast_mix(p, dev[1], dev[2], rotary_cos=dev[3], rotary_sin=dev[4])
+    y.backward(dy.cuda())
+    for a, b in zip(dev, keep):
+        assert torch.equal(a.detach(), b)
+
+
+# ---------------------------------------------------------------------------------------
+# stage-wise checks straight through ctypes
+# ---------------------------------------------------------------------------------------
+def _stage_buffers(cuda_mod, proj, base, cos):
+    shape, dims = cuda_mod._make_shape(proj, base, cos)
+    tape = cuda_mod._alloc_tape(dims, proj.device)
+    ws = cuda_mod._workspace(shape, proj.device)
+    return shape, dims, tape, ws
+
+
+@pytest.mark.parametrize("rank,head_dim,length,rot", [(32, 64, 5000, True), (64, 64, 777, False), (16, 24, 130, True),
+                                                      (48, 70, 333, True)])
+def test_stagewise_forward(cuda_mod, rank, head_dim, length, rot):
+    """Statistics <= 1e-5, inverse factor <= 2e-6, coefficients <= 2e-5 against FP64
+    (limits of tests/cuda/test_fast_path.py:1752, 2122-2123 for the compact stages)."""
+    lib = cuda_mod._LIB
+    heads, batch = 2, 2
+    proj, base, eta_raw, counts, cos, sin, dy = _random_case(900 + rank, batch, length, heads, rank, head_dim, rot=rot)
+    dp, db, de = proj.cuda(), base.cuda(), eta_raw.cuda()
+    dcos, dsin = _dev(cos), _dev(sin)
+    shape, dims, tape, ws = _stage_buffers(cuda_mod, dp, db, dcos)
+    tape_c = tape.as_struct()
+    stream = torch.cuda.current_stream().cuda_stream
+    packed = torch.empty(lib.ms_packed_stats_floats(ctypes.byref(shape), 0), device="cuda")
+    ptr = cuda_mod._ptr
+    assert lib.ms_core_forward(ctypes.byref(shape), db.data_ptr(), de.data_ptr(), ctypes.byref(tape_c), stream) == 0
+    assert lib.ms_stats_forward(ctypes.byref(shape), dp.data_ptr(), ptr(dcos), ptr(dsin), None, ws.data_ptr(),
+                                ws.numel(), packed.data_ptr(), stream) == 0
+    assert lib.ms_compact_forward(ctypes.byref(shape), None, ws.data_ptr(), ws.numel(), None,
+                                  ctypes.byref(tape_c), stream) == 0
+    torch.cuda.synchronize()
+    g, q = O.stage_stats(proj, heads, rank, None, cos, sin)
+    t, z, f, eta, w = O.stage_compact(g, q, base, eta_raw)
+    pk = packed.view(batch * heads, rank * rank + rank * head_dim).cpu()
+    got_g = pk[:, : rank * rank].reshape(batch, heads, rank, rank)
+    got_q = pk[:, rank * rank:].reshape(batch, heads, rank, head_dim)
+    assert rel_l2(got_g, g) <= 1e-5 and rel_l2(got_q, q) <= 1e-5
+    assert rel_l2(tape.core_map, f) <= 2e-5
+    assert rel_l2(tape.eta, eta) <= 1e-6
+    assert int(tape.core_info.abs().sum()) == 0
+    assert rel_l2(tape.inverse, t) <= 2e-6
+    assert rel_l2(tape.state, z) <= 1e-5
+    coeff = tape.coeff.float().sum(dim=2)[..., :head_dim]
+    assert rel_l2(coeff, w) <= 2e-5
+    # the same compact result from the packed (all-reduce) path
+    tape2 = cuda_mod._alloc_tape(dims, dp.device)
+    t2c = tape2.as_struct()
+    assert lib.ms_core_forward(ctypes.byref(shape), db.data_ptr(), de.data_ptr(), ctypes.byref(t2c), stream) == 0
+    assert lib.ms_compact_forward(ctypes.byref(shape), None, None, 0, packed.data_ptr(), ctypes.byref(t2c), stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(tape2.inverse, tape.inverse) and torch.equal(tape2.coeff, tape.coeff)
+
+
+def test_fp32_readout_before_rounding(cuda_mod):
+    """On an identical BF16 projection the coefficients W in FP32 reproduce the reference's
+    frame formulation to <= 1e-4 (the FP32 criterion), checked before the BF16 store by
+    evaluating eta*C + A W with the kernel's W on the host."""
+    heads, rank, d, n = 3, 32, 64, 4096
+    proj, base, eta_raw, counts, cos, sin, dy = _random_case(31, 1, n, heads, rank, d, rot=True)
+    dp, db, de = proj.cuda(), base.cuda(), eta_raw.cuda()
+    shape, dims, tape, ws = _stage_buffers(cuda_mod, dp, db, cos.cuda())
+    mixed = cuda_mod.fast_mix(dp, db, de, rotary_cos=cos.cuda(), rotary_sin=sin.cuda())
+    # recover W from a fresh forward tape
+    y2, tape, dims = cuda_mod._mix_forward(dp, db, de, None, None, cos.cuda(), sin.cuda())
+    torch.cuda.synchronize()
+    w = tape.coeff.float().sum(dim=2)[..., :d].cpu()
+    y32 = O.stage_readout(proj, w, tape.eta.cpu(), heads, rank, None, cos, sin, dtype=torch.float32)
+    want = O.fast_mix_frame(proj, base, eta_raw, None, cos, sin)
+    assert rel_l2(y32, want) <= 1e-4
+    assert rel_l2(mixed, want) <= 5e-3
+    assert torch.equal(mixed, y2)
+
+
+def test_full_size_config3(cuda_mod):
+    """BASELINE configuration 3 (B=1, N=32768, D=768, H=12, r=32, rotary): direct comparison
+    with the FP64 oracle at full size, forward and all gradients."""
+    heads, rank, d, n = 12, 32, 64, 32768
+    gen = torch.Generator().manual_seed(0)
+    proj = (torch.randn(1, n, heads * (rank + d), generator=gen) * 0.6).bfloat16()
+    base = torch.randn(heads, rank, rank, generator=gen) * 0.1
+    eta_raw = torch.full((heads,), 1.4722) + torch.randn(heads, generator=gen) * 0.1
+    dy = torch.randn(1, n, heads * d, generator=gen).bfloat16()
+    cos, sin = O.rotary_tables(torch.arange(n)[None], head_dim=d, train_length=128, context_length=n)
+    _assert_case(cuda_mod, proj, base, eta_raw, None, cos, sin, dy, gproj=5e-3, tag="config3")
+
+
+def test_rejects_bad_inputs(cuda_mod):
+    proj, base, eta_raw, counts, cos, sin, dy = _random_case(1, 1, 40, 2, 16, 8)
+    with pytest.raises(RuntimeError, match="mixed precision CUDA contract"):
+        cuda_mod.fast_mix(proj.cuda().float(), base.cuda(), eta_raw.cuda())
+    with pytest.raises(RuntimeError, match="rank in"):
+        cuda_mod.fast_mix(torch.zeros(1, 40, 2 * 8 + 16, device="cuda", dtype=torch.bfloat16),
+                          torch.zeros(2, 8, 8, device="cuda"), eta_raw.cuda())
+    with pytest.raises(ValueError, match="supplied together"):
+        cuda_mod.fast_mix(proj.cuda(), base.cuda(), eta_raw.cuda(), rotary_cos=torch.zeros(1, 40, 4, device="cuda"))
+    lib = cuda_mod._LIB
+    shape, dims = cuda_mod._make_shape(proj.cuda(), base.cuda(), None)
+    assert lib.ms_stats_forward(ctypes.byref(shape), proj.cuda().data_ptr(), None, None, None, None, 0, None,
+                                None) == 3  # MS_ERR_WORKSPACE
