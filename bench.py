@@ -195,7 +195,7 @@ def workload_config(args, cfg, world):
 # ---------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------
-def time_kernels(layer, cfg, tokens, device, reps=10):
+def time_kernels(layer, cfg, tokens, device, reps=10, warm=3):
     """Each mixer kernel alone, CUDA events on the launching stream, L2 flushed before each launch."""
     import ctypes
     from memsolve_b200.ball import cuda as C
@@ -248,7 +248,7 @@ def time_kernels(layer, cfg, tokens, device, reps=10):
     flush = torch.empty(256 * 1024 * 1024, device=device, dtype=torch.uint8)
     out = {}
     for name, fn in calls.items():
-        for _ in range(3):
+        for _ in range(warm):
             assert fn() == 0
         ts = []
         for _ in range(reps):
@@ -321,13 +321,22 @@ def run_ours(args, cfg):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    for _ in range(max(args.warmup, 3)):
-        step(x, dout)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step(x, dout)
     total = timed(lambda: step(x, dout), args.steps)
+    # nvidia-smi samples every 100 ms and the timed region lasts milliseconds: keep the same step
+    # running (untimed) for about a second so that the clock record covers this load
+    t_end = time.perf_counter() + 1.2
+    while time.perf_counter() < t_end:
+        for _ in range(20):
+            step(x, dout)
+        torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        clocks["window"] = "warm-up + timed steps + 1.2 s of the same step"
 
     # end to end: inputs start in pinned host memory every step, a scalar result comes back
     x_dev = torch.empty_like(x_host, device=device).requires_grad_()
@@ -402,8 +411,22 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", choices=tuple(CONFIGS), default="c3")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="launch each mixer kernel alone (--reps times) and print their timings; used for ncu")
+    ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--kernel-warmup", type=int, default=3)
     args = ap.parse_args()
     cfg = CONFIGS[args.workload]
+    if args.kernels_only:
+        from memsolve_b200.ball import cuda as C
+        device = torch.device("cuda", 0)
+        torch.cuda.set_device(device)
+        C.load(device=device)
+        tokens = cfg["global_tokens"] // args.gpus if cfg["strong"] else cfg["local_tokens"]
+        kern = time_kernels(build_layer(cfg, device), cfg, tokens, device, reps=args.reps, warm=args.kernel_warmup)
+        print(json.dumps({k: {"us": round(v["s"] * 1e6, 2), "gbs": round(v["bytes"] / v["s"] / 1e9, 1)}
+                          for k, v in kern.items()}))
+        return
     if args.impl == "reference":
         run_reference(args, cfg)
     else:

@@ -8,7 +8,8 @@
 namespace ms {
 
 int launch_stats(const ms_shape&, const Plan&, bool grad, const void* projected, const void* dy,
-                 const float* cos, const float* sin, float* partials, float* de_partials, cudaStream_t);
+                 const float* cos, const float* sin, float* partials, float* de_partials,
+                 const float* base_raw, const float* eta_raw, const ms_tape* core_tape, cudaStream_t);
 int launch_pack_stats(const ms_shape&, const Plan&, bool grad, const float* partials, const float* de_partials,
                       const float* counts, float* packed, cudaStream_t);
 int launch_core_forward(const ms_shape&, const float* base_raw, const float* eta_raw, const ms_tape&, cudaStream_t);
@@ -23,7 +24,7 @@ int launch_readout(const ms_shape&, const Plan&, const void* projected, const fl
                    const float* counts, const ms_tape&, void* mixed, cudaStream_t);
 int launch_token_backward(const ms_shape&, const Plan&, const void* projected, const void* dy, const float* cos,
                           const float* sin, const float* counts, const ms_tape&, const void* gram_grad,
-                          const void* cross_grad, void* dprojected, cudaStream_t);
+                          const void* cross_grad, void* dprojected, const CoreAdjoint* core, cudaStream_t);
 
 static std::atomic<int> g_sm_count[64];
 
@@ -175,7 +176,8 @@ int ms_stats_forward(const ms_shape* shape, const void* projected, const float* 
   plan.aligned = plan.aligned && is16(projected) && (!shape->rotary_rows || (is16(cos) && is16(sin)));
   const Workspace w = carve(workspace, plan);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  MS_TRY(launch_stats(*shape, plan, false, projected, nullptr, cos, sin, w.partials, nullptr, st));
+  MS_TRY(launch_stats(*shape, plan, false, projected, nullptr, cos, sin, w.partials, nullptr, nullptr, nullptr,
+                      nullptr, st));
   if (packed) MS_TRY(launch_pack_stats(*shape, plan, false, w.partials, nullptr, counts, packed, st));
   return MS_OK;
 }
@@ -210,10 +212,27 @@ int ms_readout(const ms_shape* shape, const void* projected, const float* cos, c
 int ms_mix_forward(const ms_shape* shape, const void* projected, const float* base_raw, const float* eta_raw,
                    const float* cos, const float* sin, const float* counts, void* workspace,
                    size_t workspace_bytes, const ms_tape* tape, void* mixed, void* stream) {
-  MS_TRY(ms_core_forward(shape, base_raw, eta_raw, tape, stream));
-  MS_TRY(ms_stats_forward(shape, projected, cos, sin, counts, workspace, workspace_bytes, nullptr, stream));
-  MS_TRY(ms_compact_forward(shape, counts, workspace, workspace_bytes, nullptr, tape, stream));
-  return ms_readout(shape, projected, cos, sin, counts, tape, mixed, stream);
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  if (!projected || !mixed || !eta_raw || !tape || !tape->eta || !tape->eta_slope || !tape->core_info ||
+      !tape->inverse || !tape->state || !tape->coeff)
+    return MS_ERR_INVALID_ARGUMENT;
+  if (!shape->complement && (!base_raw || !tape->core_map)) return MS_ERR_INVALID_ARGUMENT;
+  if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
+  Plan plan = make_plan(*shape);
+  if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+  const bool tables16 = !shape->rotary_rows || (is16(cos) && is16(sin));
+  const Workspace w = carve(workspace, plan);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Plan stats_plan = plan;
+  stats_plan.aligned = plan.aligned && is16(projected) && tables16;
+  // the per-head core (eta, F) is computed by spare CTAs of the statistics grid
+  MS_TRY(launch_stats(*shape, stats_plan, false, projected, nullptr, cos, sin, w.partials, nullptr, base_raw,
+                      eta_raw, tape, st));
+  MS_TRY(launch_compact_forward(*shape, plan, counts, w.partials, false, *tape, st));
+  Plan read_plan = plan;
+  read_plan.aligned = plan.aligned && is16(projected) && is16(mixed);
+  return launch_readout(*shape, read_plan, projected, cos, sin, counts, *tape, mixed, st);
 }
 
 int ms_stats_backward(const ms_shape* shape, const void* projected, const void* dy, const float* cos,
@@ -228,7 +247,8 @@ int ms_stats_backward(const ms_shape* shape, const void* projected, const void* 
   plan.aligned = plan.aligned && is16(projected) && is16(dy) && (!shape->rotary_rows || (is16(cos) && is16(sin)));
   const Workspace w = carve(workspace, plan);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  MS_TRY(launch_stats(*shape, plan, true, projected, dy, cos, sin, w.partials, w.de_partials, st));
+  MS_TRY(launch_stats(*shape, plan, true, projected, dy, cos, sin, w.partials, w.de_partials, nullptr, nullptr,
+                      nullptr, st));
   if (packed) MS_TRY(launch_pack_stats(*shape, plan, true, w.partials, w.de_partials, counts, packed, st));
   return MS_OK;
 }
@@ -263,7 +283,7 @@ int ms_token_backward(const ms_shape* shape, const void* projected, const void* 
   Plan plan = make_plan(*shape);
   plan.aligned = plan.aligned && is16(projected) && is16(dy) && is16(dprojected);
   return launch_token_backward(*shape, plan, projected, dy, cos, sin, counts, *tape, gram_grad, cross_grad,
-                               dprojected, static_cast<cudaStream_t>(stream));
+                               dprojected, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int ms_mix_backward(const ms_shape* shape, const void* projected, const void* dy, const float* base_raw,
@@ -280,9 +300,13 @@ int ms_mix_backward(const ms_shape* shape, const void* projected, const void* dy
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   MS_TRY(launch_compact_backward(*shape, plan, counts, w.partials, w.de_partials, false, *tape, w.hmat,
                                  w.de_sys, gram_grad, cross_grad, st));
-  // the token pass needs only dG and dQ; the per-head core adjoint follows it
-  MS_TRY(ms_token_backward(shape, projected, dy, cos, sin, counts, tape, gram_grad, cross_grad, dprojected, stream));
-  return launch_core_backward(*shape, base_raw, w.hmat, w.de_sys, *tape, 1.0f, d_base_raw, d_eta_raw, st);
+  // the token pass needs only dG and dQ; the per-head core adjoint rides in spare CTAs of its grid
+  if (!projected || !dy || !dprojected) return MS_ERR_INVALID_ARGUMENT;
+  Plan token_plan = plan;
+  token_plan.aligned = plan.aligned && is16(projected) && is16(dy) && is16(dprojected);
+  CoreAdjoint core{base_raw, w.hmat, w.de_sys, d_base_raw, d_eta_raw, 1.0f};
+  return launch_token_backward(*shape, token_plan, projected, dy, cos, sin, counts, *tape, gram_grad, cross_grad,
+                               dprojected, &core, st);
 }
 
 }  // extern "C"

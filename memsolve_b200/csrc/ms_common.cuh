@@ -32,6 +32,16 @@ struct Plan {
   size_t ws_total_bytes;
 };
 
+// arguments of the per-head core adjoint when it rides along with the token-backward launch
+struct CoreAdjoint {
+  const float* base_raw;
+  const float* hmat;
+  const float* de_sys;
+  float* d_base;
+  float* d_eta_raw;
+  float grad_scale;
+};
+
 Plan make_plan(const ms_shape& s);
 int check_shape(const ms_shape* s);
 int sm_count();

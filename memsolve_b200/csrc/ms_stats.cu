@@ -14,7 +14,7 @@
 // are mma.sync.m16n8k16 with FP32 accumulators held in registers for the whole chunk.
 // Each CTA writes one partial; partials are summed later in fixed order, so the result does
 // not depend on scheduling.
-#include "ms_common.cuh"
+#include "ms_core.cuh"
 
 namespace ms {
 
@@ -39,6 +39,14 @@ struct StatsParams {
   int batch, tokens, heads, head_dim, width, rotary_rows;
   int chunks, chunk_tokens, dblocks;
   int partial_floats;
+  // per-head core, computed by the spare CTAs blockIdx.x == chunks (forward only, optional)
+  const float* base_raw;
+  const float* eta_raw;
+  float* eta;
+  float* eta_slope;
+  float* core_map;
+  int* core_info;
+  int complement;
 };
 
 template <int R, bool GRAD, bool ROT>
@@ -50,7 +58,9 @@ struct StatsSmem {
   static constexpr int STAGES = GRAD ? 2 : 3;
   static constexpr int PIPE = STAGE * STAGES + (ROT ? X_BYTES : 0);
   static constexpr int RED = StatsCfg<R>::KS * R * ((GRAD ? 0 : R) + kChanBlock) * 4;
-  static constexpr int TOTAL = (PIPE > RED ? PIPE : RED) + 128;
+  static constexpr int CORE = GRAD ? 0 : (int)core_forward_smem_bytes(R);
+  static constexpr int BODY = PIPE > RED ? PIPE : RED;
+  static constexpr int TOTAL = (BODY > CORE ? BODY : CORE) + 128;
 };
 
 template <int R, bool GRAD, bool ROT, bool ALIGNED>
@@ -71,6 +81,13 @@ stats_kernel(const StatsParams p) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int wm = warp % MS, wk = warp / MS;
   const int chunk = blockIdx.x, sys = blockIdx.y, dblk = blockIdx.z;
+  if (!GRAD && chunk == p.chunks) {
+    // spare column of the grid: the per-head core runs beside the token reduction
+    if (dblk == 0 && sys < p.heads)
+      core_forward_device<R>(p.base_raw, p.eta_raw, sys, p.complement, p.eta, p.eta_slope, p.core_map,
+                             p.core_info, smem_gen, tid, NT);
+    return;
+  }
   const int b = sys / p.heads, h = sys - b * p.heads;
   const int d0 = dblk * kChanBlock;
   const int dvalid = min(kChanBlock, p.head_dim - d0);
@@ -336,8 +353,17 @@ static int launch_rank(const StatsParams& p, dim3 grid, bool rot, bool aligned, 
 }
 
 int launch_stats(const ms_shape& s, const Plan& plan, bool grad, const void* projected, const void* dy,
-                 const float* cos, const float* sin, float* partials, float* de_partials, cudaStream_t st) {
+                 const float* cos, const float* sin, float* partials, float* de_partials,
+                 const float* base_raw, const float* eta_raw, const ms_tape* core_tape, cudaStream_t st) {
   StatsParams p;
+  const bool fuse_core = !grad && core_tape != nullptr;
+  p.base_raw = base_raw;
+  p.eta_raw = eta_raw;
+  p.eta = fuse_core ? core_tape->eta : nullptr;
+  p.eta_slope = fuse_core ? core_tape->eta_slope : nullptr;
+  p.core_map = fuse_core ? core_tape->core_map : nullptr;
+  p.core_info = fuse_core ? core_tape->core_info : nullptr;
+  p.complement = s.complement;
   p.projected = static_cast<const __nv_bfloat16*>(projected);
   p.dy = static_cast<const __nv_bfloat16*>(dy);
   p.cos = cos;
@@ -349,7 +375,7 @@ int launch_stats(const ms_shape& s, const Plan& plan, bool grad, const void* pro
   p.rotary_rows = s.rotary_rows;
   p.chunks = plan.chunks; p.chunk_tokens = plan.chunk_tokens; p.dblocks = plan.dblocks;
   p.partial_floats = (int)(grad ? plan.bwd_partial_floats : plan.fwd_partial_floats);
-  dim3 grid(plan.chunks, plan.systems, plan.dblocks);
+  dim3 grid(plan.chunks + (fuse_core ? 1 : 0), plan.systems, plan.dblocks);
   const bool rot = s.rotary_rows > 0;
   switch (s.rank) {
     case 16: return grad ? launch_rank<16, true>(p, grid, rot, plan.aligned, st) : launch_rank<16, false>(p, grid, rot, plan.aligned, st);

@@ -11,7 +11,7 @@
 // words each) arrive through a cp.async pipeline in swizzled shared memory; each warp owns 16
 // token rows, products are mma.sync.m16n8k16 with FP32 accumulation, results are written back
 // into the tile in shared memory and leave with 16-byte coalesced stores.
-#include "ms_common.cuh"
+#include "ms_core.cuh"
 
 namespace ms {
 
@@ -29,6 +29,16 @@ struct TokenParams {
   const __nv_bfloat16* cross_grad;  // [systems][2][r][dpad]   backward only
   __nv_bfloat16* out;               // mixed [B,N,D] or dprojected [B,N,W]
   int batch, tokens, heads, head_dim, width, rotary_rows, dblocks, dpad;
+  // per-head core adjoint, computed by spare CTAs blockIdx.x >= tiles (backward only, optional)
+  const float* base_raw;
+  const float* hmat;
+  const float* de_sys;
+  const float* eta_slope;
+  const float* core_map;
+  float* d_base;
+  float* d_eta_raw;
+  float grad_scale;
+  int complement, tiles;
 };
 
 // rotary entries for the accumulator / row-operand fragment of one warp:
@@ -218,7 +228,8 @@ struct TokenBwdSmem {
   // A, C, dY, W hi/lo, dQ hi/lo, S hi/lo
   static constexpr int STAGE = A_BYTES + 2 * C_BYTES + 4 * W_BYTES + 2 * S_BYTES;
   static constexpr int STAGES = 2;
-  static constexpr int TOTAL = STAGE * STAGES + 128;
+  static constexpr int CORE = (int)core_backward_smem_bytes(R);
+  static constexpr int TOTAL = (STAGE * STAGES > CORE ? STAGE * STAGES : CORE) + 128;
 };
 
 // acc[n] += X * B^T for a 16 x 64 row operand held as fragments xf[4] and a matrix stored
@@ -273,6 +284,14 @@ token_backward_kernel(const TokenParams p) {
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int b = blockIdx.y;
+  if ((int)blockIdx.x >= p.tiles) {
+    // spare CTAs: parameter gradients of one head each, beside the token pass
+    if (b == 0)
+      core_backward_device(p.base_raw, p.hmat, p.de_sys, p.eta_slope, p.core_map, R, blockIdx.x - p.tiles,
+                           p.heads, p.batch, p.complement, p.grad_scale, p.d_base, p.d_eta_raw,
+                           smem_raw + (smem - smem_u32(smem_raw)), tid, kTokenThreads);
+    return;
+  }
   const int tk = blockIdx.x * kTileTokens;
   const int rows = min(kTileTokens, p.tokens - tk);
   const int d = p.head_dim, dmodel = p.heads * d, half = d >> 1;
@@ -467,7 +486,7 @@ template <class K>
 static int launch_token(K kern, int smem_bytes, const TokenParams& p, cudaStream_t st) {
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
     return MS_ERR_LAUNCH;
-  dim3 grid((p.tokens + kTileTokens - 1) / kTileTokens, p.batch);
+  dim3 grid(p.tiles + (p.d_eta_raw ? p.heads : 0), p.batch);
   kern<<<grid, kTokenThreads, smem_bytes, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
@@ -504,6 +523,9 @@ static TokenParams token_params(const ms_shape& s, const Plan& plan, const void*
   p.batch = s.batch; p.tokens = s.tokens; p.heads = s.heads; p.head_dim = s.head_dim;
   p.width = s.heads * (s.rank + s.head_dim);
   p.rotary_rows = s.rotary_rows; p.dblocks = plan.dblocks; p.dpad = plan.dpad;
+  p.base_raw = nullptr; p.hmat = nullptr; p.de_sys = nullptr; p.eta_slope = t.eta_slope; p.core_map = t.core_map;
+  p.d_base = nullptr; p.d_eta_raw = nullptr; p.grad_scale = 1.f; p.complement = s.complement;
+  p.tiles = (s.tokens + kTileTokens - 1) / kTileTokens;
   return p;
 }
 
@@ -522,8 +544,13 @@ int launch_readout(const ms_shape& s, const Plan& plan, const void* projected, c
 
 int launch_token_backward(const ms_shape& s, const Plan& plan, const void* projected, const void* dy,
                           const float* cos, const float* sin, const float* counts, const ms_tape& t,
-                          const void* gram_grad, const void* cross_grad, void* dprojected, cudaStream_t st) {
-  const TokenParams p = token_params(s, plan, projected, dy, cos, sin, counts, t, gram_grad, cross_grad, dprojected);
+                          const void* gram_grad, const void* cross_grad, void* dprojected,
+                          const CoreAdjoint* core, cudaStream_t st) {
+  TokenParams p = token_params(s, plan, projected, dy, cos, sin, counts, t, gram_grad, cross_grad, dprojected);
+  if (core) {
+    p.base_raw = core->base_raw; p.hmat = core->hmat; p.de_sys = core->de_sys;
+    p.d_base = core->d_base; p.d_eta_raw = core->d_eta_raw; p.grad_scale = core->grad_scale;
+  }
   const bool rot = s.rotary_rows > 0;
   switch (s.rank) {
     case 16: return launch_token_bwd_r<16>(p, rot, plan.aligned, st);
