@@ -326,13 +326,37 @@ def run_ours(args, cfg):
         sampler.start()
     for _ in range(max(args.warmup, 3)):
         step(x, dout)
-    total = timed(lambda: step(x, dout), args.steps)
+    # The reference's own benchmark times CUDA-graph replays of the step; do the same on one GPU
+    # (the step makes no host decisions, allocates through torch's graph pool and launches only
+    # on the current stream).  Eager timing is kept beside it.
+    graph = None
+    if world == 1 and not args.eager:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step(x, dout)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                graph_y = step(x, dout)
+            graph_dx = x.grad
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+        except Exception as error:  # noqa: BLE001 - report and fall back to eager timing
+            print(f"graph capture failed, timing eagerly: {error}", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+    eager_total = timed(lambda: step(x, dout), args.steps)
+    total = timed(graph.replay, args.steps) if graph is not None else eager_total
     # nvidia-smi samples every 100 ms and the timed region lasts milliseconds: keep the same step
     # running (untimed) for about a second so that the clock record covers this load
     t_end = time.perf_counter() + 1.2
     while time.perf_counter() < t_end:
         for _ in range(20):
-            step(x, dout)
+            graph.replay() if graph is not None else step(x, dout)
         torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
     if clocks is not None:
@@ -344,6 +368,15 @@ def run_ours(args, cfg):
     result = torch.zeros(1, dtype=torch.float32).pin_memory()
 
     def e2e_step():
+        if graph is not None:
+            # the captured step reads its inputs from the static device tensors x and dout
+            with torch.no_grad():
+                x.copy_(x_host, non_blocking=True)
+                dout.copy_(d_host, non_blocking=True)
+                graph.replay()
+                result.copy_((graph_y[0, :8].float().sum() + graph_dx[0, :8].float().sum()).reshape(1),
+                             non_blocking=True)
+            return
         with torch.no_grad():
             x_dev.copy_(x_host, non_blocking=True)
             d_dev.copy_(d_host, non_blocking=True)
@@ -380,7 +413,11 @@ def run_ours(args, cfg):
         "data": "synthetic", "config": workload_config(args, cfg, world), "clocks": clocks,
         "e2e": {"value": global_tokens / (e2e_total / args.steps), "unit": "tokens/s",
                 "h2d_bytes_per_step": (x_host.numel() + d_host.numel()) * 2 * world, "d2h_bytes_per_step": 4 * world},
-        "gpu_launches": 8 * args.steps,
+        # own kernels per step: statistics (+ per-head core), compact, readout, and their three adjoints;
+        # the sequence-parallel path adds a pack kernel and a separate per-head core kernel per direction
+        "gpu_launches": (6 if world == 1 else 10) * args.steps,
+        "timing": "cuda_graph_replay" if graph is not None else "eager",
+        "eager_ms_per_step": eager_total / args.steps * 1e3,
         "roofline": {
             "bound": "hbm", "kernel": name, "achieved": achieved, "peak": hbm, "unit": "GB/s",
             "frac": achieved / hbm, "traffic": None, "peak_source": f"of {which}",
@@ -411,6 +448,7 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", choices=tuple(CONFIGS), default="c3")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
     ap.add_argument("--kernels-only", action="store_true",
                     help="launch each mixer kernel alone (--reps times) and print their timings; used for ncu")
     ap.add_argument("--reps", type=int, default=10)

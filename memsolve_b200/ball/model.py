@@ -33,6 +33,7 @@ class MemSolve(nn.Module):
         super().__init__()
         self.config = config
         self._recompute_readout: Literal["auto"] | bool = _validate_recompute_readout(config.recompute_readout)
+        self._rotary_cache: dict = {}
         # creation order fixes the RNG stream and therefore the default weights (model.py:50-71)
         self.w_bc = nn.Linear(config.dim, config.num_heads * config.rank + config.dim, bias=config.bias)
         self.w_o = nn.Linear(config.dim, config.dim, bias=config.bias)
@@ -148,9 +149,10 @@ class MemSolve(nn.Module):
                 raise ValueError("position_ids and rotary_context_length require rotary=True")
             return None, None
         batch, length, _ = x.shape
-        if position_ids is None:
+        default_positions = position_ids is None
+        offset = 0
+        if default_positions:
             offset = 0 if sequence_parallel is None else sequence_parallel.offset
-            position_ids = torch.arange(offset, offset + length, device=x.device)[None]
         else:
             if not isinstance(position_ids, torch.Tensor) or position_ids.dtype not in _INTEGER_DTYPES:
                 raise TypeError("position_ids must be an integer tensor")
@@ -182,11 +184,26 @@ class MemSolve(nn.Module):
             raise TypeError("rotary_context_length must be an integer or integer tensor [B]")
         elif context_length <= 0:
             raise ValueError("rotary_context_length must be positive")
-        return rotary_position_factors(
+        # default positions with an integer context give the same table on every call: keep the
+        # most recent ones instead of rebuilding them with a dozen small launches per forward
+        key = None
+        if default_positions and isinstance(context_length, int) and x.dtype != torch.float64:
+            key = (x.device, length, offset, context_length)
+            cached = self._rotary_cache.get(key)
+            if cached is not None:
+                return cached
+        if default_positions:
+            position_ids = torch.arange(offset, offset + length, device=x.device)[None]
+        tables = rotary_position_factors(
             position_ids, head_dim=config.head_dim, base=config.rotary_base,
             train_length=config.rotary_train_length, context_length=context_length,
             scaling=config.rotary_scaling, dtype=x.dtype,
         )
+        if key is not None and not torch.cuda.is_current_stream_capturing():
+            if len(self._rotary_cache) >= 8:
+                self._rotary_cache.pop(next(iter(self._rotary_cache)))
+            self._rotary_cache[key] = tables
+        return tables
 
     # ---- CUDA forward (model.py:185-356) -----------------------------------------------
     def _forward_cuda(self, x, valid_mask, *, sequence_parallel=None, valid_counts=None, position_ids=None,

@@ -2,6 +2,8 @@
 // argument checking, launch planning and the order of kernel launches.  No allocation, no
 // host synchronisation; every launch goes to the caller's stream.
 #include <atomic>
+#include <mutex>
+#include <vector>
 
 #include "ms_common.cuh"
 
@@ -39,6 +41,23 @@ int sm_count() {
   }
   g_sm_count[dev].store(v, std::memory_order_relaxed);
   return v;
+}
+
+int ensure_dynamic_smem(const void* kernel, int bytes) {
+  struct Entry { const void* kernel; int device; int bytes; };
+  static std::mutex mu;
+  static std::vector<Entry> done;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return MS_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(mu);
+  for (const Entry& e : done)
+    if (e.kernel == kernel && e.device == dev && e.bytes >= bytes) return MS_OK;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return MS_ERR_LAUNCH;
+  }
+  done.push_back({kernel, dev, bytes});
+  return MS_OK;
 }
 
 static int device_status() {

@@ -45,6 +45,9 @@ struct CoreAdjoint {
 Plan make_plan(const ms_shape& s);
 int check_shape(const ms_shape* s);
 int sm_count();
+// Raise a kernel's dynamic shared-memory limit once per (kernel, device); later calls are a
+// table lookup, so no function attribute is touched while a stream is being captured.
+int ensure_dynamic_smem(const void* kernel, int bytes);
 
 // ---------------------------------------------------------------------------------------
 // shared-memory addressing

@@ -438,8 +438,7 @@ core_backward_kernel(const float* __restrict__ base_raw, const float* __restrict
 template <class K>
 static int set_smem(K kern, size_t bytes) {
   if (bytes > 48 * 1024) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
-      return MS_ERR_LAUNCH;
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)bytes) != MS_OK) return MS_ERR_LAUNCH;
   }
   return MS_OK;
 }

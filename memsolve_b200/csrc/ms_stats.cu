@@ -340,8 +340,7 @@ template <int R, bool GRAD, bool ROT, bool ALIGNED>
 static int launch_one(const StatsParams& p, dim3 grid, cudaStream_t st) {
   using Sm = StatsSmem<R, GRAD, ROT>;
   auto kern = stats_kernel<R, GRAD, ROT, ALIGNED>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Sm::TOTAL) != cudaSuccess)
-    return MS_ERR_LAUNCH;
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Sm::TOTAL) != MS_OK) return MS_ERR_LAUNCH;
   kern<<<grid, StatsCfg<R>::MS * StatsCfg<R>::KS * 32, Sm::TOTAL, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }

@@ -484,8 +484,7 @@ token_backward_kernel(const TokenParams p) {
 // ---------------------------------------------------------------------------------------
 template <class K>
 static int launch_token(K kern, int smem_bytes, const TokenParams& p, cudaStream_t st) {
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
-    return MS_ERR_LAUNCH;
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes) != MS_OK) return MS_ERR_LAUNCH;
   dim3 grid(p.tiles + (p.d_eta_raw ? p.heads : 0), p.batch);
   kern<<<grid, kTokenThreads, smem_bytes, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
