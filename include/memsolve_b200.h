@@ -98,6 +98,12 @@ const char* ms_status_string(int status);
 /* Row pitch, in elements, of the split coefficient tensors: d rounded up to a multiple of 8. */
 int ms_padded_head_dim(int head_dim);
 
+/* Diagnostic (synchronises the device): reads and clears the library's device-side error word of
+ * the current device.  0 = no error; 0x100 = a kernel gave up waiting on a shared-memory barrier
+ * (its bounded wait ran out) and returned early, so the last results are incomplete; -1 = the
+ * word could not be read.  No counterpart in the reference, whose kernels have no such waits. */
+int ms_device_error(void);
+
 /* Bytes of scratch the stats/compact calls need for this shape (partials of the token
  * reduction and backward intermediates).  Same workspace serves forward and backward. */
 size_t ms_workspace_bytes(const ms_shape* shape);

@@ -2,10 +2,11 @@
 // argument checking, launch planning and the order of kernel launches.  No allocation, no
 // host synchronisation; every launch goes to the caller's stream.
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
-#include "ms_common.cuh"
+#include "ms_tma.cuh"
 
 namespace ms {
 
@@ -60,6 +61,59 @@ int ensure_dynamic_smem(const void* kernel, int bytes) {
   return MS_OK;
 }
 
+// ---- TMA tensor maps (driver entry point resolved at run time; libcuda is not linked) ----------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static std::atomic<void*> cached{nullptr};
+  void* fn = cached.load(std::memory_order_acquire);
+  if (fn) return reinterpret_cast<EncodeTiledFn>(fn);
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess || !fn) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  cached.store(fn, std::memory_order_release);
+  return reinterpret_cast<EncodeTiledFn>(fn);
+}
+
+int encode_tensor_map(CUtensorMap* out, void* base, int elem_bytes, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box, Swizzle swizzle) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return MS_ERR_LAUNCH;
+  cuuint64_t gdim[3], gstr[2];
+  cuuint32_t bx[3], es[3];
+  for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+  for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+  const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_NONE;
+  if (swizzle == Swizzle::B32) sw = CU_TENSOR_MAP_SWIZZLE_32B;
+  if (swizzle == Swizzle::B64) sw = CU_TENSOR_MAP_SWIZZLE_64B;
+  if (swizzle == Swizzle::B128) sw = CU_TENSOR_MAP_SWIZZLE_128B;
+  const CUresult r = fn(out, dt, (cuuint32_t)rank, base, gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MS_OK : MS_ERR_LAUNCH;
+}
+
+__device__ int g_error_word = 0;
+
+int* device_error_word() {
+  static std::atomic<int*> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  int* p = cached[dev].load(std::memory_order_acquire);
+  if (p) return p;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_error_word) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  cached[dev].store(p, std::memory_order_release);
+  return p;
+}
+
 static int device_status() {
   static std::atomic<int> cached[64];
   int dev = 0;
@@ -101,6 +155,11 @@ Plan make_plan(const ms_shape& s) {
   p.chunk_tokens = tiles_per_chunk * kTileTokens;
   p.chunks = (s.tokens + p.chunk_tokens - 1) / p.chunk_tokens;
   p.aligned = (s.head_dim % 8) == 0;
+  static const bool no_tma = [] {
+    const char* v = std::getenv("MEMSOLVE_NO_TMA");
+    return v && v[0] == '1';
+  }();
+  p.tma = !no_tma;
   p.fwd_partial_floats = (size_t)s.rank * s.rank + (size_t)s.rank * s.head_dim;
   p.bwd_partial_floats = (size_t)s.rank * s.head_dim;
   p.ws_partials = round64((size_t)p.systems * p.chunks * p.fwd_partial_floats);
@@ -162,6 +221,15 @@ const char* ms_status_string(int status) {
 }
 
 int ms_padded_head_dim(int head_dim) { return (head_dim + 7) & ~7; }
+
+int ms_device_error(void) {
+  int* word = device_error_word();
+  if (!word) return -1;
+  int value = 0;
+  if (cudaMemcpy(&value, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (value != 0) cudaMemset(word, 0, sizeof(int));
+  return value;
+}
 
 size_t ms_workspace_bytes(const ms_shape* shape) {
   if (check_shape(shape) != MS_OK) return 0;

@@ -23,6 +23,7 @@ struct Plan {
   int chunks;        // token chunks per system in the reductions
   int chunk_tokens;  // tokens per chunk (multiple of 64)
   bool aligned;      // 16-byte vector path usable for projected / dy / tables
+  bool tma;          // TMA kernels allowed (off when the environment sets MEMSOLVE_NO_TMA=1)
   size_t fwd_partial_floats;  // per (system, chunk): r*r + r*d
   size_t bwd_partial_floats;  // per (system, chunk): r*d
   size_t ws_partials;         // floats

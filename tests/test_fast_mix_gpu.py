@@ -278,6 +278,17 @@ def test_full_size_config3(cuda_mod):
     _assert_case(cuda_mod, proj, base, eta_raw, None, cos, sin, dy, gproj=5e-3, tag="config3")
 
 
+@pytest.mark.parametrize("batch,length,heads,rank,head_dim,rot", [
+    (1, 16 * 37 + 5, 12, 32, 64, True), (3, 197, 6, 32, 64, False), (2, 1000, 3, 64, 128, True),
+    (1, 50, 2, 16, 64, True), (2, 4100, 16, 32, 64, True)])
+def test_tma_kernel_shapes(cuda_mod, batch, length, heads, rank, head_dim, rot):
+    """Shapes that take the TMA kernels (head_dim % 64 == 0, rank 16/32/64): ragged last slice,
+    several samples, head groups that do not fit shared memory at once, two channel blocks."""
+    case = _random_case(4000 + length, batch, length, heads, rank, head_dim, rot=rot, batched_table=rot and batch > 1)
+    _assert_case(cuda_mod, *case, gproj=5e-3 if rot else 3e-2, tag=f"tma B{batch} N{length} H{heads} r{rank} d{head_dim}")
+    assert cuda_mod._LIB.ms_device_error() == 0
+
+
 def test_rejects_bad_inputs(cuda_mod):
     proj, base, eta_raw, counts, cos, sin, dy = _random_case(1, 1, 40, 2, 16, 8)
     with pytest.raises(RuntimeError, match="mixed precision CUDA contract"):
