@@ -8,6 +8,20 @@
 
 #include "../../include/memsolve_b200.h"
 
+// Phase time stamps for development builds (-DMS_PROFILE_TICKS); compiled out of the library.
+#ifdef MS_PROFILE_TICKS
+static __device__ long long g_ms_ticks[64];
+#define MS_TICK(i)                                                                   \
+  do {                                                                               \
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)   \
+      g_ms_ticks[i] = clock64();                                                     \
+  } while (0)
+#else
+#define MS_TICK(i) \
+  do {             \
+  } while (0)
+#endif
+
 namespace ms {
 
 constexpr int kTileTokens = 64;   // token rows per shared-memory tile

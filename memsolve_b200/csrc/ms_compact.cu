@@ -170,6 +170,7 @@ compact_forward_kernel(const CompactFwdParams p) {
   const float* src = p.partials + (size_t)sys * nch * p.pf;
   const float eta = p.eta[h];
   const int d = p.head_dim;
+  MS_TICK(0);
 
   {
     constexpr int PER = (R * R + kCompactThreads - 1) / kCompactThreads;
@@ -196,8 +197,10 @@ compact_forward_kernel(const CompactFwdParams p) {
     }
   }
   __syncthreads();
+  MS_TICK(1);
   cholesky_inverse_rows<R>(gs, ts, rowbuf, tid);
   __syncthreads();
+  MS_TICK(2);
   for (int i = tid; i < R * R; i += kCompactThreads) {
     const int row = i / R, col = i - row * R;
     p.inverse[(size_t)sys * R * R + i] = ts[row * (R + 1) + col];
@@ -225,10 +228,12 @@ compact_forward_kernel(const CompactFwdParams p) {
       }
     }
     __syncthreads();
+    MS_TICK(3);
     // Z = T Q   (T lower triangular)
     small_mm<R>([&](int i, int j) { return ts[i * (R + 1) + j]; }, [](int) { return 0; },
                 [](int i) { return i + 1; }, qs, mid, tid);
     __syncthreads();
+    MS_TICK(4);
     for (int i = tid; i < R * 64; i += kCompactThreads) {
       const int row = i >> 6, c = i & 63;
       if (c < dv) p.state[((size_t)sys * R + row) * d + d0 + c] = mid[row * 65 + c];
@@ -241,6 +246,7 @@ compact_forward_kernel(const CompactFwdParams p) {
     small_mm<R>([&](int i, int j) { return ts[j * (R + 1) + i]; }, [](int i) { return i; },
                 [](int) { return R; }, qs, mid, tid);
     __syncthreads();
+    MS_TICK(5);
     __nv_bfloat16* hi = p.coeff + (size_t)sys * 2 * R * p.dpad;
     __nv_bfloat16* lo = hi + (size_t)R * p.dpad;
     const int cend = min(64, p.dpad - d0);
@@ -249,6 +255,7 @@ compact_forward_kernel(const CompactFwdParams p) {
       if (c < cend) store_split(hi, lo, (size_t)row * p.dpad + d0 + c, c < dv ? mid[row * 65 + c] : 0.f);
     }
     __syncthreads();
+    MS_TICK(6);
   }
 }
 

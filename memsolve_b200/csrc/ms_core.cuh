@@ -163,14 +163,17 @@ __device__ __forceinline__ void core_forward_device(const float* __restrict__ ba
   sh.cand_v = sh.rowbuf + 2 * R;
   sh.cand_i = reinterpret_cast<int*>(sh.cand_v + 2);
   sh.piv = sh.cand_i + 2;
+  MS_TICK(20);
   build_generator(base_raw + (size_t)h * R * R, R, lc, jm, tid, nthreads);
   for (int i = tid; i < R * R; i += nthreads) {
     const int row = i / R, col = i - row * R;
     if (row == col) jm[row * P + col] += 1.0;   // I + J
   }
   __syncthreads();
+  MS_TICK(21);
   const int info = gj_inverse<R>(jm, lc, sh, tid);   // lc <- (I+J)^-1
   __syncthreads();
+  MS_TICK(22);
   for (int i = tid; i < R * R; i += nthreads) {
     const int row = i / R, col = i - row * R;
     core_map[(size_t)h * R * R + i] = (float)(2.0 * lc[row * P + col] - (row == col ? 1.0 : 0.0));
