@@ -47,8 +47,13 @@ typedef enum ms_status {
   MS_ERR_WORKSPACE = 3,        /* workspace pointer null or smaller than ms_workspace_bytes()   */
   MS_ERR_LAUNCH = 4,           /* a kernel launch reported a CUDA error                         */
   MS_ERR_DEVICE = 5,           /* current device is not sm_100-class                            */
-  MS_ERR_ODD_HEAD_DIM = 6      /* rotary tables given with an odd head dimension                */
+  MS_ERR_ODD_HEAD_DIM = 6,     /* rotary tables given with an odd head dimension                */
+  MS_ERR_STATIC_SCRATCH = 7    /* shape too large for the built-in scratch of ms_stats_forward_static */
 } ms_status;
+
+/* Capacity, in floats, of the scratch buffer compiled into the library for
+ * ms_stats_forward_static (16 MiB per GPU that loads the library, held until process exit). */
+#define MS_STATIC_SCRATCH_FLOATS (4 * 1024 * 1024)
 
 /* Problem shape shared by every call. */
 typedef struct ms_shape {
@@ -129,6 +134,35 @@ int ms_core_forward(const ms_shape* shape, const float* base_raw, const float* e
 int ms_stats_forward(const ms_shape* shape, const void* projected, const float* cos,
                      const float* sin, const float* counts, void* workspace,
                      size_t workspace_bytes, float* packed, void* stream);
+
+/*
+ * ms_stats_forward for callers that have no way to hand over scratch memory.  (This entry point has
+ * no counterpart in the reference, whose Python layer always allocates its partial buffers itself.)
+ *
+ * Who needs it: code that drives the kernels from a place where device allocation is off the
+ * table -- a plugin running inside a host application that owns the allocator and hands out only
+ * the input and output buffers, a real-time or signal-handler-like context where cudaMalloc's
+ * implicit synchronisation is not acceptable, or a caller replaying fixed buffers that cannot grow
+ * a workspace after start-up.  Such a caller still passes `projected`, the tables, `counts` and the
+ * output `packed`; the per-chunk partial sums go to a buffer that is part of the library image
+ * (MS_STATIC_SCRATCH_FLOATS floats, 16 MiB on every GPU that loads the library, for the life of the
+ * process).  The call performs no cudaMalloc/cudaFree and calls no allocating library routine.
+ *
+ * Result: packed[B*H][r*r + r*d] exactly as ms_stats_forward writes it with a non-null `packed`
+ * (same kernels, same summation order, so bit-identical).  `packed` must not be null.
+ *
+ * Limits and rules:
+ *  - shapes whose partial sums exceed the built-in buffer return MS_ERR_STATIC_SCRATCH and launch
+ *    nothing (BASELINE configuration 3 needs 3.7 MB, configuration 5 per GPU 9.8 MB);
+ *  - the first call on each device looks up the buffer's device address (cudaGetSymbolAddress, with
+ *    that device current) and keeps it; make that first call before starting any stream capture;
+ *  - all calls on a device share the one buffer: two calls whose kernels can overlap on the GPU
+ *    (different streams, or graphs launched concurrently) race on it -- serialise them.  The buffer
+ *    keeps the previous call's partial sums, which is harmless because every partial the new grid
+ *    reads is first written in full by that grid.
+ */
+int ms_stats_forward_static(const ms_shape* shape, const void* projected, const float* cos,
+                            const float* sin, const float* counts, float* packed, void* stream);
 
 /*
  * Per (b,h): T, Z, W from the statistics.  `packed` null: read the partials left in

@@ -62,6 +62,7 @@ _SIGNATURES = {
     "ms_packed_stats_floats": (ctypes.c_size_t, [ctypes.POINTER(_Shape), ctypes.c_int]),
     "ms_core_forward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, ctypes.POINTER(_Tape), _P]),
     "ms_stats_forward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, ctypes.c_size_t, _P, _P]),
+    "ms_stats_forward_static": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, _P]),
     "ms_compact_forward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, ctypes.c_size_t, _P,
                                           ctypes.POINTER(_Tape), _P]),
     "ms_readout": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, ctypes.POINTER(_Tape), _P, _P]),

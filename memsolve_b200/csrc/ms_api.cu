@@ -216,6 +216,9 @@ const char* ms_status_string(int status) {
     case MS_ERR_LAUNCH: return "a CUDA kernel launch failed";
     case MS_ERR_DEVICE: return "the current CUDA device is not an sm_100-class GPU";
     case MS_ERR_ODD_HEAD_DIM: return "rotary content requires an even head dimension";
+    case MS_ERR_STATIC_SCRATCH:
+      return "this shape needs more scratch than the built-in static buffer of ms_stats_forward_static holds "
+             "(MS_STATIC_SCRATCH_FLOATS); use ms_stats_forward with a caller-provided workspace";
   }
   return "unknown status";
 }
@@ -267,6 +270,46 @@ int ms_stats_forward(const ms_shape* shape, const void* projected, const float* 
                       nullptr, st));
   if (packed) MS_TRY(launch_pack_stats(*shape, plan, false, w.partials, nullptr, counts, packed, st));
   return MS_OK;
+}
+
+// Scratch of ms_stats_forward_static: lives in the library image, one copy per GPU that loads it.
+static __device__ __align__(256) float g_static_scratch[MS_STATIC_SCRATCH_FLOATS];
+
+// Device address of g_static_scratch on the current device.  In host code the symbol's name is
+// only a handle, so the address is asked for once per device (with that device current) and kept.
+static float* static_scratch_address() {
+  static std::atomic<float*> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  float* p = cached[dev].load(std::memory_order_acquire);
+  if (p) return p;
+  void* addr = nullptr;
+  if (cudaGetSymbolAddress(&addr, g_static_scratch) != cudaSuccess || !addr) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  p = static_cast<float*>(addr);
+  cached[dev].store(p, std::memory_order_release);
+  return p;
+}
+
+int ms_stats_forward_static(const ms_shape* shape, const void* projected, const float* cos, const float* sin,
+                            const float* counts, float* packed, void* stream) {
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  if (!projected || !packed) return MS_ERR_INVALID_ARGUMENT;
+  if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
+  Plan plan = make_plan(*shape);
+  if (plan.ws_partials > (size_t)MS_STATIC_SCRATCH_FLOATS) return MS_ERR_STATIC_SCRATCH;
+  float* scratch = static_scratch_address();
+  if (!scratch) return MS_ERR_LAUNCH;
+  plan.aligned = plan.aligned && is16(projected) && (!shape->rotary_rows || (is16(cos) && is16(sin)));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // every partial of the launched grid is written in full before it is read, so nothing in the
+  // shared scratch needs clearing between calls
+  MS_TRY(launch_stats(*shape, plan, false, projected, nullptr, cos, sin, scratch, nullptr, nullptr, nullptr,
+                      nullptr, st));
+  return launch_pack_stats(*shape, plan, false, scratch, nullptr, counts, packed, st);
 }
 
 int ms_compact_forward(const ms_shape* shape, const float* counts, const void* workspace, size_t workspace_bytes,
