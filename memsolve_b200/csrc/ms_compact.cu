@@ -26,15 +26,18 @@ constexpr int kCompactThreads = 256;
 // FP32, pitch R+1) to ts.  Executed by the first ceil(R/32) warps.  Gaussian elimination
 // applies the unit-lower factor to the identity in place; a final row scaling by the inverse
 // square roots of the pivots turns it into the Cholesky inverse.
+// One elimination step per template instance, so that every register index is a constant.
+// The bulk is FP32; each row's diagonal entry (its future pivot) is carried in FP64, as the
+// reference's native Cholesky does.
 template <int R, int K>
-__device__ __forceinline__ void cholesky_eliminate(double (&a)[R], double* rowbuf, int i, bool live) {
-  // one elimination step per template instance so that every register index is a constant
+__device__ __forceinline__ void cholesky_eliminate(float (&a)[R], double& diag, float* rowbuf, int i, bool live) {
   if constexpr (K < R) {
     constexpr int NW = (R + 31) / 32;
-    double* rb = rowbuf + (K & 1) * R;
+    float* rb = rowbuf + (K & 1) * R;
     if (i == K) {
-      const double inv = 1.0 / a[K];
-      rb[K] = inv;
+      const float inv0 = __frcp_rn((float)diag);
+      const double inv = (double)inv0 * fma(-diag, (double)inv0, 2.0);   // one Newton step in FP64
+      rb[K] = (float)inv;
 #pragma unroll
       for (int j = K + 1; j < R; ++j) rb[j] = a[j];
 #pragma unroll
@@ -43,41 +46,35 @@ __device__ __forceinline__ void cholesky_eliminate(double (&a)[R], double* rowbu
     if (NW == 1) __syncwarp();
     else asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32));
     if (live && i > K) {
-      const double f = a[K] * rb[K];
+      const float f = a[K] * rb[K];
+      diag = fma(-(double)f, (double)rb[i], diag);
 #pragma unroll
       for (int j = 0; j < R; ++j) {
-        if (j != K) a[j] = fma(-f, rb[j], a[j]);
+        if (j != K) a[j] = fmaf(-f, rb[j], a[j]);
       }
       a[K] = -f;
     }
-    cholesky_eliminate<R, K + 1>(a, rowbuf, i, live);
+    cholesky_eliminate<R, K + 1>(a, diag, rowbuf, i, live);
   }
 }
 
 template <int R>
-__device__ __noinline__ void cholesky_inverse_rows(const float* gs, float* ts, double* rowbuf, int tid) {
+__device__ __noinline__ void cholesky_inverse_rows(const float* gs, float* ts, float* rowbuf, int tid) {
   constexpr int NW = (R + 31) / 32;
   if (tid >= NW * 32) return;
   const int i = tid;
   const bool live = i < R;
-  double a[R];
+  float a[R];
 #pragma unroll
-  for (int j = 0; j < R; ++j) {
-    double v = 0.0;
-    if (live) v = 0.5 * ((double)gs[i * R + j] + (double)gs[j * R + i]) + (i == j ? 1.0 : 0.0);
-    a[j] = v;
-  }
-  cholesky_eliminate<R, 0>(a, rowbuf, i, live);
+  for (int j = 0; j < R; ++j) a[j] = live ? 0.5f * (gs[i * R + j] + gs[j * R + i]) + (i == j ? 1.0f : 0.0f) : 0.f;
+  double diag = live ? 1.0 + (double)gs[i * R + i] : 1.0;
+  cholesky_eliminate<R, 0>(a, diag, rowbuf, i, live);
   if (live) {
-    // pivot of row i sits at a[i]; select it without a dynamic register index
-    double piv = 1.0;
-#pragma unroll
-    for (int j = 0; j < R; ++j) piv = (j == i) ? a[j] : piv;
-    const double sc = 1.0 / sqrt(piv);
+    const double sc = rsqrt(diag);
 #pragma unroll
     for (int j = 0; j < R; ++j) {
       float v = 0.f;
-      if (j < i) v = (float)(a[j] * sc);
+      if (j < i) v = (float)((double)a[j] * sc);
       else if (j == i) v = (float)sc;
       ts[i * (R + 1) + j] = v;
     }
@@ -89,15 +86,24 @@ __device__ __noinline__ void cholesky_inverse_rows(const float* gs, float* ts, d
 // ---------------------------------------------------------------------------------------
 // out[i][c] = sum_j lhs(i,j) * rhs[j][c] for i < R, c < 64 (rhs/out pitch 65); jlo/jhi bound
 // the inner index (triangular factors).
+// Each thread owns one column and R/4 interleaved rows: one load of the right-hand side feeds R/4
+// independent FMA chains.  Triangular left factors hold explicit zeros, so the inner index runs
+// over the full range (the bounds jlo/jhi are accepted for documentation only).
 template <int R, class LHS, class LO, class HI>
-__device__ __forceinline__ void small_mm(LHS lhs, LO jlo, HI jhi, const float* rhs, float* out, int tid) {
-  const int c = tid & 63;
-  for (int i = tid >> 6; i < R; i += kCompactThreads / 64) {
-    float acc = 0.f;
-    const int j1 = jhi(i);
-    for (int j = jlo(i); j < j1; ++j) acc = fmaf(lhs(i, j), rhs[j * 65 + c], acc);
-    out[i * 65 + c] = acc;
+__device__ __forceinline__ void small_mm(LHS lhs, LO, HI, const float* rhs, float* out, int tid) {
+  constexpr int ROWS = R / (kCompactThreads / 64);
+  const int c = tid & 63, rg = tid >> 6;
+  float acc[ROWS];
+#pragma unroll
+  for (int k = 0; k < ROWS; ++k) acc[k] = 0.f;
+#pragma unroll 4
+  for (int j = 0; j < R; ++j) {
+    const float r = rhs[j * 65 + c];
+#pragma unroll
+    for (int k = 0; k < ROWS; ++k) acc[k] = fmaf(lhs(rg + (kCompactThreads / 64) * k, j), r, acc[k]);
   }
+#pragma unroll
+  for (int k = 0; k < ROWS; ++k) out[(rg + (kCompactThreads / 64) * k) * 65 + c] = acc[k];
 }
 
 // acc[e] = sum over chunks (in chunk order) of src[c*stride + off[e]] for PER entries of this
@@ -125,6 +131,31 @@ __device__ __forceinline__ void sum_partials(const float* __restrict__ src, size
     for (int e = 0; e < PER; ++e) v[e] = ok[e] ? __ldg(src + (size_t)c * stride + off[e]) : 0.f;
 #pragma unroll
     for (int e = 0; e < PER; ++e) acc[e] += v[e];
+  }
+}
+
+// Sum, in chunk order, one R x 64 block of a partial r x d matrix (first element at `base`,
+// row pitch d, columns [d0, d0+dv)) with NT cooperating threads (t = 0..NT-1) and write it,
+// scaled, to dst (pitch 65; columns >= dv become zero).
+template <int R, int NT>
+__device__ __forceinline__ void sum_block(const float* __restrict__ src, size_t stride, int nch, size_t base, int d,
+                                          int d0, int dv, float scale, float* dst, int t) {
+  constexpr int PER = (R * 64 + NT - 1) / NT;
+  size_t off[PER];
+  bool ok[PER];
+  float acc[PER];
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int i = t + e * NT;
+    const int row = i >> 6, c = i & 63;
+    ok[e] = i < R * 64 && c < dv;
+    off[e] = ok[e] ? base + (size_t)row * d + d0 + c : 0;
+  }
+  sum_partials<PER>(src, stride, nch, off, ok, acc);
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int i = t + e * NT;
+    if (i < R * 64) dst[(i >> 6) * 65 + (i & 63)] = acc[e] * scale;
   }
 }
 
@@ -157,7 +188,7 @@ compact_forward_kernel(const CompactFwdParams p) {
   float* ms_ = ts + R * (R + 1);        // R*(R+1)        F - eta I
   float* qs = ms_ + R * (R + 1);        // R*65           Q block -> scratch
   float* mid = qs + R * 65;             // R*65
-  double* rowbuf = reinterpret_cast<double*>(mid + R * 65);  // 2*R doubles
+  float* rowbuf = mid + R * 65;         // 2*R floats (pivot-row broadcast, double buffered)
 
   const int tid = threadIdx.x;
   const int sys = blockIdx.x;
@@ -198,7 +229,15 @@ compact_forward_kernel(const CompactFwdParams p) {
   }
   __syncthreads();
   MS_TICK(1);
-  cholesky_inverse_rows<R>(gs, ts, rowbuf, tid);
+  // the factorisation occupies the first warp(s); the other warps meanwhile sum the partial
+  // moments of the first channel block
+  constexpr int CHOL_THREADS = ((R + 31) / 32) * 32;
+  if (tid < CHOL_THREADS) {
+    cholesky_inverse_rows<R>(gs, ts, rowbuf, tid);
+  } else {
+    sum_block<R, kCompactThreads - CHOL_THREADS>(src, p.pf, nch, (size_t)R * R, d, 0, min(64, d), inv_s, qs,
+                                                  tid - CHOL_THREADS);
+  }
   __syncthreads();
   MS_TICK(2);
   for (int i = tid; i < R * R; i += kCompactThreads) {
@@ -208,26 +247,10 @@ compact_forward_kernel(const CompactFwdParams p) {
 
   for (int jb = 0; jb < p.dblocks; ++jb) {
     const int d0 = jb * 64, dv = min(64, d - d0);
-    {
-      constexpr int PER = R * 64 / kCompactThreads;
-      size_t off[PER];
-      bool ok[PER];
-      float acc[PER];
-#pragma unroll
-      for (int e = 0; e < PER; ++e) {
-        const int i = tid + e * kCompactThreads;
-        const int row = i >> 6, c = i & 63;
-        ok[e] = c < dv;
-        off[e] = (size_t)R * R + (size_t)row * d + d0 + (ok[e] ? c : 0);
-      }
-      sum_partials<PER>(src, p.pf, nch, off, ok, acc);
-#pragma unroll
-      for (int e = 0; e < PER; ++e) {
-        const int i = tid + e * kCompactThreads;
-        qs[(i >> 6) * 65 + (i & 63)] = acc[e] * inv_s;
-      }
+    if (jb > 0) {
+      sum_block<R, kCompactThreads>(src, p.pf, nch, (size_t)R * R, d, d0, dv, inv_s, qs, tid);
+      __syncthreads();
     }
-    __syncthreads();
     MS_TICK(3);
     // Z = T Q   (T lower triangular)
     small_mm<R>([&](int i, int j) { return ts[i * (R + 1) + j]; }, [](int) { return 0; },

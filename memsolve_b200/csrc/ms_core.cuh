@@ -10,16 +10,22 @@
 //
 // Replaces the reference's `complement`, `core_forward`, `compact_lu`, `compact_getrs`,
 // `eta_trace` and `core_backward` (memsolve/ball/cuda.py:2281-2360, 2517-2527;
-// csrc/ball/solvers.cuh:227-560).  The inverse is a Gauss-Jordan elimination with partial
-// pivoting in FP64, one matrix row per lane held in registers; rows are never moved between
-// lanes, the pivot order is recorded instead.
+// csrc/ball/solvers.cuh:227-560).  The inverse of I+J is a Gauss-Jordan elimination with partial
+// pivoting in FP32, one matrix row per lane held in registers (rows are never moved between
+// lanes, the pivot order is recorded instead), polished by two Newton-Schulz steps
+// X <- X + X (I - A X) in FP64 carried out by the whole CTA; the generator J itself is FP64.
 #pragma once
 
 #include "ms_common.cuh"
 
 namespace ms {
 
-constexpr double kSoftplusShift = 0.54132485461291810;  // log(expm1(1))
+constexpr float kSoftplusShiftF = 0.5413248546129181f;  // log(expm1(1))
+
+__device__ __forceinline__ double softplus_shifted(float u) {
+  const float x = u + kSoftplusShiftF;
+  return (double)(x > 20.f ? x : log1pf(expf(x)));
+}
 
 // L -> lc, J -> jm (FP64, pitch r+1).  All threads of the CTA take part.
 __device__ __forceinline__ void build_generator(const float* __restrict__ base, int r, double* lc, double* jm,
@@ -28,12 +34,8 @@ __device__ __forceinline__ void build_generator(const float* __restrict__ base, 
   for (int i = tid; i < r * r; i += nthreads) {
     const int row = i / r, col = i - row * r;
     double v = 0.0;
-    if (row > col) {
-      v = (double)base[i];
-    } else if (row == col) {
-      const double x = (double)base[i] + kSoftplusShift;
-      v = x > 30.0 ? x : log1p(exp(x));
-    }
+    if (row > col) v = (double)base[i];
+    else if (row == col) v = softplus_shifted(base[i]);
     lc[row * p + col] = v;
   }
   __syncthreads();
@@ -50,30 +52,33 @@ __device__ __forceinline__ void build_generator(const float* __restrict__ base, 
 }
 
 __device__ __forceinline__ void eta_maps(float raw, float& eta, float& slope) {
-  const double scale = 1.0 - 1.1920928955078125e-7;  // 1 - FP32 epsilon
-  const double x = (double)raw;
-  eta = (float)(scale * tanh(x));
-  const double q = exp(-2.0 * fabs(x));
-  slope = (float)(scale * 4.0 * q / ((1.0 + q) * (1.0 + q)));
+  const float scale = 1.0f - 1.1920928955078125e-7f;  // 1 - FP32 epsilon
+  eta = scale * tanhf(raw);
+  const float q = expf(-2.0f * fabsf(raw));
+  slope = scale * 4.0f * q / ((1.0f + q) * (1.0f + q));
 }
 
 struct GjShared {
-  double* rowbuf;   // 2 * R doubles
-  double* cand_v;   // 2 doubles   (cross-warp pivot candidates)
+  float* rowbuf;    // 2 * R floats
+  float* cand_v;    // 2 floats    (cross-warp pivot candidates)
   int* cand_i;      // 2 ints
   int* piv;         // R ints      pivot lane of step k
 };
 
-template <int R, int K>
-__device__ __forceinline__ void gj_step(double (&a)[R], const GjShared& sh, int lane_id, bool live, bool& used,
-                                        int& my_step, int& info) {
-  if constexpr (K < R) {
-    constexpr int NW = (R + 31) / 32;
-    double v = (live && !used) ? fabs(a[K]) : -1.0;
+// Run-time loop over the elimination steps; the row registers are rotated by one after every
+// step, so the pivot column is always register 0 and all register indices stay compile-time
+// constants while the loop body fits the instruction cache.
+template <int R>
+__device__ __forceinline__ void gj_eliminate(float (&a)[R], const GjShared& sh, int lane_id, bool live, bool& used,
+                                             int& my_step, int& info) {
+  constexpr int NW = (R + 31) / 32;
+#pragma unroll 1
+  for (int K = 0; K < R; ++K) {
+    float v = (live && !used) ? fabsf(a[0]) : -1.0f;
     int best = lane_id;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-      const double ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
       const int ob = __shfl_xor_sync(0xffffffffu, best, o);
       if (ov > v || (ov == v && ob < best)) { v = ov; best = ob; }
     }
@@ -81,15 +86,15 @@ __device__ __forceinline__ void gj_step(double (&a)[R], const GjShared& sh, int 
       const int w = lane_id >> 5;
       if ((lane_id & 31) == 0) { sh.cand_v[w] = v; sh.cand_i[w] = best; }
       asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32));
-      const double v0 = sh.cand_v[0], v1 = sh.cand_v[1];
+      const float v0 = sh.cand_v[0], v1 = sh.cand_v[1];
       const int i0 = sh.cand_i[0], i1 = sh.cand_i[1];
       if (v1 > v0) { v = v1; best = i1; } else { v = v0; best = i0; }
     }
-    if (v == 0.0 && info == 0) info = K + 1;
-    double* rb = sh.rowbuf + (K & 1) * R;
+    if (v == 0.0f && info == 0) info = K + 1;
+    float* rb = sh.rowbuf + (K & 1) * R;
     if (lane_id == best) {
-      const double inv = 1.0 / a[K];
-      a[K] = 1.0;
+      const float inv = __frcp_rn(a[0]);
+      a[0] = 1.0f;
 #pragma unroll
       for (int j = 0; j < R; ++j) {
         a[j] *= inv;
@@ -102,42 +107,46 @@ __device__ __forceinline__ void gj_step(double (&a)[R], const GjShared& sh, int 
     if (NW == 1) __syncwarp();
     else asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32));
     if (live && lane_id != best) {
-      const double f = a[K];
-      a[K] = 0.0;
+      const float f = a[0];
+      a[0] = 0.0f;
 #pragma unroll
-      for (int j = 0; j < R; ++j) a[j] = fma(-f, rb[j], a[j]);
+      for (int j = 0; j < R; ++j) a[j] = fmaf(-f, rb[j], a[j]);
     }
-    gj_step<R, K + 1>(a, sh, lane_id, live, used, my_step, info);
+    const float first = a[0];
+#pragma unroll
+    for (int j = 0; j + 1 < R; ++j) a[j] = a[j + 1];
+    a[R - 1] = first;
   }
 }
 
-// Inverse of the R x R matrix `src` (FP64, pitch R+1) into `dst` (FP64, pitch R+1); run by the
-// first ceil(R/32) warps of the CTA (the other threads return at once).  Returns 0, or k+1
-// when the k-th pivot was exactly zero.
+// Approximate (FP32) inverse of the R x R matrix `src` (FP64, pitch R+1) into `dst` (FP64, pitch
+// R+1); run by the first ceil(R/32) warps of the CTA (the other threads return at once).
+// Returns 0, or k+1 when the k-th pivot was exactly zero.
 template <int R>
 __device__ __noinline__ int gj_inverse(const double* src, double* dst, const GjShared sh, int tid) {
   constexpr int NW = (R + 31) / 32;
   if (tid >= NW * 32) return 0;
   const bool live = tid < R;
-  double a[R];
+  float a[R];
 #pragma unroll
-  for (int j = 0; j < R; ++j) a[j] = live ? src[tid * (R + 1) + j] : 0.0;
+  for (int j = 0; j < R; ++j) a[j] = live ? (float)src[tid * (R + 1) + j] : 0.0f;
   bool used = false;
   int my_step = 0, info = 0;
-  gj_step<R, 0>(a, sh, tid, live, used, my_step, info);
+  gj_eliminate<R>(a, sh, tid, live, used, my_step, info);
   if (NW == 1) __syncwarp();
   else asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32));
   // this lane holds row `my_step` of (P A)^-1; column k of it is column piv[k] of A^-1
   if (live) {
 #pragma unroll
-    for (int k = 0; k < R; ++k) dst[my_step * (R + 1) + sh.piv[k]] = a[k];
+    for (int k = 0; k < R; ++k) dst[my_step * (R + 1) + sh.piv[k]] = (double)a[k];
   }
   return info;
 }
 
 __host__ __device__ constexpr size_t core_forward_smem_bytes(int r) {
-  // jm, lc (later: inverse) + row buffers + pivot bookkeeping
-  return (size_t)(2 * r * (r + 1) + 2 * r + 2) * sizeof(double) + (size_t)(r + 2) * sizeof(int) + 16;
+  // A = I+J, X, residual (FP64) + row buffers + pivot bookkeeping
+  return (size_t)(3 * r * (r + 1)) * sizeof(double) + (size_t)(2 * r + 2) * sizeof(float) +
+         (size_t)(r + 2) * sizeof(int) + 32;
 }
 
 // One CTA computes one head.  `smem` must provide core_forward_smem_bytes(R), 8-byte aligned.
@@ -147,7 +156,7 @@ __device__ __forceinline__ void core_forward_device(const float* __restrict__ ba
                                                     float* __restrict__ eta_out, float* __restrict__ slope_out,
                                                     float* __restrict__ core_map, int* __restrict__ core_info,
                                                     unsigned char* smem, int tid, int nthreads) {
-  if (tid == 0) {
+  if (tid == nthreads - 1) {
     float e, s;
     eta_maps(eta_raw[h], e, s);
     eta_out[h] = e;
@@ -156,27 +165,58 @@ __device__ __forceinline__ void core_forward_device(const float* __restrict__ ba
   }
   if (complement) return;
   constexpr int P = R + 1;
-  double* jm = reinterpret_cast<double*>(smem);
-  double* lc = jm + R * P;
+  double* am = reinterpret_cast<double*>(smem);  // I + J
+  double* xm = am + R * P;                       // L, then the inverse
+  double* rm = xm + R * P;                       // Newton-Schulz residual
   GjShared sh;
-  sh.rowbuf = lc + R * P;
+  sh.rowbuf = reinterpret_cast<float*>(rm + R * P);
   sh.cand_v = sh.rowbuf + 2 * R;
   sh.cand_i = reinterpret_cast<int*>(sh.cand_v + 2);
   sh.piv = sh.cand_i + 2;
   MS_TICK(20);
-  build_generator(base_raw + (size_t)h * R * R, R, lc, jm, tid, nthreads);
-  for (int i = tid; i < R * R; i += nthreads) {
-    const int row = i / R, col = i - row * R;
-    if (row == col) jm[row * P + col] += 1.0;   // I + J
-  }
+  build_generator(base_raw + (size_t)h * R * R, R, xm, am, tid, nthreads);
+  for (int i = tid; i < R; i += nthreads) am[i * P + i] += 1.0;   // I + J
   __syncthreads();
   MS_TICK(21);
-  const int info = gj_inverse<R>(jm, lc, sh, tid);   // lc <- (I+J)^-1
+  const int info = gj_inverse<R>(am, xm, sh, tid);   // xm <- FP32-accurate inverse
   __syncthreads();
   MS_TICK(22);
+#pragma unroll 1
+  for (int sweep = 0; sweep < 2; ++sweep) {
+    // residual = I - A X
+    for (int i = tid; i < R * R; i += nthreads) {
+      const int row = i / R, col = i - row * R;
+      double acc = row == col ? 1.0 : 0.0;
+      for (int k = 0; k < R; ++k) acc = fma(-am[row * P + k], xm[k * P + col], acc);
+      rm[row * P + col] = acc;
+    }
+    __syncthreads();
+    // X <- X + X residual   (each thread keeps its entries until all reads of X are done)
+    constexpr int PER = (R * R + 127) / 128;   // callers run at least 128 threads
+    double upd[PER];
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+      const int i = tid + e * nthreads;
+      double acc = 0.0;
+      if (i < R * R) {
+        const int row = i / R, col = i - row * R;
+        acc = xm[row * P + col];
+        for (int k = 0; k < R; ++k) acc = fma(xm[row * P + k], rm[k * P + col], acc);
+      }
+      upd[e] = acc;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+      const int i = tid + e * nthreads;
+      if (i < R * R) xm[(i / R) * P + (i % R)] = upd[e];
+    }
+    __syncthreads();
+  }
+  MS_TICK(23);
   for (int i = tid; i < R * R; i += nthreads) {
     const int row = i / R, col = i - row * R;
-    core_map[(size_t)h * R * R + i] = (float)(2.0 * lc[row * P + col] - (row == col ? 1.0 : 0.0));
+    core_map[(size_t)h * R * R + i] = (float)(2.0 * xm[row * P + col] - (row == col ? 1.0 : 0.0));
   }
   if (tid == 0 && info) core_info[h] = info;
 }
@@ -209,7 +249,13 @@ __device__ __forceinline__ void core_backward_device(const float* __restrict__ b
     for (int b = 0; b < batch; ++b) acc += hmat[((size_t)b * heads + h) * r * r + i];
     dfm[row * p + col] = (double)acc;
     if (row == col) tr += (double)acc;
-    if (!complement) pm[row * p + col] = (double)core_map[(size_t)h * r * r + i] + (row == col ? 1.0 : 0.0);
+    if (!complement) {
+      pm[row * p + col] = (double)core_map[(size_t)h * r * r + i] + (row == col ? 1.0 : 0.0);
+      double v = 0.0;
+      if (row > col) v = (double)base_raw[(size_t)h * r * r + i];
+      else if (row == col) v = softplus_shifted(base_raw[(size_t)h * r * r + i]);
+      lc[row * p + col] = v;
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) tr += __shfl_xor_sync(0xffffffffu, tr, o);
@@ -236,18 +282,6 @@ __device__ __forceinline__ void core_backward_device(const float* __restrict__ b
     for (int k = 0; k < r; ++k) acc = fma(pm[k * p + row], dfm[k * p + col], acc);
     t1[row * p + col] = acc;
   }
-  // L (does not touch dfm/t1); the generator itself is not needed
-  for (int i = tid; i < r * r; i += nthreads) {
-    const int row = i / r, col = i - row * r;
-    double v = 0.0;
-    if (row > col) {
-      v = (double)base_raw[(size_t)h * r * r + i];
-    } else if (row == col) {
-      const double x = (double)base_raw[(size_t)h * r * r + i] + kSoftplusShift;
-      v = x > 30.0 ? x : log1p(exp(x));
-    }
-    lc[row * p + col] = v;
-  }
   __syncthreads();
   for (int i = tid; i < r * r; i += nthreads) {
     const int row = i / r, col = i - row * r;
@@ -265,8 +299,8 @@ __device__ __forceinline__ void core_backward_device(const float* __restrict__ b
       double acc = 0.0;
       for (int k = col; k < r; ++k) acc = fma(dfm[row * p + k] + dfm[k * p + row], lc[k * p + col], acc);
       if (row == col) {
-        const double x = (double)base_raw[(size_t)h * r * r + i] + kSoftplusShift;
-        acc *= 1.0 / (1.0 + exp(-x));
+        const float x = base_raw[(size_t)h * r * r + i] + kSoftplusShiftF;
+        acc *= (double)(1.0f / (1.0f + expf(-x)));
       }
       out = acc;
     }
