@@ -146,9 +146,16 @@ Plan make_plan(const ms_shape& s) {
   p.dblocks = (s.head_dim + kChanBlock - 1) / kChanBlock;
   p.dpad = (s.head_dim + 7) & ~7;
   const int tiles = (s.tokens + kTileTokens - 1) / kTileTokens;
-  const long want = 2L * sm_count();
+  static const bool no_tma_env = [] {
+    const char* v = std::getenv("MEMSOLVE_NO_TMA");
+    return v && v[0] == '1';
+  }();
+  // the TMA statistics kernels (rank 16/32, head dimension a multiple of 64) run one 8-warp CTA
+  // per SM; the generic kernels two 4-warp CTAs
+  const bool wide_ctas = !no_tma_env && (s.head_dim % 64) == 0 && (s.rank == 16 || s.rank == 32);
+  const long want = (wide_ctas ? 1L : 2L) * sm_count();
   long per = (long)p.systems * p.dblocks;
-  long chunks = (want + per - 1) / per;
+  long chunks = want / per;   // rounded down: the whole grid is resident in one wave
   if (chunks < 1) chunks = 1;
   if (chunks > tiles) chunks = tiles;
   const int tiles_per_chunk = (int)((tiles + chunks - 1) / chunks);

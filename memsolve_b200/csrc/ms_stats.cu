@@ -313,6 +313,10 @@ stats_kernel(const StatsParams p) {
   }
 }
 
+int launch_stats_tma(const ms_shape& s, const Plan& plan, bool grad, const void* projected, const void* dy,
+                     const float* cos, const float* sin, float* partials, float* de_partials,
+                     const float* base_raw, const float* eta_raw, const ms_tape* core_tape, cudaStream_t st);
+
 // Sum partials in chunk order and apply 1/n (Gram) and 1/sqrt(n) (moment) with IEEE rounding.
 // packed forward:  [systems][r*r + r*d]      packed adjoint: [systems][r*d] then [systems] de
 __global__ void pack_stats_kernel(const float* __restrict__ partials, const float* __restrict__ de_partials,
@@ -354,6 +358,11 @@ static int launch_rank(const StatsParams& p, dim3 grid, bool rot, bool aligned, 
 int launch_stats(const ms_shape& s, const Plan& plan, bool grad, const void* projected, const void* dy,
                  const float* cos, const float* sin, float* partials, float* de_partials,
                  const float* base_raw, const float* eta_raw, const ms_tape* core_tape, cudaStream_t st) {
+  if (plan.tma) {
+    const int r = launch_stats_tma(s, plan, grad, projected, dy, cos, sin, partials, de_partials, base_raw, eta_raw,
+                                   core_tape, st);
+    if (r != -1) return r;
+  }
   StatsParams p;
   const bool fuse_core = !grad && core_tape != nullptr;
   p.base_raw = base_raw;
