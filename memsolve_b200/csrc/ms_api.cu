@@ -155,7 +155,9 @@ Plan make_plan(const ms_shape& s) {
   const bool wide_ctas = !no_tma_env && (s.head_dim % 64) == 0 && (s.rank == 16 || s.rank == 32);
   const long want = (wide_ctas ? 1L : 2L) * sm_count();
   long per = (long)p.systems * p.dblocks;
-  long chunks = want / per;   // rounded down: the whole grid is resident in one wave
+  // rounded down so that the whole grid (plus the per-head CTAs that ride along with the forward
+  // statistics of the one-CTA-per-SM kernels) is resident in one wave
+  long chunks = (want - (wide_ctas ? s.heads : 0)) / per;
   if (chunks < 1) chunks = 1;
   if (chunks > tiles) chunks = tiles;
   const int tiles_per_chunk = (int)((tiles + chunks - 1) / chunks);

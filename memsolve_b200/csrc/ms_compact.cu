@@ -9,8 +9,10 @@
 //
 // Replaces the reference's native Cholesky-inverse (csrc/ball/solvers.cuh:34-217) and its
 // Triton compact kernels (memsolve/ball/cuda.py:2530-2768).  The Cholesky factor is computed
-// in FP64 with one matrix row per lane in registers; the r x d products are FP32 FMA on
-// shared-memory operands.  Partial sums of the token reductions are added in chunk order with
+// with one matrix row per lane in registers (FP32, the diagonal carried in FP64, like the
+// reference's native kernel) while the other warps already sum the partial moments; the
+// r x d and r x r products are FP32 FMA on shared-memory operands with several independent
+// accumulation chains per thread.  Partial sums of the token reductions are added in chunk order with
 // several independent loads in flight, so the result is order-deterministic and the kernel is
 // not bound by load latency.
 #include "ms_core.cuh"
@@ -163,6 +165,46 @@ __device__ __forceinline__ void store_split(__nv_bfloat16* hi, __nv_bfloat16* lo
   const __nv_bfloat16 hv = __float2bfloat16_rn(v);
   hi[idx] = hv;
   lo[idx] = __float2bfloat16_rn(v - __bfloat162float(hv));
+}
+
+// r x r products spread over the CTA: thread t owns entries t, t+256, ... (kRRPer<R> of them) and
+// advances all of their dot products together, so the FMA chains are independent.
+template <int R>
+constexpr int kRRPer = (R * R + kCompactThreads - 1) / kCompactThreads;
+
+template <int R, class INIT>
+__device__ __forceinline__ void rr_init(float (&acc)[kRRPer<R>], INIT init, int tid) {
+#pragma unroll
+  for (int e = 0; e < kRRPer<R>; ++e) {
+    const int i = tid + e * kCompactThreads;
+    acc[e] = i < R * R ? init(i / R, i % R) : 0.f;
+  }
+}
+
+// acc[e] += sum_k fa(row_e, k) * fb(k, col_e)
+template <int R, int KLEN, class FA, class FB>
+__device__ __forceinline__ void rr_accumulate(float (&acc)[kRRPer<R>], FA fa, FB fb, int tid) {
+  int row[kRRPer<R>], col[kRRPer<R>];
+#pragma unroll
+  for (int e = 0; e < kRRPer<R>; ++e) {
+    const int i = min(tid + e * kCompactThreads, R * R - 1);
+    row[e] = i / R;
+    col[e] = i % R;
+  }
+#pragma unroll 4
+  for (int k = 0; k < KLEN; ++k) {
+#pragma unroll
+    for (int e = 0; e < kRRPer<R>; ++e) acc[e] = fmaf(fa(row[e], k), fb(k, col[e]), acc[e]);
+  }
+}
+
+template <int R, class STORE>
+__device__ __forceinline__ void rr_store(const float (&acc)[kRRPer<R>], STORE store, int tid) {
+#pragma unroll
+  for (int e = 0; e < kRRPer<R>; ++e) {
+    const int i = tid + e * kCompactThreads;
+    if (i < R * R) store(i / R, i % R, i, acc[e]);
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -322,6 +364,7 @@ compact_backward_kernel(const CompactBwdParams p) {
   const float* src = p.partials + (size_t)sys * nch * p.pf;
   const float eta = p.eta[h];
   const int d = p.head_dim;
+  MS_TICK(9);
 
   for (int i = tid; i < R * R; i += kCompactThreads) {
     const int row = i / R, col = i - row * R;
@@ -346,6 +389,7 @@ compact_backward_kernel(const CompactBwdParams p) {
   }
   __syncthreads();
 
+  MS_TICK(10);
   for (int jb = 0; jb < p.dblocks; ++jb) {
     const int d0 = jb * 64, dv = min(64, d - d0);
     {
@@ -370,22 +414,26 @@ compact_backward_kernel(const CompactBwdParams p) {
       }
     }
     __syncthreads();
+    MS_TICK(11);
     // U = T E
     small_mm<R>([&](int i, int j) { return ts[i * P + j]; }, [](int) { return 0; },
                 [](int i) { return i + 1; }, es, us, tid);
     __syncthreads();
+    MS_TICK(12);
     // H += U Z^T   (r x r, contraction over the 64 channels)
-    for (int i = tid; i < R * R; i += kCompactThreads) {
-      const int row = i / R, col = i - row * R;
-      float acc = hm[row * P + col];
-#pragma unroll 8
-      for (int c = 0; c < 64; ++c) acc = fmaf(us[row * 65 + c], zs[col * 65 + c], acc);
-      hm[row * P + col] = acc;
+    {
+      float acc[kRRPer<R>];
+      rr_init<R>(acc, [&](int row, int col) { return hm[row * P + col]; }, tid);
+      rr_accumulate<R, 64>(acc, [&](int row, int c) { return us[row * 65 + c]; },
+                           [&](int c, int col) { return zs[col * 65 + c]; }, tid);
+      rr_store<R>(acc, [&](int row, int col, int, float v) { hm[row * P + col] = v; }, tid);
     }
+    MS_TICK(13);
     // dZ = M^T U -> es
     small_mm<R>([&](int i, int j) { return mm[j * P + i]; }, [](int) { return 0; },
                 [](int) { return R; }, us, es, tid);
     __syncthreads();
+    MS_TICK(14);
     // dQ = T^T dZ -> zs
     small_mm<R>([&](int i, int j) { return ts[j * P + i]; }, [](int i) { return i; },
                 [](int) { return R; }, es, zs, tid);
@@ -400,41 +448,48 @@ compact_backward_kernel(const CompactBwdParams p) {
     __syncthreads();
   }
 
+  MS_TICK(16);
   // H to global for the per-head sum; X = -M H^T - M^T H
   float* xs = es;   // R*P fits in R*65
   float* ys = us;
-  for (int i = tid; i < R * R; i += kCompactThreads) {
-    const int row = i / R, col = i - row * R;
-    p.hmat[(size_t)sys * R * R + i] = hm[row * P + col];
-    float acc = 0.f;
-    for (int k = 0; k < R; ++k) {
-      acc = fmaf(-mm[row * P + k], hm[col * P + k], acc);
-      acc = fmaf(-mm[k * P + row], hm[k * P + col], acc);
-    }
-    xs[row * P + col] = acc;
+  {
+    float acc[kRRPer<R>];
+    rr_init<R>(acc, [&](int, int) { return 0.f; }, tid);
+    rr_accumulate<R, R>(acc, [&](int row, int k) { return -mm[row * P + k]; },
+                        [&](int k, int col) { return hm[col * P + k]; }, tid);
+    rr_accumulate<R, R>(acc, [&](int row, int k) { return -mm[k * P + row]; },
+                        [&](int k, int col) { return hm[k * P + col]; }, tid);
+    rr_store<R>(acc, [&](int row, int col, int i, float v) {
+      p.hmat[(size_t)sys * R * R + i] = hm[row * P + col];
+      xs[row * P + col] = v;
+    }, tid);
   }
   __syncthreads();
-  // sym = low + low^T with low = tril(X,-1)/2 + diag(X)/4;   Y = sym T
-  for (int i = tid; i < R * R; i += kCompactThreads) {
-    const int row = i / R, col = i - row * R;
-    float acc = 0.f;
-    for (int k = col; k < R; ++k) {
-      const float s = 0.5f * (row >= k ? xs[row * P + k] : xs[k * P + row]);
-      acc = fmaf(s, ts[k * P + col], acc);
-    }
-    ys[row * P + col] = acc;
+  MS_TICK(17);
+  // sym = low + low^T with low = tril(X,-1)/2 + diag(X)/4, i.e. sym[r][k] = X[max(r,k)][min(r,k)]/2;
+  // Y = sym T  (T lower triangular with explicit zeros above the diagonal)
+  {
+    float acc[kRRPer<R>];
+    rr_init<R>(acc, [&](int, int) { return 0.f; }, tid);
+    rr_accumulate<R, R>(acc, [&](int row, int k) { return 0.5f * (row >= k ? xs[row * P + k] : xs[k * P + row]); },
+                        [&](int k, int col) { return ts[k * P + col]; }, tid);
+    rr_store<R>(acc, [&](int row, int col, int, float v) { ys[row * P + col] = v; }, tid);
   }
   __syncthreads();
+  MS_TICK(18);
   // dG = T^T Y ;  stored as dG + dG^T (dG is symmetric) in two BF16 words
   __nv_bfloat16* ghi = p.gram_grad + (size_t)sys * 2 * R * R;
   __nv_bfloat16* glo = ghi + R * R;
-  for (int i = tid; i < R * R; i += kCompactThreads) {
-    const int row = i / R, col = i - row * R;
-    float acc = 0.f, acct = 0.f;
-    for (int k = row; k < R; ++k) acc = fmaf(ts[k * P + row], ys[k * P + col], acc);
-    for (int k = col; k < R; ++k) acct = fmaf(ts[k * P + col], ys[k * P + row], acct);
-    store_split(ghi, glo, i, acc + acct);
+  {
+    float acc[kRRPer<R>];
+    rr_init<R>(acc, [&](int, int) { return 0.f; }, tid);
+    rr_accumulate<R, R>(acc, [&](int row, int k) { return ts[k * P + row]; },
+                        [&](int k, int col) { return ys[k * P + col]; }, tid);
+    rr_accumulate<R, R>(acc, [&](int row, int k) { return ys[k * P + row]; },
+                        [&](int k, int col) { return ts[k * P + col]; }, tid);
+    rr_store<R>(acc, [&](int, int, int i, float v) { store_split(ghi, glo, i, v); }, tid);
   }
+  MS_TICK(19);
 }
 
 // ---------------------------------------------------------------------------------------
