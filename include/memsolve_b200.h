@@ -200,7 +200,8 @@ int ms_stats_backward(const ms_shape* shape, const void* projected, const void* 
  *   d_base_raw f32  [H,r,r]       (not written in complement mode)
  *   d_eta_raw  f32  [H]
  * `grad_scale` multiplies d_base_raw and d_eta_raw (1/world_size under sequence parallelism,
- * memsolve/ball/cuda.py:3221-3226).
+ * memsolve/ball/cuda.py:3221-3226).  With d_eta_raw == NULL only the per-(b,h) part runs and the
+ * per-head sums stay in `workspace` for ms_token_backward_core.
  */
 int ms_compact_backward(const ms_shape* shape, const float* counts, void* workspace,
                         size_t workspace_bytes, const float* packed, const ms_tape* tape,
@@ -213,6 +214,26 @@ int ms_token_backward(const ms_shape* shape, const void* projected, const void* 
                       const float* cos, const float* sin, const float* counts,
                       const ms_tape* tape, const void* gram_grad, const void* cross_grad,
                       void* dprojected, void* stream);
+
+/*
+ * Sequence-parallel building blocks that keep the per-head core off the critical path (same work
+ * as the separate calls, fewer launches): the statistics launch also computes eta / F in spare
+ * CTAs, and the token-backward launch also computes d_base_raw / d_eta_raw in spare CTAs.
+ *   ms_stats_forward_core   = ms_core_forward + ms_stats_forward   (cuda.py:2798-2840 + 2121-2247)
+ *   ms_token_backward_core  = ms_token_backward + the per-head half of ms_compact_backward; call
+ *                             ms_compact_backward first with d_eta_raw == NULL (it then leaves the
+ *                             per-head sums H and de in `workspace` and skips the core adjoint).
+ */
+int ms_stats_forward_core(const ms_shape* shape, const void* projected, const float* base_raw,
+                          const float* eta_raw, const float* cos, const float* sin,
+                          const float* counts, void* workspace, size_t workspace_bytes, float* packed,
+                          const ms_tape* tape, void* stream);
+int ms_token_backward_core(const ms_shape* shape, const void* projected, const void* dy,
+                           const float* cos, const float* sin, const float* counts,
+                           const ms_tape* tape, const void* gram_grad, const void* cross_grad,
+                           void* dprojected, const float* base_raw, void* workspace,
+                           size_t workspace_bytes, float grad_scale, float* d_base_raw,
+                           float* d_eta_raw, void* stream);
 
 /* Whole backward on one rank: adjoint stats + compact adjoint + token pass (no collective). */
 int ms_mix_backward(const ms_shape* shape, const void* projected, const void* dy,

@@ -73,6 +73,10 @@ _SIGNATURES = {
                                            ctypes.POINTER(_Tape), _P, _P, ctypes.c_float, _P, _P, _P, _P, _P]),
     "ms_token_backward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, ctypes.POINTER(_Tape),
                                          _P, _P, _P, _P]),
+    "ms_stats_forward_core": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t,
+                                             _P, ctypes.POINTER(_Tape), _P]),
+    "ms_token_backward_core": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, ctypes.POINTER(_Tape),
+                                              _P, _P, _P, _P, _P, ctypes.c_size_t, ctypes.c_float, _P, _P, _P]),
     "ms_mix_backward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t,
                                        ctypes.POINTER(_Tape), _P, _P, _P, _P, _P, _P]),
 }
@@ -324,12 +328,11 @@ def _mix_forward(projected, base, raw, counts, sequence_parallel, cos, sin):
                 _ptr(counts), ws.data_ptr(), ws.numel(), ctypes.byref(tape_c), mixed.data_ptr(), stream),
                 "forward")
         else:
-            _check(_LIB.ms_core_forward(ctypes.byref(shape), base_ptr, raw.data_ptr(), ctypes.byref(tape_c),
-                                        stream), "core forward")
             packed = torch.empty(_LIB.ms_packed_stats_floats(ctypes.byref(shape), 0), device=device,
                                  dtype=torch.float32)
-            _check(_LIB.ms_stats_forward(ctypes.byref(shape), projected.data_ptr(), _ptr(cos), _ptr(sin),
-                                         _ptr(counts), ws.data_ptr(), ws.numel(), packed.data_ptr(), stream),
+            _check(_LIB.ms_stats_forward_core(ctypes.byref(shape), projected.data_ptr(), base_ptr, raw.data_ptr(),
+                                              _ptr(cos), _ptr(sin), _ptr(counts), ws.data_ptr(), ws.numel(),
+                                              packed.data_ptr(), ctypes.byref(tape_c), stream),
                    "statistics")
             # the only cross-GPU step of the forward: SUM of the packed (G, Q) statistics
             (packed,) = sequence_parallel.sum_tensors(packed)
@@ -385,11 +388,13 @@ def _mix_backward(projected, gradient, base, raw, counts, sequence_parallel, cos
             _check(_LIB.ms_compact_backward(
                 ctypes.byref(shape), _ptr(counts), ws.data_ptr(), ws.numel(), packed.data_ptr(),
                 ctypes.byref(tape_c), base_ptr, raw.data_ptr(), scale, gram_grad.data_ptr(),
-                cross_grad.data_ptr(), _ptr(d_base), d_raw.data_ptr(), stream), "compact backward")
-            _check(_LIB.ms_token_backward(
+                cross_grad.data_ptr(), None, None, stream), "compact backward")
+            # the per-head parameter gradients ride along with the token pass
+            _check(_LIB.ms_token_backward_core(
                 ctypes.byref(shape), projected.data_ptr(), gradient.data_ptr(), _ptr(cos), _ptr(sin),
                 _ptr(counts), ctypes.byref(tape_c), gram_grad.data_ptr(), cross_grad.data_ptr(),
-                d_projected.data_ptr(), stream), "token backward")
+                d_projected.data_ptr(), base_ptr, ws.data_ptr(), ws.numel(), scale, _ptr(d_base),
+                d_raw.data_ptr(), stream), "token backward")
     return d_projected, d_base, d_raw
 
 

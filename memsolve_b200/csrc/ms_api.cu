@@ -400,15 +400,59 @@ int ms_compact_backward(const ms_shape* shape, const float* counts, void* worksp
   MS_TRY(device_status());
   (void)eta_raw;
   if (!tape || !tape->eta || !tape->eta_slope || !tape->inverse || !tape->state) return MS_ERR_INVALID_ARGUMENT;
-  if (!gram_grad || !cross_grad || !d_eta_raw) return MS_ERR_INVALID_ARGUMENT;
-  if (!shape->complement && (!base_raw || !tape->core_map || !d_base_raw)) return MS_ERR_INVALID_ARGUMENT;
+  if (!gram_grad || !cross_grad) return MS_ERR_INVALID_ARGUMENT;
+  const bool with_core = d_eta_raw != nullptr;
+  if (with_core && !shape->complement && (!base_raw || !tape->core_map || !d_base_raw)) return MS_ERR_INVALID_ARGUMENT;
   const Plan plan = make_plan(*shape);
   if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
   const Workspace w = carve(workspace, plan);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   MS_TRY(launch_compact_backward(*shape, plan, counts, packed ? packed : w.partials, w.de_partials,
                                  packed != nullptr, *tape, w.hmat, w.de_sys, gram_grad, cross_grad, st));
+  if (!with_core) return MS_OK;
   return launch_core_backward(*shape, base_raw, w.hmat, w.de_sys, *tape, grad_scale, d_base_raw, d_eta_raw, st);
+}
+
+int ms_token_backward_core(const ms_shape* shape, const void* projected, const void* dy, const float* cos,
+                           const float* sin, const float* counts, const ms_tape* tape, const void* gram_grad,
+                           const void* cross_grad, void* dprojected, const float* base_raw, void* workspace,
+                           size_t workspace_bytes, float grad_scale, float* d_base_raw, float* d_eta_raw,
+                           void* stream) {
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  if (!projected || !dy || !dprojected || !gram_grad || !cross_grad || !tape || !tape->eta || !tape->coeff ||
+      !tape->eta_slope || !d_eta_raw)
+    return MS_ERR_INVALID_ARGUMENT;
+  if (!shape->complement && (!base_raw || !tape->core_map || !d_base_raw)) return MS_ERR_INVALID_ARGUMENT;
+  if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
+  Plan plan = make_plan(*shape);
+  if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+  const Workspace w = carve(workspace, plan);
+  plan.aligned = plan.aligned && is16(projected) && is16(dy) && is16(dprojected);
+  CoreAdjoint core{base_raw, w.hmat, w.de_sys, d_base_raw, d_eta_raw, grad_scale};
+  return launch_token_backward(*shape, plan, projected, dy, cos, sin, counts, *tape, gram_grad, cross_grad,
+                               dprojected, &core, static_cast<cudaStream_t>(stream));
+}
+
+int ms_stats_forward_core(const ms_shape* shape, const void* projected, const float* base_raw,
+                          const float* eta_raw, const float* cos, const float* sin, const float* counts,
+                          void* workspace, size_t workspace_bytes, float* packed, const ms_tape* tape,
+                          void* stream) {
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  if (!projected || !eta_raw || !tape || !tape->eta || !tape->eta_slope || !tape->core_info)
+    return MS_ERR_INVALID_ARGUMENT;
+  if (!shape->complement && (!base_raw || !tape->core_map)) return MS_ERR_INVALID_ARGUMENT;
+  if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
+  Plan plan = make_plan(*shape);
+  if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+  plan.aligned = plan.aligned && is16(projected) && (!shape->rotary_rows || (is16(cos) && is16(sin)));
+  const Workspace w = carve(workspace, plan);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MS_TRY(launch_stats(*shape, plan, false, projected, nullptr, cos, sin, w.partials, nullptr, base_raw, eta_raw,
+                      tape, st));
+  if (packed) MS_TRY(launch_pack_stats(*shape, plan, false, w.partials, nullptr, counts, packed, st));
+  return MS_OK;
 }
 
 int ms_token_backward(const ms_shape* shape, const void* projected, const void* dy, const float* cos,
