@@ -263,6 +263,18 @@ def time_kernels(layer, cfg, tokens, device, reps=10, warm=3):
     return out
 
 
+# DRAM bytes (read + write) of one launch at 32768 tokens, rank 32, from the ncu capture summarised in
+# profiles/mixer_kernels_c3_ncu_full.md.  Traffic of these streaming kernels grows in proportion to tokens.
+_NCU_DRAM_BYTES_C3 = {"stats_forward": 87.5e6, "readout": 101.2e6, "stats_backward": 138.2e6,
+                      "token_backward": 180.3e6}
+
+
+def _ncu_traffic(workload, kernel, tokens):
+    if workload != "c3" or kernel not in _NCU_DRAM_BYTES_C3:
+        return None
+    return _NCU_DRAM_BYTES_C3[kernel] * tokens / 32768
+
+
 def run_ours(args, cfg):
     import torch.distributed as dist
     from memsolve_b200.ball import cuda as C
@@ -428,7 +440,10 @@ def run_ours(args, cfg):
         "eager_ms_per_step": eager_total / args.steps * 1e3,
         "roofline": {
             "bound": "hbm", "kernel": name, "achieved": achieved, "peak": hbm, "unit": "GB/s",
-            "frac": achieved / hbm, "traffic": None, "peak_source": f"of {which}",
+            "frac": achieved / hbm, "traffic": _ncu_traffic(args.workload, name, tokens),
+            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 32768 tokens "
+                              "(profiles/mixer_kernels_c3_ncu_full.md), scaled by tokens",
+            "peak_source": f"of {which}",
             "per_kernel_us": {k: round(v["s"] * 1e6, 2) for k, v in kern.items()},
             "per_kernel_gbs": {k: round(v["bytes"] / v["s"] / 1e9, 1) for k, v in kern.items() if v["bytes"]},
             "mix_core": {"bytes_per_token": 2 * (5 * width + 3 * cfg["dim"]), "us": round(mixer_time * 1e6, 2),
