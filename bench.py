@@ -476,6 +476,7 @@ def main():
                     help="launch each mixer kernel alone (--reps times) and print their timings; used for ncu")
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--kernel-warmup", type=int, default=3)
+    ap.add_argument("--tokens", type=int, default=0, help="with --kernels-only: tokens per launch instead of the workload's")
     args = ap.parse_args()
     cfg = CONFIGS[args.workload]
     if args.kernels_only:
@@ -484,6 +485,8 @@ def main():
         torch.cuda.set_device(device)
         C.load(device=device)
         tokens = cfg["global_tokens"] // args.gpus if cfg["strong"] else cfg["local_tokens"]
+        if args.tokens > 0:
+            tokens = args.tokens
         kern = time_kernels(build_layer(cfg, device), cfg, tokens, device, reps=args.reps, warm=args.kernel_warmup)
         print(json.dumps({k: {"us": round(v["s"] * 1e6, 2), "gbs": round(v["bytes"] / v["s"] / 1e9, 1)}
                           for k, v in kern.items()}))

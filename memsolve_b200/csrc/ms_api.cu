@@ -152,12 +152,15 @@ Plan make_plan(const ms_shape& s) {
   }();
   // the TMA statistics kernels (rank 16/32, head dimension a multiple of 64) run one 8-warp CTA
   // per SM; the generic kernels two 4-warp CTAs
-  const bool wide_ctas = !no_tma_env && (s.head_dim % 64) == 0 && (s.rank == 16 || s.rank == 32);
+  const bool tma_stats = !no_tma_env && (s.head_dim % 64) == 0 && (s.rank == 16 || s.rank == 32);
+  p.stats_cb = (tma_stats && s.rank == 32 && tuning_variant("MEMSOLVE_STATS_VARIANT") > 0) ? 32 : 64;
+  p.de_slots = 2 * p.dblocks;
+  const bool wide_ctas = tma_stats && p.stats_cb == 64;
   const long want = (wide_ctas ? 1L : 2L) * sm_count();
-  long per = (long)p.systems * p.dblocks;
+  long per = (long)p.systems * (p.stats_cb == 32 ? s.head_dim / 32 : p.dblocks);
   // rounded down so that the whole grid (plus the per-head CTAs that ride along with the forward
-  // statistics of the one-CTA-per-SM kernels) is resident in one wave
-  long chunks = (want - (wide_ctas ? s.heads : 0)) / per;
+  // statistics of the TMA kernels) is resident in one wave
+  long chunks = (want - (tma_stats ? s.heads : 0)) / per;
   if (chunks < 1) chunks = 1;
   if (chunks > tiles) chunks = tiles;
   const int tiles_per_chunk = (int)((tiles + chunks - 1) / chunks);
@@ -172,7 +175,7 @@ Plan make_plan(const ms_shape& s) {
   p.fwd_partial_floats = (size_t)s.rank * s.rank + (size_t)s.rank * s.head_dim;
   p.bwd_partial_floats = (size_t)s.rank * s.head_dim;
   p.ws_partials = round64((size_t)p.systems * p.chunks * p.fwd_partial_floats);
-  p.ws_de = round64((size_t)p.systems * p.chunks * p.dblocks);
+  p.ws_de = round64((size_t)p.systems * p.chunks * p.de_slots);
   p.ws_hmat = round64((size_t)p.systems * s.rank * s.rank);
   p.ws_de_sys = round64((size_t)p.systems);
   p.ws_total_bytes = (p.ws_partials + p.ws_de + p.ws_hmat + p.ws_de_sys) * sizeof(float);

@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/memsolve_b200.h"
 
@@ -33,6 +34,8 @@ constexpr int kChanBlock = 64;    // content channels handled per pass (one 128-
 struct Plan {
   int systems;       // B*H
   int dblocks;       // ceil(d / 64)
+  int stats_cb;      // channels per CTA of the token reductions (64, or 32 for two CTAs per SM)
+  int de_slots;      // <dY,C> partial entries per (system, chunk): two per 64-channel block
   int dpad;          // d rounded up to a multiple of 8 (pitch of split coefficient tensors)
   int chunks;        // token chunks per system in the reductions
   int chunk_tokens;  // tokens per chunk (multiple of 64)
@@ -41,7 +44,7 @@ struct Plan {
   size_t fwd_partial_floats;  // per (system, chunk): r*r + r*d
   size_t bwd_partial_floats;  // per (system, chunk): r*d
   size_t ws_partials;         // floats
-  size_t ws_de;               // floats: systems * chunks * dblocks
+  size_t ws_de;               // floats: systems * chunks * de_slots
   size_t ws_hmat;             // floats: systems * r * r
   size_t ws_de_sys;           // floats: systems
   size_t ws_total_bytes;
@@ -60,6 +63,12 @@ struct CoreAdjoint {
 Plan make_plan(const ms_shape& s);
 int check_shape(const ms_shape* s);
 int sm_count();
+// Developer switch: integer value of an environment variable (0 when unset) selecting one of the
+// compiled launch configurations of a kernel.
+inline int tuning_variant(const char* name) {
+  const char* v = getenv(name);
+  return v ? atoi(v) : 0;
+}
 // Raise a kernel's dynamic shared-memory limit once per (kernel, device); later calls are a
 // table lookup, so no function attribute is touched while a stream is being captured.
 int ensure_dynamic_smem(const void* kernel, int bytes);

@@ -8,202 +8,227 @@
 //                                 ms_core.cuh (also run from spare CTAs of the streaming kernels)
 //
 // Replaces the reference's native Cholesky-inverse (csrc/ball/solvers.cuh:34-217) and its
-// Triton compact kernels (memsolve/ball/cuda.py:2530-2768).  The Cholesky factor is computed
-// with one matrix row per lane in registers (FP32, the diagonal carried in FP64, like the
-// reference's native kernel) while the other warps already sum the partial moments; the
-// r x d and r x r products are FP32 FMA on shared-memory operands with several independent
-// accumulation chains per thread.  Partial sums of the token reductions are added in chunk order with
-// several independent loads in flight, so the result is order-deterministic and the kernel is
-// not bound by load latency.
+// Triton compact kernels (memsolve/ball/cuda.py:2530-2768).  These kernels run on one CTA per
+// (sample, head) and are bound by latency, not by throughput, so each stage is shaped for a
+// short dependency chain: the partial sums of the token reductions are fetched with bulk
+// asynchronous copies into shared memory while the per-head matrices are set up and are then
+// added in chunk order (order-deterministic); the Cholesky factor is computed by the whole
+// CTA (FP32, the diagonal carried in FP64, like the reference's native kernel) with one
+// barrier per elimination step; the r x d and r x r products are FP32 FMA on 4 x 2 register
+// tiles with vector loads from shared memory.
 #include "ms_core.cuh"
+#include "ms_tma.cuh"
 
 namespace ms {
 
 constexpr int kCompactThreads = 256;
-
-// ---------------------------------------------------------------------------------------
-// Cholesky inverse factor, one matrix row per lane, FP64 registers
-// ---------------------------------------------------------------------------------------
-// gs: G (FP32, pitch R) in shared memory.  Writes T = chol(I + sym(G))^-1 (lower triangular,
-// FP32, pitch R+1) to ts.  Executed by the first ceil(R/32) warps.  Gaussian elimination
-// applies the unit-lower factor to the identity in place; a final row scaling by the inverse
-// square roots of the pivots turns it into the Cholesky inverse.
-// One elimination step per template instance, so that every register index is a constant.
-// The bulk is FP32; each row's diagonal entry (its future pivot) is carried in FP64, as the
-// reference's native Cholesky does.
-template <int R, int K>
-__device__ __forceinline__ void cholesky_eliminate(float (&a)[R], double& diag, float* rowbuf, int i, bool live) {
-  if constexpr (K < R) {
-    constexpr int NW = (R + 31) / 32;
-    float* rb = rowbuf + (K & 1) * R;
-    if (i == K) {
-      const float inv0 = __frcp_rn((float)diag);
-      const double inv = (double)inv0 * fma(-diag, (double)inv0, 2.0);   // one Newton step in FP64
-      rb[K] = (float)inv;
-#pragma unroll
-      for (int j = K + 1; j < R; ++j) rb[j] = a[j];
-#pragma unroll
-      for (int j = 0; j < K; ++j) rb[j] = a[j];
-    }
-    if (NW == 1) __syncwarp();
-    else asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32));
-    if (live && i > K) {
-      const float f = a[K] * rb[K];
-      diag = fma(-(double)f, (double)rb[i], diag);
-#pragma unroll
-      for (int j = 0; j < R; ++j) {
-        if (j != K) a[j] = fmaf(-f, rb[j], a[j]);
-      }
-      a[K] = -f;
-    }
-    cholesky_eliminate<R, K + 1>(a, diag, rowbuf, i, live);
-  }
-}
+constexpr int kQP = 68;   // pitch in floats of the r x 64 blocks: rows 16-byte aligned, 4-bank skew
 
 template <int R>
-__device__ __noinline__ void cholesky_inverse_rows(const float* gs, float* ts, float* rowbuf, int tid) {
-  constexpr int NW = (R + 31) / 32;
-  if (tid >= NW * 32) return;
-  const int i = tid;
-  const bool live = i < R;
-  float a[R];
+struct CompactDims {
+  static constexpr int TPR = R <= 16 ? 16 : (R <= 32 ? 8 : 4);   // threads per matrix row in the factorisation
+  static constexpr int CPT = R / TPR;                            // columns per thread
+  static constexpr int RP = R + 4;                               // pitch in floats of the r x r matrices
+  static_assert(R * TPR <= kCompactThreads && CPT * TPR == R, "factorisation layout");
+};
+
+// ---------------------------------------------------------------------------------------
+// Cholesky inverse factor with the whole CTA
+// ---------------------------------------------------------------------------------------
+// gs: G (FP32, pitch R).  Writes T = chol(I + sym(G))^-1 (lower triangular, FP32) to ts (row
+// major, pitch RP) and its transpose to tT.  Gaussian elimination applies the unit-lower factor
+// to the identity in place; a final row scaling by the inverse square roots of the pivots turns
+// it into the Cholesky inverse.  The bulk is FP32; each row's diagonal entry (its future pivot)
+// is carried in FP64, as the reference's native Cholesky does.
+// Row i lives in the registers of TPR neighbouring threads (columns q, q+TPR, ...).  Per step
+// the owners of the pivot row and of the pivot column publish them (double buffered) and one
+// CTA barrier separates the steps, so a step costs one barrier, a handful of shared-memory
+// reads and CPT FMAs per thread instead of a whole row per lane.
+template <int R>
+__device__ __forceinline__ void cholesky_inverse_cta(const float* gs, float* ts, float* tT, float* rowbuf,
+                                                     float* colbuf, double* dscale, int tid) {
+  using D = CompactDims<R>;
+  constexpr int TPR = D::TPR, CPT = D::CPT, RP = D::RP;
+  const int i = tid / TPR, q = tid % TPR;
+  const bool active = i < R;
+  const bool diag_owner = active && (i % TPR) == q;
+  float a[CPT];
 #pragma unroll
-  for (int j = 0; j < R; ++j) a[j] = live ? 0.5f * (gs[i * R + j] + gs[j * R + i]) + (i == j ? 1.0f : 0.0f) : 0.f;
-  double diag = live ? 1.0 + (double)gs[i * R + i] : 1.0;
-  cholesky_eliminate<R, 0>(a, diag, rowbuf, i, live);
-  if (live) {
-    const double sc = rsqrt(diag);
+  for (int c = 0; c < CPT; ++c) {
+    const int j = q + TPR * c;
+    a[c] = active ? 0.5f * (gs[i * R + j] + gs[j * R + i]) + (i == j ? 1.0f : 0.0f) : 0.f;
+  }
+  double diag = diag_owner ? 1.0 + (double)gs[i * R + i] : 1.0;
+
+  // publish row k and, from the register `colv` of its owners, column k (below the diagonal) as
+  // they stand after the steps before k
+  auto publish = [&](int k, int buf, float colv) {
+    if (!active) return;
+    if (i == k) {
 #pragma unroll
-    for (int j = 0; j < R; ++j) {
+      for (int c = 0; c < CPT; ++c) rowbuf[buf * (R + 1) + q + TPR * c] = a[c];
+      if (diag_owner) {
+        // reciprocal of the pivot: hardware approximation plus one FP32 Newton step (this value sits
+        // on the dependency chain of every step, the FP64 diagonal keeps the pivot itself accurate)
+        const float df = (float)diag;
+        float r0;
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(df));
+        rowbuf[buf * (R + 1) + R] = fmaf(r0, fmaf(-df, r0, 1.0f), r0);
+      }
+    }
+    if (i > k && q == k % TPR) colbuf[buf * R + i] = colv;
+  };
+  publish(0, 0, a[0]);
+  // step K = cK * TPR + qK; the outer index is unrolled so that every register index is a constant
+#pragma unroll
+  for (int cK = 0; cK < CPT; ++cK) {
+    for (int qK = 0; qK < TPR; ++qK) {
+      const int K = cK * TPR + qK;
+      __syncthreads();
+      const int buf = K & 1;
+      if (active && i > K) {
+        const float* rb = rowbuf + buf * (R + 1);
+        const float f = colbuf[buf * R + i] * rb[R];
+        if (diag_owner) diag = fma(-(double)f, (double)rb[i], diag);
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          const float upd = fmaf(-f, rb[q + TPR * c], a[c]);
+          a[c] = (c == cK && q == qK) ? -f : upd;
+        }
+      }
+      if (K + 1 < R) publish(K + 1, buf ^ 1, (qK + 1 < TPR) ? a[cK] : a[cK + 1 < CPT ? cK + 1 : cK]);
+    }
+  }
+  if (diag_owner) dscale[i] = rsqrt(diag);
+  __syncthreads();
+  if (active) {
+    const double sc = dscale[i];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+      const int j = q + TPR * c;
       float v = 0.f;
-      if (j < i) v = (float)((double)a[j] * sc);
+      if (j < i) v = (float)((double)a[c] * sc);
       else if (j == i) v = (float)sc;
-      ts[i * (R + 1) + j] = v;
+      ts[i * RP + j] = v;
+      tT[j * RP + i] = v;
     }
   }
 }
 
 // ---------------------------------------------------------------------------------------
-// helpers
+// small FP32 products on shared-memory operands, 4 x 2 register tiles
 // ---------------------------------------------------------------------------------------
-// out[i][c] = sum_j lhs(i,j) * rhs[j][c] for i < R, c < 64 (rhs/out pitch 65); jlo/jhi bound
-// the inner index (triangular factors).
-// Each thread owns one column and R/4 interleaved rows: one load of the right-hand side feeds R/4
-// independent FMA chains.  Triangular left factors hold explicit zeros, so the inner index runs
-// over the full range (the bounds jlo/jhi are accepted for documentation only).
-template <int R, class LHS, class LO, class HI>
-__device__ __forceinline__ void small_mm(LHS lhs, LO, HI, const float* rhs, float* out, int tid) {
-  constexpr int ROWS = R / (kCompactThreads / 64);
-  const int c = tid & 63, rg = tid >> 6;
-  float acc[ROWS];
-#pragma unroll
-  for (int k = 0; k < ROWS; ++k) acc[k] = 0.f;
+// acc[r][c] += sum_{k0 <= k < k1} At[k][i0 + r] * B[k][j0 + c]      (both operands k-major)
+__device__ __forceinline__ void mm_tn(float (&acc)[4][2], const float* At, int lda, const float* B, int ldb,
+                                      int i0, int j0, int k0, int k1) {
 #pragma unroll 4
-  for (int j = 0; j < R; ++j) {
-    const float r = rhs[j * 65 + c];
-#pragma unroll
-    for (int k = 0; k < ROWS; ++k) acc[k] = fmaf(lhs(rg + (kCompactThreads / 64) * k, j), r, acc[k]);
-  }
-#pragma unroll
-  for (int k = 0; k < ROWS; ++k) out[(rg + (kCompactThreads / 64) * k) * 65 + c] = acc[k];
-}
-
-// acc[e] = sum over chunks (in chunk order) of src[c*stride + off[e]] for PER entries of this
-// thread; four chunks x PER entries of loads are issued before any of them is consumed.
-template <int PER>
-__device__ __forceinline__ void sum_partials(const float* __restrict__ src, size_t stride, int nch,
-                                             const size_t (&off)[PER], const bool (&ok)[PER], float (&acc)[PER]) {
-#pragma unroll
-  for (int e = 0; e < PER; ++e) acc[e] = 0.f;
-  int c = 0;
-  for (; c + 4 <= nch; c += 4) {
-    float v[4][PER];
-#pragma unroll
-    for (int k = 0; k < 4; ++k)
-#pragma unroll
-      for (int e = 0; e < PER; ++e) v[k][e] = ok[e] ? __ldg(src + (size_t)(c + k) * stride + off[e]) : 0.f;
-#pragma unroll
-    for (int k = 0; k < 4; ++k)
-#pragma unroll
-      for (int e = 0; e < PER; ++e) acc[e] += v[k][e];
-  }
-  for (; c < nch; ++c) {
-    float v[PER];
-#pragma unroll
-    for (int e = 0; e < PER; ++e) v[e] = ok[e] ? __ldg(src + (size_t)c * stride + off[e]) : 0.f;
-#pragma unroll
-    for (int e = 0; e < PER; ++e) acc[e] += v[e];
+  for (int k = k0; k < k1; ++k) {
+    const float4 a = *reinterpret_cast<const float4*>(At + k * lda + i0);
+    const float2 b = *reinterpret_cast<const float2*>(B + k * ldb + j0);
+    acc[0][0] = fmaf(a.x, b.x, acc[0][0]); acc[0][1] = fmaf(a.x, b.y, acc[0][1]);
+    acc[1][0] = fmaf(a.y, b.x, acc[1][0]); acc[1][1] = fmaf(a.y, b.y, acc[1][1]);
+    acc[2][0] = fmaf(a.z, b.x, acc[2][0]); acc[2][1] = fmaf(a.z, b.y, acc[2][1]);
+    acc[3][0] = fmaf(a.w, b.x, acc[3][0]); acc[3][1] = fmaf(a.w, b.y, acc[3][1]);
   }
 }
 
-// Sum, in chunk order, one R x 64 block of a partial r x d matrix (first element at `base`,
-// row pitch d, columns [d0, d0+dv)) with NT cooperating threads (t = 0..NT-1) and write it,
-// scaled, to dst (pitch 65; columns >= dv become zero).
-template <int R, int NT>
-__device__ __forceinline__ void sum_block(const float* __restrict__ src, size_t stride, int nch, size_t base, int d,
-                                          int d0, int dv, float scale, float* dst, int t) {
-  constexpr int PER = (R * 64 + NT - 1) / NT;
-  size_t off[PER];
-  bool ok[PER];
-  float acc[PER];
+// acc[r][c] += sum_{k < K} X[i0 + r][k] * Y[j(c)][k],  j(0) = j0, j(1) = j1   (both operands row-major)
+template <int K>
+__device__ __forceinline__ void mm_nt(float (&acc)[4][2], const float* X, int ldx, const float* Y, int ldy,
+                                      int i0, int j0, int j1) {
+#pragma unroll 2
+  for (int k = 0; k < K; k += 4) {
+    float4 x[4], y[2];
 #pragma unroll
-  for (int e = 0; e < PER; ++e) {
-    const int i = t + e * NT;
-    const int row = i >> 6, c = i & 63;
-    ok[e] = i < R * 64 && c < dv;
-    off[e] = ok[e] ? base + (size_t)row * d + d0 + c : 0;
-  }
-  sum_partials<PER>(src, stride, nch, off, ok, acc);
+    for (int r = 0; r < 4; ++r) x[r] = *reinterpret_cast<const float4*>(X + (i0 + r) * ldx + k);
+    y[0] = *reinterpret_cast<const float4*>(Y + j0 * ldy + k);
+    y[1] = *reinterpret_cast<const float4*>(Y + j1 * ldy + k);
 #pragma unroll
-  for (int e = 0; e < PER; ++e) {
-    const int i = t + e * NT;
-    if (i < R * 64) dst[(i >> 6) * 65 + (i & 63)] = acc[e] * scale;
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        acc[r][c] = fmaf(x[r].x, y[c].x, acc[r][c]);
+        acc[r][c] = fmaf(x[r].y, y[c].y, acc[r][c]);
+        acc[r][c] = fmaf(x[r].z, y[c].z, acc[r][c]);
+        acc[r][c] = fmaf(x[r].w, y[c].w, acc[r][c]);
+      }
   }
 }
 
+__device__ __forceinline__ void zero_tile(float (&acc)[4][2]) {
+#pragma unroll
+  for (int r = 0; r < 4; ++r) acc[r][0] = acc[r][1] = 0.f;
+}
+
+// two adjacent values as (dominant, residual) BF16 words
+__device__ __forceinline__ void store_split2(__nv_bfloat16* hi, __nv_bfloat16* lo, size_t idx, float v0, float v1) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+  *reinterpret_cast<__nv_bfloat162*>(hi + idx) = h;
+  *reinterpret_cast<__nv_bfloat162*>(lo + idx) =
+      __floats2bfloat162_rn(v0 - __low2float(h), v1 - __high2float(h));
+}
 __device__ __forceinline__ void store_split(__nv_bfloat16* hi, __nv_bfloat16* lo, size_t idx, float v) {
   const __nv_bfloat16 hv = __float2bfloat16_rn(v);
   hi[idx] = hv;
   lo[idx] = __float2bfloat16_rn(v - __bfloat162float(hv));
 }
 
-// r x r products spread over the CTA: thread t owns entries t, t+256, ... (kRRPer<R> of them) and
-// advances all of their dot products together, so the FMA chains are independent.
-template <int R>
-constexpr int kRRPer = (R * R + kCompactThreads - 1) / kCompactThreads;
-
-template <int R, class INIT>
-__device__ __forceinline__ void rr_init(float (&acc)[kRRPer<R>], INIT init, int tid) {
-#pragma unroll
-  for (int e = 0; e < kRRPer<R>; ++e) {
-    const int i = tid + e * kCompactThreads;
-    acc[e] = i < R * R ? init(i / R, i % R) : 0.f;
+// ---------------------------------------------------------------------------------------
+// staging of the partial sums
+// ---------------------------------------------------------------------------------------
+// One thread copies `chunks` partials of `floats` floats each (contiguous in global memory) into
+// shared memory with bulk asynchronous copies on one mbarrier; the CTA then adds them in chunk
+// order from shared memory.  The copy needs 16-byte aligned addresses and sizes; the launcher
+// checks that and the size, and otherwise the kernel adds the partials straight from global
+// memory.
+__device__ __forceinline__ void stage_partials(uint32_t dst, const float* src, int chunks, int stride_floats,
+                                               int first, int floats, uint32_t bar) {
+  mbar_expect_tx(bar, (uint32_t)chunks * (uint32_t)floats * 4u);
+  for (int c = 0; c < chunks; ++c) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst + ((uint32_t)c * (uint32_t)stride_floats + (uint32_t)first) * 4u),
+                   "l"(reinterpret_cast<uint64_t>(src + (size_t)c * stride_floats + first)),
+                   "r"((uint32_t)floats * 4u), "r"(bar)
+                 : "memory");
   }
 }
 
-// acc[e] += sum_k fa(row_e, k) * fb(k, col_e)
-template <int R, int KLEN, class FA, class FB>
-__device__ __forceinline__ void rr_accumulate(float (&acc)[kRRPer<R>], FA fa, FB fb, int tid) {
-  int row[kRRPer<R>], col[kRRPer<R>];
+// out[e] = sum over chunks, in chunk order, of src[c * stride + off[e]] for four entries at a time
+// (independent chains); entries with ok[e] false stay zero
+template <class PTR>
+__device__ __forceinline__ void sum_chunks4(PTR src, size_t stride, int nch, const int (&off)[4], const bool (&ok)[4],
+                                            float (&acc)[4]) {
 #pragma unroll
-  for (int e = 0; e < kRRPer<R>; ++e) {
-    const int i = min(tid + e * kCompactThreads, R * R - 1);
-    row[e] = i / R;
-    col[e] = i % R;
+  for (int e = 0; e < 4; ++e) acc[e] = 0.f;
+  int c = 0;
+  for (; c + 2 <= nch; c += 2) {
+    float v[2][4];
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[k][e] = ok[e] ? src[(size_t)(c + k) * stride + off[e]] : 0.f;
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[e] += v[k][e];
   }
+  for (; c < nch; ++c) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[e] += ok[e] ? src[(size_t)c * stride + off[e]] : 0.f;
+  }
+}
+
+// acc[r][c] += sum_{k0 <= k < k1} At[k][i0 + r] * B[k][j(c)],  j(0) = j0, j(1) = j1
+__device__ __forceinline__ void mm_tn_s(float (&acc)[4][2], const float* At, int lda, const float* B, int ldb,
+                                        int i0, int j0, int j1, int k0, int k1) {
 #pragma unroll 4
-  for (int k = 0; k < KLEN; ++k) {
-#pragma unroll
-    for (int e = 0; e < kRRPer<R>; ++e) acc[e] = fmaf(fa(row[e], k), fb(k, col[e]), acc[e]);
-  }
-}
-
-template <int R, class STORE>
-__device__ __forceinline__ void rr_store(const float (&acc)[kRRPer<R>], STORE store, int tid) {
-#pragma unroll
-  for (int e = 0; e < kRRPer<R>; ++e) {
-    const int i = tid + e * kCompactThreads;
-    if (i < R * R) store(i / R, i % R, i, acc[e]);
+  for (int k = k0; k < k1; ++k) {
+    const float4 a = *reinterpret_cast<const float4*>(At + k * lda + i0);
+    const float b0 = B[k * ldb + j0], b1 = B[k * ldb + j1];
+    acc[0][0] = fmaf(a.x, b0, acc[0][0]); acc[0][1] = fmaf(a.x, b1, acc[0][1]);
+    acc[1][0] = fmaf(a.y, b0, acc[1][0]); acc[1][1] = fmaf(a.y, b1, acc[1][1]);
+    acc[2][0] = fmaf(a.z, b0, acc[2][0]); acc[2][1] = fmaf(a.z, b1, acc[2][1]);
+    acc[3][0] = fmaf(a.w, b0, acc[3][0]); acc[3][1] = fmaf(a.w, b1, acc[3][1]);
   }
 }
 
@@ -218,19 +243,35 @@ struct CompactFwdParams {
   float* inverse;
   float* state;
   __nv_bfloat16* coeff;
+  int* error;
   int heads, tokens, head_dim, dpad, dblocks, chunks, pf, complement;
+  int staged;     // the partials of one system fit the staging area and are 16-byte aligned
+  int pair_ok;    // the BF16 outputs are 4-byte aligned (paired stores)
 };
+
+// floats of shared memory before the staging area
+template <int R>
+constexpr int compact_fwd_fixed_floats() {
+  return R * R + 3 * R * CompactDims<R>::RP + 2 * R * kQP + 2 * (R + 4) + 2 * R + 2 * R + 4;
+}
 
 template <int R>
 __global__ void __launch_bounds__(kCompactThreads)
 compact_forward_kernel(const CompactFwdParams p) {
-  extern __shared__ float fsm[];
-  float* gs = fsm;                      // R*R            G
-  float* ts = gs + R * R;               // R*(R+1)        T
-  float* ms_ = ts + R * (R + 1);        // R*(R+1)        F - eta I
-  float* qs = ms_ + R * (R + 1);        // R*65           Q block -> scratch
-  float* mid = qs + R * 65;             // R*65
-  float* rowbuf = mid + R * 65;         // 2*R floats (pivot-row broadcast, double buffered)
+  using D = CompactDims<R>;
+  constexpr int RP = D::RP;
+  extern __shared__ __align__(16) unsigned char csm[];
+  float* gs = reinterpret_cast<float*>(csm);   // R*R      G
+  float* ts = gs + R * R;                      // R*RP     T
+  float* tT = ts + R * RP;                     // R*RP     T^T
+  float* mT = tT + R * RP;                     // R*RP     (F - eta I)^T
+  float* qs = mT + R * RP;                     // R*kQP    Q block -> scratch
+  float* mid = qs + R * kQP;                   // R*kQP
+  float* rowbuf = mid + R * kQP;               // 2*(R+4)  pivot rows (double buffered)
+  float* colbuf = rowbuf + 2 * (R + 4);        // 2*R      pivot columns
+  double* dscale = reinterpret_cast<double*>(colbuf + 2 * R);   // R
+  uint64_t* bar = reinterpret_cast<uint64_t*>(dscale + R);      // 2 words
+  float* stage = reinterpret_cast<float*>(bar + 2);             // chunks * pf when staged
 
   const int tid = threadIdx.x;
   const int sys = blockIdx.x;
@@ -243,85 +284,136 @@ compact_forward_kernel(const CompactFwdParams p) {
   const float* src = p.partials + (size_t)sys * nch * p.pf;
   const float eta = p.eta[h];
   const int d = p.head_dim;
+  const bool staged = p.staged != 0;
   MS_TICK(0);
 
-  {
-    constexpr int PER = (R * R + kCompactThreads - 1) / kCompactThreads;
-    size_t off[PER];
-    bool ok[PER];
-    float acc[PER];
-#pragma unroll
-    for (int e = 0; e < PER; ++e) {
-      const int i = tid + e * kCompactThreads;
-      ok[e] = i < R * R;
-      off[e] = ok[e] ? i : 0;
+  if (staged) {
+    const uint32_t bar_addr = smem_u32(bar);
+    if (tid == 0) {
+      mbar_init(bar_addr, 1);
+      mbar_init(bar_addr + 8, 1);
+      mbar_fence_init();
     }
-    sum_partials<PER>(src, p.pf, nch, off, ok, acc);
-#pragma unroll
-    for (int e = 0; e < PER; ++e) {
-      const int i = tid + e * kCompactThreads;
-      if (i < R * R) {
-        gs[i] = acc[e] * inv_n;
-        const int row = i / R, col = i - row * R;
-        float f = p.complement ? 0.f : p.core_map[(size_t)h * R * R + i];
-        if (row == col) f -= eta;
-        ms_[row * (R + 1) + col] = f;
-      }
+    __syncthreads();
+    if (tid == 0) {
+      // Gram partials first (their own barrier): the factorisation starts while the moments land
+      stage_partials(smem_u32(stage), src, nch, p.pf, 0, R * R, bar_addr);
+      stage_partials(smem_u32(stage), src, nch, p.pf, R * R, p.pf - R * R, bar_addr + 8);
     }
+  }
+  for (int i = tid; i < R * R; i += kCompactThreads) {
+    const int row = i / R, col = i - row * R;
+    float f = p.complement ? 0.f : p.core_map[(size_t)h * R * R + i];
+    if (row == col) f -= eta;
+    mT[col * RP + row] = f;
+  }
+  bool ok = true;
+  if (staged) ok = mbar_wait(smem_u32(bar), 0);
+  for (int i0 = tid; i0 < R * R; i0 += 4 * kCompactThreads) {
+    int off[4];
+    bool valid[4];
+    float acc[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      off[e] = i0 + e * kCompactThreads;
+      valid[e] = off[e] < R * R;
+    }
+    if (staged) sum_chunks4(stage, (size_t)p.pf, nch, off, valid, acc);
+    else sum_chunks4(src, (size_t)p.pf, nch, off, valid, acc);
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (valid[e]) gs[off[e]] = acc[e] * inv_n;
   }
   __syncthreads();
   MS_TICK(1);
-  // the factorisation occupies the first warp(s); the other warps meanwhile sum the partial
-  // moments of the first channel block
-  constexpr int CHOL_THREADS = ((R + 31) / 32) * 32;
-  if (tid < CHOL_THREADS) {
-    cholesky_inverse_rows<R>(gs, ts, rowbuf, tid);
-  } else {
-    sum_block<R, kCompactThreads - CHOL_THREADS>(src, p.pf, nch, (size_t)R * R, d, 0, min(64, d), inv_s, qs,
-                                                  tid - CHOL_THREADS);
-  }
+  cholesky_inverse_cta<R>(gs, ts, tT, rowbuf, colbuf, dscale, tid);
   __syncthreads();
   MS_TICK(2);
   for (int i = tid; i < R * R; i += kCompactThreads) {
     const int row = i / R, col = i - row * R;
-    p.inverse[(size_t)sys * R * R + i] = ts[row * (R + 1) + col];
+    p.inverse[(size_t)sys * R * R + i] = ts[row * RP + col];
   }
 
+  constexpr int TILES = (R / 4) * 32;   // 4 x 2 tiles of an r x 64 block
   for (int jb = 0; jb < p.dblocks; ++jb) {
     const int d0 = jb * 64, dv = min(64, d - d0);
-    if (jb > 0) {
-      sum_block<R, kCompactThreads>(src, p.pf, nch, (size_t)R * R, d, d0, dv, inv_s, qs, tid);
-      __syncthreads();
+    if (staged && jb == 0) ok = mbar_wait(smem_u32(bar) + 8, 0) && ok;
+    for (int i0 = tid; i0 < R * 64; i0 += 4 * kCompactThreads) {
+      int off[4];
+      bool valid[4];
+      float acc[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = i0 + e * kCompactThreads, row = i >> 6, c = i & 63;
+        valid[e] = c < dv;
+        off[e] = R * R + row * d + d0 + (valid[e] ? c : 0);
+      }
+      if (staged) sum_chunks4(stage, (size_t)p.pf, nch, off, valid, acc);
+      else sum_chunks4(src, (size_t)p.pf, nch, off, valid, acc);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = i0 + e * kCompactThreads;
+        qs[(i >> 6) * kQP + (i & 63)] = acc[e] * inv_s;
+      }
     }
+    __syncthreads();
     MS_TICK(3);
-    // Z = T Q   (T lower triangular)
-    small_mm<R>([&](int i, int j) { return ts[i * (R + 1) + j]; }, [](int) { return 0; },
-                [](int i) { return i + 1; }, qs, mid, tid);
+    // Z = T Q   (T lower triangular: the inner index stops at the row)
+    for (int tile = tid; tile < TILES; tile += kCompactThreads) {
+      const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
+      float acc[4][2];
+      zero_tile(acc);
+      mm_tn(acc, tT, RP, qs, kQP, i0, j0, 0, i0 + 4);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        *reinterpret_cast<float2*>(mid + (i0 + r) * kQP + j0) = make_float2(acc[r][0], acc[r][1]);
+        float* st = p.state + ((size_t)sys * R + i0 + r) * d + d0 + j0;
+        if (j0 < dv) st[0] = acc[r][0];
+        if (j0 + 1 < dv) st[1] = acc[r][1];
+      }
+    }
     __syncthreads();
     MS_TICK(4);
-    for (int i = tid; i < R * 64; i += kCompactThreads) {
-      const int row = i >> 6, c = i & 63;
-      if (c < dv) p.state[((size_t)sys * R + row) * d + d0 + c] = mid[row * 65 + c];
-    }
     // (F - eta I) Z -> qs
-    small_mm<R>([&](int i, int j) { return ms_[i * (R + 1) + j]; }, [](int) { return 0; },
-                [](int) { return R; }, mid, qs, tid);
+    for (int tile = tid; tile < TILES; tile += kCompactThreads) {
+      const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
+      float acc[4][2];
+      zero_tile(acc);
+      mm_tn(acc, mT, RP, mid, kQP, i0, j0, 0, R);
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+        *reinterpret_cast<float2*>(qs + (i0 + r) * kQP + j0) = make_float2(acc[r][0], acc[r][1]);
+    }
     __syncthreads();
-    // W = T^T (F - eta I) Z -> mid
-    small_mm<R>([&](int i, int j) { return ts[j * (R + 1) + i]; }, [](int i) { return i; },
-                [](int) { return R; }, qs, mid, tid);
-    __syncthreads();
-    MS_TICK(5);
+    MS_TICK(7);
+    // W = T^T (F - eta I) Z   (the inner index starts at the row), two BF16 words
     __nv_bfloat16* hi = p.coeff + (size_t)sys * 2 * R * p.dpad;
     __nv_bfloat16* lo = hi + (size_t)R * p.dpad;
     const int cend = min(64, p.dpad - d0);
-    for (int i = tid; i < R * 64; i += kCompactThreads) {
-      const int row = i >> 6, c = i & 63;
-      if (c < cend) store_split(hi, lo, (size_t)row * p.dpad + d0 + c, c < dv ? mid[row * 65 + c] : 0.f);
+    for (int tile = tid; tile < TILES; tile += kCompactThreads) {
+      const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
+      float acc[4][2];
+      zero_tile(acc);
+      mm_tn(acc, ts, RP, qs, kQP, i0, j0, i0, R);
+      if (j0 < cend) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const size_t idx = (size_t)(i0 + r) * p.dpad + d0 + j0;
+          const float v0 = j0 < dv ? acc[r][0] : 0.f, v1 = j0 + 1 < dv ? acc[r][1] : 0.f;
+          if (p.pair_ok) {
+            store_split2(hi, lo, idx, v0, v1);
+          } else {
+            store_split(hi, lo, idx, v0);
+            store_split(hi, lo, idx + 1, v1);
+          }
+        }
+      }
     }
     __syncthreads();
-    MS_TICK(6);
+    MS_TICK(5);
   }
+  MS_TICK(6);
+  if (!ok && tid == 0) atomicExch(p.error, kErrBarrierTimeout);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -329,7 +421,7 @@ compact_forward_kernel(const CompactFwdParams p) {
 // ---------------------------------------------------------------------------------------
 struct CompactBwdParams {
   const float* partials;     // E partials [systems][chunks][r*d] or packed when chunks == 0
-  const float* de_partials;  // [systems][chunks*dblocks]; unused when packed
+  const float* de_partials;  // [systems][chunks*de_slots]; unused when packed
   const float* counts;
   const float* eta;
   const float* core_map;
@@ -339,20 +431,32 @@ struct CompactBwdParams {
   float* de_sys;             // [systems]
   __nv_bfloat16* gram_grad;  // [systems][2][r][r]
   __nv_bfloat16* cross_grad; // [systems][2][r][dpad]
-  int heads, tokens, head_dim, dpad, dblocks, chunks, pf, complement, systems;
+  int* error;
+  int heads, tokens, head_dim, dpad, dblocks, chunks, pf, complement, systems, de_slots;
+  int staged, pair_ok;
 };
+
+template <int R>
+constexpr int compact_bwd_fixed_floats() {
+  return 5 * R * CompactDims<R>::RP + 3 * R * kQP + 4;
+}
 
 template <int R>
 __global__ void __launch_bounds__(kCompactThreads)
 compact_backward_kernel(const CompactBwdParams p) {
-  extern __shared__ float fsm[];
-  constexpr int P = R + 1;
-  float* ts = fsm;             // T
-  float* mm = ts + R * P;      // M = F - eta I
-  float* hm = mm + R * P;      // H accumulator
-  float* es = hm + R * P;      // E block / scratch, R*65
-  float* us = es + R * 65;     // U block
-  float* zs = us + R * 65;     // Z block / scratch
+  using D = CompactDims<R>;
+  constexpr int RP = D::RP;
+  extern __shared__ __align__(16) unsigned char csm[];
+  float* ts = reinterpret_cast<float*>(csm);   // T
+  float* tT = ts + R * RP;                     // T^T
+  float* mm = tT + R * RP;                     // M = F - eta I
+  float* mT = mm + R * RP;                     // M^T
+  float* hm = mT + R * RP;                     // H
+  float* es = hm + R * RP;                     // E block / dZ / sym(X)
+  float* us = es + R * kQP;                    // U block / Y
+  float* zs = us + R * kQP;                    // Z block
+  uint64_t* bar = reinterpret_cast<uint64_t*>(zs + R * kQP);
+  float* stage = reinterpret_cast<float*>(bar + 2);
 
   const int tid = threadIdx.x;
   const int sys = blockIdx.x;
@@ -364,15 +468,27 @@ compact_backward_kernel(const CompactBwdParams p) {
   const float* src = p.partials + (size_t)sys * nch * p.pf;
   const float eta = p.eta[h];
   const int d = p.head_dim;
+  const bool staged = p.staged != 0;
   MS_TICK(9);
 
+  if (staged) {
+    const uint32_t bar_addr = smem_u32(bar);
+    if (tid == 0) {
+      mbar_init(bar_addr, 1);
+      mbar_fence_init();
+    }
+    __syncthreads();
+    if (tid == 0) stage_partials(smem_u32(stage), src, nch, p.pf, 0, p.pf, bar_addr);
+  }
   for (int i = tid; i < R * R; i += kCompactThreads) {
     const int row = i / R, col = i - row * R;
-    ts[row * P + col] = p.inverse[(size_t)sys * R * R + i];
+    const float t = p.inverse[(size_t)sys * R * R + i];
+    ts[row * RP + col] = t;
+    tT[col * RP + row] = t;
     float f = p.complement ? 0.f : p.core_map[(size_t)h * R * R + i];
     if (row == col) f -= eta;
-    mm[row * P + col] = f;
-    hm[row * P + col] = 0.f;
+    mm[row * RP + col] = f;
+    mT[col * RP + row] = f;
   }
   if (tid < 32) {
     // <dY, C> of this system: lane-strided sums in index order, then a shuffle tree
@@ -380,116 +496,175 @@ compact_backward_kernel(const CompactBwdParams p) {
     if (packed) {
       if (tid == 0) v = p.partials[(size_t)p.systems * p.pf + sys];
     } else {
-      const int cnt = p.chunks * p.dblocks;
+      const int cnt = p.chunks * p.de_slots;
       for (int c = tid; c < cnt; c += 32) v += p.de_partials[(size_t)sys * cnt + c];
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     if (tid == 0) p.de_sys[sys] = v;
   }
-  __syncthreads();
-
+  bool ok = true;
+  if (staged) ok = mbar_wait(smem_u32(bar), 0);
   MS_TICK(10);
+
+  constexpr int TILES = (R / 4) * 32;          // 4 x 2 tiles of an r x 64 block
+  constexpr int RTILES = (R / 4) * (R / 2);    // 4 x 2 tiles of an r x r matrix, columns j and j + r/2
+  constexpr int RT_PER = (RTILES + kCompactThreads - 1) / kCompactThreads;
+  float hacc[RT_PER][4][2];                    // H = sum over channel blocks of U Z^T, kept in registers
+#pragma unroll
+  for (int e = 0; e < RT_PER; ++e) zero_tile(hacc[e]);
+
   for (int jb = 0; jb < p.dblocks; ++jb) {
     const int d0 = jb * 64, dv = min(64, d - d0);
-    {
-      constexpr int PER = R * 64 / kCompactThreads;
-      size_t off[PER];
-      bool ok[PER];
-      float acc[PER];
+    for (int i0 = tid; i0 < R * 64; i0 += 4 * kCompactThreads) {
+      int off[4];
+      bool valid[4];
+      float acc[4], zv[4];
 #pragma unroll
-      for (int e = 0; e < PER; ++e) {
-        const int i = tid + e * kCompactThreads;
-        const int row = i >> 6, c = i & 63;
-        ok[e] = c < dv;
-        off[e] = (size_t)row * d + d0 + (ok[e] ? c : 0);
+      for (int e = 0; e < 4; ++e) {
+        const int i = i0 + e * kCompactThreads, row = i >> 6, c = i & 63;
+        valid[e] = c < dv;
+        off[e] = row * d + d0 + (valid[e] ? c : 0);
+        zv[e] = valid[e] ? p.state[(size_t)sys * R * d + off[e]] : 0.f;
       }
-      sum_partials<PER>(src, p.pf, nch, off, ok, acc);
+      if (staged) sum_chunks4(stage, (size_t)p.pf, nch, off, valid, acc);
+      else sum_chunks4(src, (size_t)p.pf, nch, off, valid, acc);
 #pragma unroll
-      for (int e = 0; e < PER; ++e) {
-        const int i = tid + e * kCompactThreads;
-        const int row = i >> 6, c = i & 63;
-        es[row * 65 + c] = acc[e] * inv_s;
-        zs[row * 65 + c] = ok[e] ? p.state[(size_t)sys * R * d + off[e]] : 0.f;
+      for (int e = 0; e < 4; ++e) {
+        const int i = i0 + e * kCompactThreads;
+        es[(i >> 6) * kQP + (i & 63)] = acc[e] * inv_s;
+        zs[(i >> 6) * kQP + (i & 63)] = zv[e];
       }
     }
     __syncthreads();
     MS_TICK(11);
     // U = T E
-    small_mm<R>([&](int i, int j) { return ts[i * P + j]; }, [](int) { return 0; },
-                [](int i) { return i + 1; }, es, us, tid);
+    for (int tile = tid; tile < TILES; tile += kCompactThreads) {
+      const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
+      float acc[4][2];
+      zero_tile(acc);
+      mm_tn(acc, tT, RP, es, kQP, i0, j0, 0, i0 + 4);
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+        *reinterpret_cast<float2*>(us + (i0 + r) * kQP + j0) = make_float2(acc[r][0], acc[r][1]);
+    }
     __syncthreads();
     MS_TICK(12);
     // H += U Z^T   (r x r, contraction over the 64 channels)
-    {
-      float acc[kRRPer<R>];
-      rr_init<R>(acc, [&](int row, int col) { return hm[row * P + col]; }, tid);
-      rr_accumulate<R, 64>(acc, [&](int row, int c) { return us[row * 65 + c]; },
-                           [&](int c, int col) { return zs[col * 65 + c]; }, tid);
-      rr_store<R>(acc, [&](int row, int col, int, float v) { hm[row * P + col] = v; }, tid);
+#pragma unroll
+    for (int e = 0; e < RT_PER; ++e) {
+      const int tile = tid + e * kCompactThreads;
+      if (tile < RTILES) {
+        const int i0 = (tile / (R / 2)) * 4, j0 = tile % (R / 2);
+        mm_nt<64>(hacc[e], us, kQP, zs, kQP, i0, j0, j0 + R / 2);
+      }
     }
     MS_TICK(13);
     // dZ = M^T U -> es
-    small_mm<R>([&](int i, int j) { return mm[j * P + i]; }, [](int) { return 0; },
-                [](int) { return R; }, us, es, tid);
+    for (int tile = tid; tile < TILES; tile += kCompactThreads) {
+      const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
+      float acc[4][2];
+      zero_tile(acc);
+      mm_tn(acc, mm, RP, us, kQP, i0, j0, 0, R);
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+        *reinterpret_cast<float2*>(es + (i0 + r) * kQP + j0) = make_float2(acc[r][0], acc[r][1]);
+    }
     __syncthreads();
     MS_TICK(14);
-    // dQ = T^T dZ -> zs
-    small_mm<R>([&](int i, int j) { return ts[j * P + i]; }, [](int i) { return i; },
-                [](int) { return R; }, es, zs, tid);
-    __syncthreads();
+    // dQ = T^T dZ, two BF16 words
     __nv_bfloat16* hi = p.cross_grad + (size_t)sys * 2 * R * p.dpad;
     __nv_bfloat16* lo = hi + (size_t)R * p.dpad;
     const int cend = min(64, p.dpad - d0);
-    for (int i = tid; i < R * 64; i += kCompactThreads) {
-      const int row = i >> 6, c = i & 63;
-      if (c < cend) store_split(hi, lo, (size_t)row * p.dpad + d0 + c, c < dv ? zs[row * 65 + c] : 0.f);
+    for (int tile = tid; tile < TILES; tile += kCompactThreads) {
+      const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
+      float acc[4][2];
+      zero_tile(acc);
+      mm_tn(acc, ts, RP, es, kQP, i0, j0, i0, R);
+      if (j0 < cend) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const size_t idx = (size_t)(i0 + r) * p.dpad + d0 + j0;
+          const float v0 = j0 < dv ? acc[r][0] : 0.f, v1 = j0 + 1 < dv ? acc[r][1] : 0.f;
+          if (p.pair_ok) {
+            store_split2(hi, lo, idx, v0, v1);
+          } else {
+            store_split(hi, lo, idx, v0);
+            store_split(hi, lo, idx + 1, v1);
+          }
+        }
+      }
     }
     __syncthreads();
   }
 
   MS_TICK(16);
-  // H to global for the per-head sum; X = -M H^T - M^T H
-  float* xs = es;   // R*P fits in R*65
+  // H to shared memory and to global (for the per-head sum over the batch)
+#pragma unroll
+  for (int e = 0; e < RT_PER; ++e) {
+    const int tile = tid + e * kCompactThreads;
+    if (tile < RTILES) {
+      const int i0 = (tile / (R / 2)) * 4, j0 = tile % (R / 2), j1 = j0 + R / 2;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        hm[(i0 + r) * RP + j0] = hacc[e][r][0];
+        hm[(i0 + r) * RP + j1] = hacc[e][r][1];
+        p.hmat[(size_t)sys * R * R + (i0 + r) * R + j0] = hacc[e][r][0];
+        p.hmat[(size_t)sys * R * R + (i0 + r) * R + j1] = hacc[e][r][1];
+      }
+    }
+  }
+  __syncthreads();
+  // X = -M H^T - M^T H;  sym = low + low^T with low = tril(X,-1)/2 + diag(X)/4, i.e.
+  // sym[r][k] = X[max(r,k)][min(r,k)] / 2, written to both triangles from the lower one
+  float* sym = es;
   float* ys = us;
-  {
-    float acc[kRRPer<R>];
-    rr_init<R>(acc, [&](int, int) { return 0.f; }, tid);
-    rr_accumulate<R, R>(acc, [&](int row, int k) { return -mm[row * P + k]; },
-                        [&](int k, int col) { return hm[col * P + k]; }, tid);
-    rr_accumulate<R, R>(acc, [&](int row, int k) { return -mm[k * P + row]; },
-                        [&](int k, int col) { return hm[k * P + col]; }, tid);
-    rr_store<R>(acc, [&](int row, int col, int i, float v) {
-      p.hmat[(size_t)sys * R * R + i] = hm[row * P + col];
-      xs[row * P + col] = v;
-    }, tid);
+  for (int tile = tid; tile < RTILES; tile += kCompactThreads) {
+    const int i0 = (tile / (R / 2)) * 4, j0 = tile % (R / 2), j1 = j0 + R / 2;
+    float acc[4][2];
+    zero_tile(acc);
+    mm_nt<R>(acc, mm, RP, hm, RP, i0, j0, j1);
+    mm_tn_s(acc, mm, RP, hm, RP, i0, j0, j1, 0, R);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int i = i0 + r;
+      if (i >= j0) sym[i * RP + j0] = sym[j0 * RP + i] = -0.5f * acc[r][0];
+      if (i >= j1) sym[i * RP + j1] = sym[j1 * RP + i] = -0.5f * acc[r][1];
+    }
   }
   __syncthreads();
   MS_TICK(17);
-  // sym = low + low^T with low = tril(X,-1)/2 + diag(X)/4, i.e. sym[r][k] = X[max(r,k)][min(r,k)]/2;
-  // Y = sym T  (T lower triangular with explicit zeros above the diagonal)
-  {
-    float acc[kRRPer<R>];
-    rr_init<R>(acc, [&](int, int) { return 0.f; }, tid);
-    rr_accumulate<R, R>(acc, [&](int row, int k) { return 0.5f * (row >= k ? xs[row * P + k] : xs[k * P + row]); },
-                        [&](int k, int col) { return ts[k * P + col]; }, tid);
-    rr_store<R>(acc, [&](int row, int col, int, float v) { ys[row * P + col] = v; }, tid);
+  // Y = sym T  (T lower triangular: row k of T is zero beyond column k)
+  for (int tile = tid; tile < RTILES; tile += kCompactThreads) {
+    const int i0 = (tile / (R / 2)) * 4, j0 = tile % (R / 2), j1 = j0 + R / 2;
+    float acc[4][2];
+    zero_tile(acc);
+    mm_tn_s(acc, sym, RP, ts, RP, i0, j0, j1, j0, R);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      ys[(i0 + r) * RP + j0] = acc[r][0];
+      ys[(i0 + r) * RP + j1] = acc[r][1];
+    }
   }
   __syncthreads();
   MS_TICK(18);
   // dG = T^T Y ;  stored as dG + dG^T (dG is symmetric) in two BF16 words
   __nv_bfloat16* ghi = p.gram_grad + (size_t)sys * 2 * R * R;
   __nv_bfloat16* glo = ghi + R * R;
-  {
-    float acc[kRRPer<R>];
-    rr_init<R>(acc, [&](int, int) { return 0.f; }, tid);
-    rr_accumulate<R, R>(acc, [&](int row, int k) { return ts[k * P + row]; },
-                        [&](int k, int col) { return ys[k * P + col]; }, tid);
-    rr_accumulate<R, R>(acc, [&](int row, int k) { return ys[k * P + row]; },
-                        [&](int k, int col) { return ts[k * P + col]; }, tid);
-    rr_store<R>(acc, [&](int, int, int i, float v) { store_split(ghi, glo, i, v); }, tid);
+  for (int tile = tid; tile < RTILES; tile += kCompactThreads) {
+    const int i0 = (tile / (R / 2)) * 4, j0 = tile % (R / 2), j1 = j0 + R / 2;
+    float acc[4][2];
+    zero_tile(acc);
+    mm_tn_s(acc, ts, RP, ys, RP, i0, j0, j1, i0, R);
+    mm_tn_s(acc, ys, RP, ts, RP, i0, j0, j1, j0, R);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      store_split(ghi, glo, (size_t)(i0 + r) * R + j0, acc[r][0]);
+      store_split(ghi, glo, (size_t)(i0 + r) * R + j1, acc[r][1]);
+    }
   }
   MS_TICK(19);
+  if (!ok && tid == 0) atomicExch(p.error, kErrBarrierTimeout);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -549,9 +724,23 @@ int launch_core_forward(const ms_shape& s, const float* base_raw, const float* e
   return MS_ERR_UNSUPPORTED_RANK;
 }
 
+constexpr size_t kCompactSmemLimit = 227 * 1024;
+
+// bytes of the staging area for `chunks` partials of `floats` floats, or 0 when they do not fit
+// beside `fixed_floats` or the source is not 16-byte aligned
+static size_t staging_bytes(const float* partials, int chunks, size_t floats, size_t fixed_floats) {
+  const size_t need = (size_t)chunks * floats * sizeof(float);
+  if ((reinterpret_cast<uintptr_t>(partials) & 15u) != 0 || (floats & 3u) != 0) return 0;
+  if (need >= (1u << 20)) return 0;   // one mbarrier phase counts less than 2^20 bytes
+  return fixed_floats * sizeof(float) + need <= kCompactSmemLimit ? need : 0;
+}
+
 template <int R>
-static int launch_compact_fwd_r(const CompactFwdParams& p, int systems, cudaStream_t st) {
-  const size_t bytes = (R * R + 2 * R * (R + 1) + 2 * R * 65) * sizeof(float) + 2 * R * sizeof(double) + 16;
+static int launch_compact_fwd_r(CompactFwdParams& p, int systems, cudaStream_t st) {
+  const size_t fixed = compact_fwd_fixed_floats<R>();
+  const size_t stage = staging_bytes(p.partials, p.chunks == 0 ? 1 : p.chunks, (size_t)p.pf, fixed);
+  p.staged = stage != 0;
+  const size_t bytes = fixed * sizeof(float) + stage;
   if (set_smem(compact_forward_kernel<R>, bytes)) return MS_ERR_LAUNCH;
   compact_forward_kernel<R><<<systems, kCompactThreads, bytes, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
@@ -562,9 +751,13 @@ int launch_compact_forward(const ms_shape& s, const Plan& plan, const float* cou
   CompactFwdParams p;
   p.partials = partials; p.counts = counts; p.eta = t.eta; p.core_map = t.core_map;
   p.inverse = t.inverse; p.state = t.state; p.coeff = static_cast<__nv_bfloat16*>(t.coeff);
+  p.error = device_error_word();
+  if (!p.error) return MS_ERR_LAUNCH;
   p.heads = s.heads; p.tokens = s.tokens; p.head_dim = s.head_dim; p.dpad = plan.dpad;
   p.dblocks = plan.dblocks; p.chunks = packed ? 0 : plan.chunks; p.pf = (int)plan.fwd_partial_floats;
   p.complement = s.complement;
+  p.staged = 0;
+  p.pair_ok = (reinterpret_cast<uintptr_t>(t.coeff) & 3u) == 0;
   switch (s.rank) {
     case 16: return launch_compact_fwd_r<16>(p, plan.systems, st);
     case 32: return launch_compact_fwd_r<32>(p, plan.systems, st);
@@ -575,8 +768,11 @@ int launch_compact_forward(const ms_shape& s, const Plan& plan, const float* cou
 }
 
 template <int R>
-static int launch_compact_bwd_r(const CompactBwdParams& p, int systems, cudaStream_t st) {
-  const size_t bytes = (3 * R * (R + 1) + 3 * R * 65) * sizeof(float);
+static int launch_compact_bwd_r(CompactBwdParams& p, int systems, cudaStream_t st) {
+  const size_t fixed = compact_bwd_fixed_floats<R>();
+  const size_t stage = staging_bytes(p.partials, p.chunks == 0 ? 1 : p.chunks, (size_t)p.pf, fixed);
+  p.staged = stage != 0;
+  const size_t bytes = fixed * sizeof(float) + stage;
   if (set_smem(compact_backward_kernel<R>, bytes)) return MS_ERR_LAUNCH;
   compact_backward_kernel<R><<<systems, kCompactThreads, bytes, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
@@ -590,9 +786,14 @@ int launch_compact_backward(const ms_shape& s, const Plan& plan, const float* co
   p.core_map = t.core_map; p.inverse = t.inverse; p.state = t.state; p.hmat = hmat; p.de_sys = de_sys;
   p.gram_grad = static_cast<__nv_bfloat16*>(gram_grad);
   p.cross_grad = static_cast<__nv_bfloat16*>(cross_grad);
+  p.error = device_error_word();
+  if (!p.error) return MS_ERR_LAUNCH;
   p.heads = s.heads; p.tokens = s.tokens; p.head_dim = s.head_dim; p.dpad = plan.dpad;
   p.dblocks = plan.dblocks; p.chunks = packed ? 0 : plan.chunks; p.pf = (int)plan.bwd_partial_floats;
+  p.de_slots = plan.de_slots;
   p.complement = s.complement; p.systems = plan.systems;
+  p.staged = 0;
+  p.pair_ok = (reinterpret_cast<uintptr_t>(cross_grad) & 3u) == 0;
   switch (s.rank) {
     case 16: return launch_compact_bwd_r<16>(p, plan.systems, st);
     case 32: return launch_compact_bwd_r<32>(p, plan.systems, st);

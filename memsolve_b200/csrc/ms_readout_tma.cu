@@ -17,17 +17,21 @@
 
 namespace ms {
 
-constexpr int kRtWarps = 8;
-constexpr int kRtWBudget = 96 * 1024;   // resident coefficient bytes per CTA
+constexpr int kRtSmemLimit = 227 * 1024;   // dynamic shared memory available to one CTA
 
-template <int R>
+// WARPS independent warps per CTA, each with a ring of STAGES buffers of which PRE are in flight
+// ahead of the one being computed (STAGES - PRE - 1 buffers may still be read by earlier stores).
+template <int R, int WARPS_, int STAGES_, int PRE_>
 struct ReadoutTmaCfg {
+  static constexpr int WARPS = WARPS_;
+  static constexpr int STAGES = STAGES_;
+  static constexpr int PRE = PRE_;
   static constexpr int A_SLICE = 16 * R * 2;
   static constexpr int C_SLICE = 16 * 128;
   static constexpr int STAGE = ((A_SLICE + C_SLICE + 1023) / 1024) * 1024;
-  static constexpr int STAGES = R == 64 ? 3 : 4;
   static constexpr int W_BYTES = R * 128;  // one word of one (head, 64-channel block)
-  static constexpr int RING = kRtWarps * STAGES * STAGE;
+  static constexpr int RING = WARPS * STAGES * STAGE;
+  static_assert(PRE >= 1 && PRE < STAGES, "prefetch depth");
 };
 
 struct ReadoutTmaParams {
@@ -39,16 +43,18 @@ struct ReadoutTmaParams {
   int tokens, heads, head_dim, rotary_rows, dblocks;
   int group_heads;   // heads per CTA group
   int slices;        // ceil(tokens / 16)
+  int probe;         // developer probe: 1 = no arithmetic, 2 = no arithmetic and no stores
+  int order;         // 1 = the warps of a CTA take the heads of one slice side by side
 };
 
-template <int R, bool ROT>
-__global__ void __launch_bounds__(kRtWarps * 32)
+template <int R, bool ROT, class Cfg>
+__global__ void __launch_bounds__(Cfg::WARPS * 32)
 readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_c,
                    const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
                    const ReadoutTmaParams p) {
-  using Cfg = ReadoutTmaCfg<R>;
   constexpr int STAGES = Cfg::STAGES;
-  constexpr int PRE = STAGES - 2;
+  constexpr int PRE = Cfg::PRE;
+  constexpr int kRtWarps = Cfg::WARPS;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
@@ -82,8 +88,17 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const int total = p.slices * mats;
   const int nwarps = gridDim.x * kRtWarps;
   const int per = (total + nwarps - 1) / nwarps;
-  const int it0 = min(total, (blockIdx.x * kRtWarps + warp) * per);
-  const int n_items = min(total, it0 + per) - it0;
+  int it0 = min(total, (blockIdx.x * kRtWarps + warp) * per);
+  int n_items = min(total, it0 + per) - it0;
+  int it_step = 1;
+  if (p.order == 1 && (kRtWarps % mats) == 0) {
+    // warp -> (head, block) pair warp % mats; slices strided over (CTA, warp / mats)
+    const int lanes = kRtWarps / mats;
+    const int first = blockIdx.x * lanes + warp / mats, stride = gridDim.x * lanes;
+    it0 = first * mats + warp % mats;
+    it_step = stride * mats;
+    n_items = first < p.slices ? (p.slices - first + stride - 1) / stride : 0;
+  }
 
   const int d = p.head_dim, half = d >> 1;
   const float n = p.counts ? p.counts[b] : (float)p.tokens;
@@ -93,12 +108,22 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const int mi = lane >> 3, mr = lane & 7;
 
   auto issue = [&](int k) {
-    const int e = it0 + k;
+    const int e = it0 + k * it_step;
     const int slice = e / mats, m = e - slice * mats;
     const int hl = m / p.dblocks, jb = m - hl * p.dblocks;
     const int h = h0 + hl;
     const uint32_t st = ring + (k % STAGES) * Cfg::STAGE;
     const uint32_t bar = mybar + (k % STAGES) * 8;
+    if (p.probe == 3) {          // content only
+      mbar_expect_tx(bar, Cfg::C_SLICE);
+      tma_load_3d(st, &map_c, p.heads * R + h * d + jb * 64, slice * 16, b, bar);
+      return;
+    }
+    if (p.probe == 4) {          // relation only
+      mbar_expect_tx(bar, Cfg::A_SLICE);
+      tma_load_3d(st + Cfg::C_SLICE, &map_a, h * R, slice * 16, b, bar);
+      return;
+    }
     mbar_expect_tx(bar, Cfg::A_SLICE + Cfg::C_SLICE);
     tma_load_3d(st, &map_c, p.heads * R + h * d + jb * 64, slice * 16, b, bar);
     tma_load_3d(st + Cfg::C_SLICE, &map_a, h * R, slice * 16, b, bar);
@@ -115,10 +140,11 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
   for (int k = 0; k < n_items && ok; ++k) {
     if (lane == 0 && k + PRE < n_items) {
-      tma_store_wait_read<1>();   // the buffer being refilled was the source of the store two items ago
+      // the buffer being refilled was the source of the store of item k + PRE - STAGES
+      tma_store_wait_read<STAGES - PRE - 1>();
       issue(k + PRE);
     }
-    const int e = it0 + k;
+    const int e = it0 + k * it_step;
     const int slice = e / mats, m = e - slice * mats;
     const int hl = m / p.dblocks, jb = m - hl * p.dblocks;
     const int h = h0 + hl;
@@ -127,7 +153,7 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const uint32_t wh_tile = w_base + (m * 2) * Cfg::W_BYTES;
     const uint32_t wl_tile = wh_tile + Cfg::W_BYTES;
 
-    if (ROT && (slice != tab_slice || jb != tab_jb)) {
+    if (ROT && (slice != tab_slice || jb != tab_jb) && p.probe == 0) {
       const int row0 = slice * 16;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -153,6 +179,20 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
 
+    if (p.probe != 0) {
+      if (p.probe == 1) {
+        fence_async_shared();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_3d(&map_y, h * d + jb * 64, slice * 16, b, c_tile);
+          tma_store_commit();
+        }
+      } else {
+        __syncwarp();
+        if (lane == 0) tma_store_commit();   // empty group keeps the wait bookkeeping uniform
+      }
+      continue;
+    }
     float acc[8][4];
 #pragma unroll
     for (int j = 0; j < 8; ++j)
@@ -198,17 +238,19 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   }
 }
 
-template <int R>
-static int launch_readout_tma_r(const ms_shape& s, const Plan& plan, const void* projected, const float* cos,
-                                const float* sin, const float* counts, const ms_tape& t, void* mixed,
-                                cudaStream_t st) {
-  using Cfg = ReadoutTmaCfg<R>;
+template <int R, class Cfg>
+static int launch_readout_tma_cfg(const ms_shape& s, const Plan& plan, const void* projected, const float* cos,
+                                  const float* sin, const float* counts, const ms_tape& t, void* mixed,
+                                  cudaStream_t st) {
+  constexpr int WARPS = Cfg::WARPS;
   const int d = s.head_dim, heads = s.heads, width = heads * (R + d), dmodel = heads * d;
   const int per_head = plan.dblocks * 2 * Cfg::W_BYTES;
-  int group = kRtWBudget / per_head;
+  const int fixed = 1024 + Cfg::RING + (WARPS * Cfg::STAGES + 1) * 8;
+  int group = (kRtSmemLimit - fixed) / per_head;   // heads whose coefficients stay resident in one CTA
   if (group < 1) return -1;
   if (group > heads) group = heads;
   const int groups = (heads + group - 1) / group;
+  group = (heads + groups - 1) / groups;           // balance the groups
 
   CUtensorMap map_a, map_c, map_w, map_y;
   {
@@ -240,25 +282,43 @@ static int launch_readout_tma_r(const ms_shape& s, const Plan& plan, const void*
   if (!p.error) return MS_ERR_LAUNCH;
   p.tokens = s.tokens; p.heads = heads; p.head_dim = d; p.rotary_rows = s.rotary_rows;
   p.dblocks = plan.dblocks; p.group_heads = group; p.slices = (s.tokens + 15) / 16;
+  p.probe = tuning_variant("MEMSOLVE_READOUT_PROBE");
+  p.order = tuning_variant("MEMSOLVE_READOUT_ORDER");
 
   const long total = (long)p.slices * group * plan.dblocks;
   long ctas = sm_count() / ((long)s.batch * groups);
   if (ctas < 1) ctas = 1;
-  const long need = (total + kRtWarps * 12 - 1) / (kRtWarps * 12);   // at least ~12 items per warp
+  const long need = (total + WARPS * 6 - 1) / (WARPS * 6);   // at least ~6 items per warp
   if (ctas > need) ctas = need < 1 ? 1 : need;
   dim3 grid((unsigned)ctas, s.batch, groups);
-  const int smem_bytes = 1024 + group * per_head + Cfg::RING + (kRtWarps * Cfg::STAGES + 1) * 8;
+  const int smem_bytes = fixed + group * per_head;
   const bool rot = s.rotary_rows > 0;
   if (rot) {
-    auto kern = readout_tma_kernel<R, true>;
+    auto kern = readout_tma_kernel<R, true, Cfg>;
     if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
-    kern<<<grid, kRtWarps * 32, smem_bytes, st>>>(map_a, map_c, map_w, map_y, p);
+    kern<<<grid, WARPS * 32, smem_bytes, st>>>(map_a, map_c, map_w, map_y, p);
   } else {
-    auto kern = readout_tma_kernel<R, false>;
+    auto kern = readout_tma_kernel<R, false, Cfg>;
     if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
-    kern<<<grid, kRtWarps * 32, smem_bytes, st>>>(map_a, map_c, map_w, map_y, p);
+    kern<<<grid, WARPS * 32, smem_bytes, st>>>(map_a, map_c, map_w, map_y, p);
   }
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
+}
+
+template <int R>
+static int launch_readout_tma_r(const ms_shape& s, const Plan& plan, const void* projected, const float* cos,
+                                const float* sin, const float* counts, const ms_tape& t, void* mixed,
+                                cudaStream_t st) {
+  switch (tuning_variant("MEMSOLVE_READOUT_VARIANT")) {
+    case 1: return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 16, 3, 1>>(s, plan, projected, cos, sin, counts, t, mixed, st);
+    case 2: return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 16, 3, 2>>(s, plan, projected, cos, sin, counts, t, mixed, st);
+    case 3: return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 16, 2, 1>>(s, plan, projected, cos, sin, counts, t, mixed, st);
+    case 4: return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 12, 3, 1>>(s, plan, projected, cos, sin, counts, t, mixed, st);
+    case 5: return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 12, 4, 2>>(s, plan, projected, cos, sin, counts, t, mixed, st);
+    case 6: return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 8, 4, 2>>(s, plan, projected, cos, sin, counts, t, mixed, st);
+    case 7: return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 8, (R == 64 ? 3 : 4), (R == 64 ? 1 : 2)>>(s, plan, projected, cos, sin, counts, t, mixed, st);
+  }
+  return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 16, 3, 1>>(s, plan, projected, cos, sin, counts, t, mixed, st);
 }
 
 // Returns MS_OK / an error, or -1 when the shape is outside this kernel's envelope (the caller

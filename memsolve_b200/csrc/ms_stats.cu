@@ -35,7 +35,7 @@ struct StatsParams {
   const float* cos;
   const float* sin;
   float* partials;          // [systems][chunks][partial_floats]
-  float* de_partials;       // [systems][chunks*dblocks]   (adjoint only)
+  float* de_partials;       // [systems][chunks*2*dblocks] (adjoint only)
   int batch, tokens, heads, head_dim, width, rotary_rows;
   int chunks, chunk_tokens, dblocks;
   int partial_floats;
@@ -308,7 +308,10 @@ stats_kernel(const StatsParams p) {
     if (tid == 0) {
       float v = 0.f;
       for (int w = 0; w < NT / 32; ++w) v += red[w];
-      p.de_partials[((size_t)sys * p.chunks + chunk) * p.dblocks + dblk] = v;
+      // two slots per 64-channel block (the 32-channel TMA kernel fills both)
+      float* de = p.de_partials + ((size_t)sys * p.chunks + chunk) * (2 * p.dblocks);
+      de[2 * dblk] = v;
+      de[2 * dblk + 1] = 0.f;
     }
   }
 }
@@ -321,7 +324,7 @@ int launch_stats_tma(const ms_shape& s, const Plan& plan, bool grad, const void*
 // packed forward:  [systems][r*r + r*d]      packed adjoint: [systems][r*d] then [systems] de
 __global__ void pack_stats_kernel(const float* __restrict__ partials, const float* __restrict__ de_partials,
                                   const float* __restrict__ counts, float* __restrict__ packed,
-                                  int heads, int tokens, int chunks, int dblocks, int gram_floats,
+                                  int heads, int tokens, int chunks, int de_slots, int gram_floats,
                                   int partial_floats, int systems, int grad) {
   const int sys = blockIdx.y;
   const int b = sys / heads;
@@ -335,7 +338,7 @@ __global__ void pack_stats_kernel(const float* __restrict__ partials, const floa
   }
   if (grad && blockIdx.x == 0 && threadIdx.x == 0) {
     float v = 0.f;
-    for (int c = 0; c < chunks * dblocks; ++c) v += de_partials[(size_t)sys * chunks * dblocks + c];
+    for (int c = 0; c < chunks * de_slots; ++c) v += de_partials[(size_t)sys * chunks * de_slots + c];
     packed[(size_t)systems * partial_floats + sys] = v;
   }
 }
@@ -399,7 +402,7 @@ int launch_pack_stats(const ms_shape& s, const Plan& plan, bool grad, const floa
   const int pf = (int)(grad ? plan.bwd_partial_floats : plan.fwd_partial_floats);
   dim3 grid((pf + 255) / 256, plan.systems);
   pack_stats_kernel<<<grid, 256, 0, st>>>(partials, de_partials, counts, packed, s.heads, s.tokens,
-                                          plan.chunks, plan.dblocks, grad ? 0 : s.rank * s.rank, pf,
+                                          plan.chunks, plan.de_slots, grad ? 0 : s.rank * s.rank, pf,
                                           plan.systems, grad ? 1 : 0);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }

@@ -21,18 +21,22 @@ namespace ms {
 
 constexpr int kStWarps = 8;
 
-template <int R, bool GRAD, bool ROT>
+// CB: channels of one CTA (64, or 32 so that two CTAs with half the accumulators share an SM; the
+// Gram columns are then divided between the first two channel blocks of a head).
+template <int R, bool GRAD, bool ROT, int CB, int STAGES_>
 struct StatsTmaCfg {
   static constexpr int A_SLICE = 16 * R * 2;
-  static constexpr int X_BYTES = 2048;
-  static constexpr int T_BYTES = 2048;   // one table (cos or sin), 16 rows x 32 floats
+  static constexpr int X_BYTES = 16 * CB * 2;
+  static constexpr int T_BYTES = 16 * (CB / 2) * 4;   // one table (cos or sin), 16 rows x CB/2 floats
   static constexpr int RAW = X_BYTES + (GRAD ? X_BYTES : 0) + (ROT ? 2 * T_BYTES : 0) + A_SLICE;
   static constexpr int STAGE = ((RAW + 1023) / 1024) * 1024;
-  static constexpr int STAGES = GRAD ? 2 : 3;
+  static constexpr int STAGES = STAGES_;
   static constexpr int LO = ROT ? X_BYTES : 0;
-  static constexpr int WARP_BYTES = STAGES * STAGE + LO;
+  static constexpr int WARP_BYTES = STAGES * STAGE + ((LO + 1023) / 1024) * 1024;
   static constexpr int RING = kStWarps * WARP_BYTES;
-  static constexpr int RCOLS = (GRAD ? 0 : R) + 64;
+  static constexpr int GP = (CB == 32 && R >= 32) ? 2 : 1;            // channel blocks sharing the Gram columns
+  static constexpr int GCOLS = GRAD ? 0 : R / GP;
+  static constexpr int RCOLS = GCOLS + CB;
   static constexpr int RED = kStWarps * R * RCOLS * 4;
   static constexpr int CORE = GRAD ? 0 : (int)core_forward_smem_bytes(R);
   static constexpr int BODY = RING > RED ? (RING > CORE ? RING : CORE) : (RED > CORE ? RED : CORE);
@@ -44,7 +48,7 @@ struct StatsTmaParams {
   float* partials;
   float* de_partials;
   int* error;
-  int tokens, heads, head_dim, rotary_rows, chunks, chunk_tokens, dblocks, partial_floats;
+  int tokens, heads, head_dim, rotary_rows, chunks, chunk_tokens, de_slots, partial_floats;
   const float* base_raw;
   const float* eta_raw;
   float* eta;
@@ -52,17 +56,19 @@ struct StatsTmaParams {
   float* core_map;
   int* core_info;
   int complement;
+  int probe;   // developer probe: 1 = loads only
 };
 
-template <int R, bool GRAD, bool ROT>
-__global__ void __launch_bounds__(kStWarps * 32)
+template <int R, bool GRAD, bool ROT, int CB, int STAGES_>
+__global__ void __launch_bounds__(kStWarps * 32, CB == 32 ? 2 : 1)
 stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_c,
                  const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_cos,
                  const __grid_constant__ CUtensorMap map_sin, const StatsTmaParams p) {
-  using Cfg = StatsTmaCfg<R, GRAD, ROT>;
+  using Cfg = StatsTmaCfg<R, GRAD, ROT, CB, STAGES_>;
   constexpr int STAGES = Cfg::STAGES;
-  constexpr int MT = R / 16, NG = R / 8;
+  constexpr int MT = R / 16, NG = Cfg::GCOLS / 8, NQ = CB / 8;
   constexpr int NT = kStWarps * 32;
+  constexpr int XP = CB * 2;   // row pitch in bytes of the content / gradient / table tiles
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* smem_gen = smem_raw + (smem - smem_u32(smem_raw));
@@ -77,13 +83,14 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     return;
   }
   const int b = sys / p.heads, h = sys - b * p.heads;
-  const int d0 = dblk * 64;
+  const int d0 = dblk * CB;
   const int tok0 = chunk * p.chunk_tokens;
   const int tok1 = min(p.tokens, tok0 + p.chunk_tokens);
   const int slice0 = tok0 >> 4;
   const int nslices = (tok1 - tok0 + 15) >> 4;
   const int n_items = nslices > warp ? (nslices - warp + kStWarps - 1) / kStWarps : 0;
-  const bool do_gram = !GRAD && dblk == 0;
+  const bool do_gram = !GRAD && dblk < Cfg::GP;
+  const int gcol0 = dblk * Cfg::GCOLS;   // first Gram column of this CTA (when do_gram)
   const int tab_b = p.rotary_rows > 1 ? b : 0;
 
   const uint32_t ring = smem + warp * Cfg::WARP_BYTES;
@@ -123,7 +130,7 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   };
 
   float accG[GRAD ? 1 : MT][GRAD ? 1 : NG][4];
-  float accQ[MT][8][4];
+  float accQ[MT][NQ][4];
 #pragma unroll
   for (int i = 0; i < (GRAD ? 1 : MT); ++i)
 #pragma unroll
@@ -133,7 +140,7 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
   for (int i = 0; i < MT; ++i)
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < NQ; ++j)
 #pragma unroll
       for (int q = 0; q < 4; ++q) accQ[i][j][q] = 0.f;
   float de_acc = 0.f;
@@ -154,14 +161,19 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     ok = mbar_wait(mybar + (k % STAGES) * 8, (uint32_t)((k / STAGES) & 1));
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
+    if (p.probe != 0) {
+      __syncwarp();
+      if (k + STAGES < n_items && lane == 0) issue(k + STAGES);
+      continue;
+    }
 
     if (ROT || GRAD) {
-      // elementwise pass over the 16 x 64 slice, one 16-byte chunk (8 channels) at a time
+      // elementwise pass over the 16 x CB slice, one 16-byte chunk (8 channels) at a time
 #pragma unroll
-      for (int it = 0; it < 4; ++it) {
+      for (int it = 0; it < CB / 16; ++it) {
         const int i = lane + it * 32;
-        const int row = i >> 3, c = i & 7;
-        const uint32_t off = swz_rows<128>(row * 128 + c * 16);
+        const int row = i / (CB / 8), c = i % (CB / 8);
+        const uint32_t off = swz_rows<XP>(row * XP + c * 16);
         const uint4 xv = ld_shared_v4(x_tile + off);
         const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w};
         if (GRAD) {
@@ -175,8 +187,8 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         }
         if (ROT) {
-          const float4 cc = ld_shared_f4(cos_tile + row * 128 + c * 16);
-          const float4 ss = ld_shared_f4(sin_tile + row * 128 + c * 16);
+          const float4 cc = ld_shared_f4(cos_tile + row * XP + c * 16);
+          const float4 ss = ld_shared_f4(sin_tile + row * XP + c * 16);
           const float cf[4] = {cc.x, cc.y, cc.z, cc.w};
           const float sf[4] = {ss.x, ss.y, ss.z, ss.w};
           uint32_t hi[4], lo[4];
@@ -204,7 +216,8 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
         for (int n2 = 0; n2 < NG / 2; ++n2) {
           uint32_t bf[4];
-          ldsm_x4_t(bf, a_tile + swz_rows<R * 2>((mr + 8 * (mi & 1)) * (R * 2) + (n2 * 16 + 8 * (mi >> 1)) * 2));
+          ldsm_x4_t(bf, a_tile + swz_rows<R * 2>((mr + 8 * (mi & 1)) * (R * 2) +
+                                                 (gcol0 + n2 * 16 + 8 * (mi >> 1)) * 2));
 #pragma unroll
           for (int m = 0; m < MT; ++m) {
             mma_bf16(accG[m][2 * n2], af[m], bf[0], bf[1]);
@@ -214,8 +227,8 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
     }
 #pragma unroll
-    for (int n2 = 0; n2 < 4; ++n2) {
-      const uint32_t off = swz_rows<128>((mr + 8 * (mi & 1)) * 128 + (n2 * 16 + 8 * (mi >> 1)) * 2);
+    for (int n2 = 0; n2 < NQ / 2; ++n2) {
+      const uint32_t off = swz_rows<XP>((mr + 8 * (mi & 1)) * XP + (n2 * 16 + 8 * (mi >> 1)) * 2);
       uint32_t bf[4];
       if (ROT) {
         ldsm_x4_t(bf, lo_tile + off);   // residual word first, dominant word last
@@ -260,8 +273,8 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
       }
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
-        const int col = (GRAD ? 0 : R) + n * 8 + 2 * tq;
+      for (int n = 0; n < NQ; ++n) {
+        const int col = Cfg::GCOLS + n * 8 + 2 * tq;
         *reinterpret_cast<float2*>(mine + r0 * RCOLS + col) = make_float2(accQ[m][n][0], accQ[m][n][1]);
         *reinterpret_cast<float2*>(mine + (r0 + 8) * RCOLS + col) = make_float2(accQ[m][n][2], accQ[m][n][3]);
       }
@@ -275,10 +288,10 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < kStWarps; ++w) v += red[(size_t)w * R * RCOLS + i];
-    if (!GRAD && col < R) {
-      if (do_gram) out[row * R + col] = v;
+    if (col < Cfg::GCOLS) {
+      if (do_gram) out[row * R + gcol0 + col] = v;
     } else {
-      out[gfloats + row * p.head_dim + d0 + col - (GRAD ? 0 : R)] = v;
+      out[gfloats + row * p.head_dim + d0 + col - Cfg::GCOLS] = v;
     }
   }
   if (GRAD) {
@@ -290,23 +303,30 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (tid == 0) {
       float v = 0.f;
       for (int w = 0; w < kStWarps; ++w) v += red[w];
-      p.de_partials[((size_t)sys * p.chunks + chunk) * p.dblocks + dblk] = v;
+      // de slots: two per 64-channel block
+      float* de = p.de_partials + ((size_t)sys * p.chunks + chunk) * p.de_slots;
+      if (CB == 32) {
+        de[dblk] = v;
+      } else {
+        de[2 * dblk] = v;
+        de[2 * dblk + 1] = 0.f;
+      }
     }
   }
 }
 
-template <int R, bool GRAD, bool ROT>
+template <int R, bool GRAD, bool ROT, int CB, int STAGES>
 static int launch_stats_tma_one(const ms_shape& s, const Plan& plan, const CUtensorMap* maps, const StatsTmaParams& p,
                                 bool fuse_core, cudaStream_t st) {
-  using Cfg = StatsTmaCfg<R, GRAD, ROT>;
-  auto kern = stats_tma_kernel<R, GRAD, ROT>;
+  using Cfg = StatsTmaCfg<R, GRAD, ROT, CB, STAGES>;
+  auto kern = stats_tma_kernel<R, GRAD, ROT, CB, STAGES>;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Cfg::TOTAL)) return MS_ERR_LAUNCH;
-  dim3 grid(plan.chunks + (fuse_core ? 1 : 0), plan.systems, plan.dblocks);
+  dim3 grid(plan.chunks + (fuse_core ? 1 : 0), plan.systems, s.head_dim / CB);
   kern<<<grid, kStWarps * 32, Cfg::TOTAL, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
 
-template <int R, bool GRAD>
+template <int R, bool GRAD, int CB, int STAGES>
 static int launch_stats_tma_r(const ms_shape& s, const Plan& plan, const void* projected, const void* dy,
                               const float* cos, const float* sin, StatsTmaParams& p, bool fuse_core,
                               cudaStream_t st) {
@@ -316,18 +336,19 @@ static int launch_stats_tma_r(const ms_shape& s, const Plan& plan, const void* p
     const uint64_t dims[3] = {(uint64_t)width, (uint64_t)s.tokens, (uint64_t)s.batch};
     const uint64_t str[2] = {(uint64_t)width * 2, (uint64_t)s.tokens * width * 2};
     const uint32_t box_a[3] = {(uint32_t)R, 16, 1};
-    const uint32_t box_c[3] = {64, 16, 1};
+    const uint32_t box_c[3] = {(uint32_t)CB, 16, 1};
     if (encode_tensor_map(&maps[0], const_cast<void*>(projected), 2, 3, dims, str, box_a, swizzle_for_rows<R * 2>()))
       return MS_ERR_LAUNCH;
-    if (encode_tensor_map(&maps[1], const_cast<void*>(projected), 2, 3, dims, str, box_c, Swizzle::B128))
+    if (encode_tensor_map(&maps[1], const_cast<void*>(projected), 2, 3, dims, str, box_c, swizzle_for_rows<CB * 2>()))
       return MS_ERR_LAUNCH;
   }
   maps[2] = maps[1];
   if (GRAD) {
     const uint64_t dims[3] = {(uint64_t)dmodel, (uint64_t)s.tokens, (uint64_t)s.batch};
     const uint64_t str[2] = {(uint64_t)dmodel * 2, (uint64_t)s.tokens * dmodel * 2};
-    const uint32_t box[3] = {64, 16, 1};
-    if (encode_tensor_map(&maps[2], const_cast<void*>(dy), 2, 3, dims, str, box, Swizzle::B128)) return MS_ERR_LAUNCH;
+    const uint32_t box[3] = {(uint32_t)CB, 16, 1};
+    if (encode_tensor_map(&maps[2], const_cast<void*>(dy), 2, 3, dims, str, box, swizzle_for_rows<CB * 2>()))
+      return MS_ERR_LAUNCH;
   }
   maps[3] = maps[1];
   maps[4] = maps[1];
@@ -336,12 +357,12 @@ static int launch_stats_tma_r(const ms_shape& s, const Plan& plan, const void* p
     const int half = d / 2;
     const uint64_t dims[3] = {(uint64_t)half, (uint64_t)s.tokens, (uint64_t)s.rotary_rows};
     const uint64_t str[2] = {(uint64_t)half * 4, (uint64_t)s.tokens * half * 4};
-    const uint32_t box[3] = {32, 16, 1};
+    const uint32_t box[3] = {(uint32_t)(CB / 2), 16, 1};
     if (encode_tensor_map(&maps[3], const_cast<float*>(cos), 4, 3, dims, str, box, Swizzle::None)) return MS_ERR_LAUNCH;
     if (encode_tensor_map(&maps[4], const_cast<float*>(sin), 4, 3, dims, str, box, Swizzle::None)) return MS_ERR_LAUNCH;
   }
-  return rot ? launch_stats_tma_one<R, GRAD, true>(s, plan, maps, p, fuse_core, st)
-             : launch_stats_tma_one<R, GRAD, false>(s, plan, maps, p, fuse_core, st);
+  return rot ? launch_stats_tma_one<R, GRAD, true, CB, STAGES>(s, plan, maps, p, fuse_core, st)
+             : launch_stats_tma_one<R, GRAD, false, CB, STAGES>(s, plan, maps, p, fuse_core, st);
 }
 
 // MS_OK / error, or -1 when the shape is outside this kernel's envelope.
@@ -355,7 +376,7 @@ int launch_stats_tma(const ms_shape& s, const Plan& plan, bool grad, const void*
   p.error = device_error_word();
   if (!p.error) return MS_ERR_LAUNCH;
   p.tokens = s.tokens; p.heads = s.heads; p.head_dim = s.head_dim; p.rotary_rows = s.rotary_rows;
-  p.chunks = plan.chunks; p.chunk_tokens = plan.chunk_tokens; p.dblocks = plan.dblocks;
+  p.chunks = plan.chunks; p.chunk_tokens = plan.chunk_tokens; p.de_slots = plan.de_slots;
   p.partial_floats = (int)(grad ? plan.bwd_partial_floats : plan.fwd_partial_floats);
   const bool fuse_core = !grad && core_tape != nullptr;
   p.base_raw = base_raw; p.eta_raw = eta_raw;
@@ -364,17 +385,26 @@ int launch_stats_tma(const ms_shape& s, const Plan& plan, bool grad, const void*
   p.core_map = fuse_core ? core_tape->core_map : nullptr;
   p.core_info = fuse_core ? core_tape->core_info : nullptr;
   p.complement = s.complement;
+  p.probe = tuning_variant("MEMSOLVE_STATS_PROBE");
+  if (plan.stats_cb == 32) {
+    // two CTAs per SM, 32 channels each (rank 32 only; make_plan chooses)
+    if (s.rank != 32) return -1;
+    if (grad) return launch_stats_tma_r<32, true, 32, 2>(s, plan, projected, dy, cos, sin, p, false, st);
+    if (tuning_variant("MEMSOLVE_STATS_VARIANT") == 2)
+      return launch_stats_tma_r<32, false, 32, 2>(s, plan, projected, dy, cos, sin, p, fuse_core, st);
+    return launch_stats_tma_r<32, false, 32, 3>(s, plan, projected, dy, cos, sin, p, fuse_core, st);
+  }
   if (grad) {
     switch (s.rank) {
-      case 16: return launch_stats_tma_r<16, true>(s, plan, projected, dy, cos, sin, p, false, st);
-      case 32: return launch_stats_tma_r<32, true>(s, plan, projected, dy, cos, sin, p, false, st);
-      case 64: return launch_stats_tma_r<64, true>(s, plan, projected, dy, cos, sin, p, false, st);
+      case 16: return launch_stats_tma_r<16, true, 64, 2>(s, plan, projected, dy, cos, sin, p, false, st);
+      case 32: return launch_stats_tma_r<32, true, 64, 2>(s, plan, projected, dy, cos, sin, p, false, st);
+      case 64: return launch_stats_tma_r<64, true, 64, 2>(s, plan, projected, dy, cos, sin, p, false, st);
     }
     return -1;
   }
   switch (s.rank) {
-    case 16: return launch_stats_tma_r<16, false>(s, plan, projected, dy, cos, sin, p, fuse_core, st);
-    case 32: return launch_stats_tma_r<32, false>(s, plan, projected, dy, cos, sin, p, fuse_core, st);
+    case 16: return launch_stats_tma_r<16, false, 64, 3>(s, plan, projected, dy, cos, sin, p, fuse_core, st);
+    case 32: return launch_stats_tma_r<32, false, 64, 3>(s, plan, projected, dy, cos, sin, p, fuse_core, st);
   }
   return -1;
 }

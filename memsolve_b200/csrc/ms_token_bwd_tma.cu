@@ -18,20 +18,23 @@
 
 namespace ms {
 
-constexpr int kTbWarps = 8;
-
-template <int R>
+// WARPS independent warps per CTA, each with a ring of STAGES buffers of which PRE are in flight
+// ahead of the one being computed (STAGES - PRE - 1 buffers may still be read by earlier stores).
+template <int R, int WARPS_, int STAGES_, int PRE_>
 struct TokenBwdTmaCfg {
+  static constexpr int WARPS = WARPS_;
+  static constexpr int STAGES = STAGES_;
+  static constexpr int PRE = PRE_;
   static constexpr int A_SLICE = 16 * R * 2;
   static constexpr int STAGE = ((4096 + A_SLICE + 1023) / 1024) * 1024;   // C, dY, A
-  static constexpr int STAGES = 3;
-  static constexpr int RING = kTbWarps * STAGES * STAGE;
+  static constexpr int RING = WARPS * STAGES * STAGE;
   static constexpr int W_BYTES = R * 128;
   static constexpr int S_BYTES = R * R * 2;
   static constexpr int HEAD_BYTES = 4 * W_BYTES + 2 * S_BYTES;   // W hi/lo, dQ hi/lo, S hi/lo
-  static constexpr int BAR_BYTES = (kTbWarps * STAGES + 1) * 8;
+  static constexpr int BAR_BYTES = (WARPS * STAGES + 1) * 8;
   static constexpr int MAX_SMEM = 227 * 1024;
   static constexpr int RESIDENT_BUDGET = MAX_SMEM - 1024 - RING - BAR_BYTES - 64;
+  static_assert(PRE >= 1 && PRE < STAGES, "prefetch depth");
 };
 
 struct TokenBwdTmaParams {
@@ -51,18 +54,61 @@ struct TokenBwdTmaParams {
   float* d_eta_raw;
   float grad_scale;
   int complement;
+  int probe;   // developer probe: 1 = no arithmetic, 2 = no arithmetic and no stores
 };
 
+// acc += rot(X) M^T for the 16 x 64 row operand `raw` (BF16 fragments of one warp) and a matrix
+// stored [R output columns][64 channels] as two BF16 words (128-byte pitch, 128-byte swizzle).
+// One 16-channel step at a time: rotate and split the step's fragment, then the two residual
+// products and the dominant one, so that only one step of split fragments is live.
 template <int R, bool ROT>
-__global__ void __launch_bounds__(kTbWarps * 32)
+__device__ __forceinline__ void mma_rotated_rows(float (&acc)[R / 8][4], const uint32_t (&raw)[4][4],
+                                                 const TableFrag& tab, uint32_t hi_tile, uint32_t lo_tile,
+                                                 int lane) {
+  const int mi = lane >> 3, mr = lane & 7;
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks) {
+    uint32_t xh[4], xl[4];
+    if (ROT) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int j = 2 * ks + (q >> 1), k = q & 1;   // q: (row g|g+8) x (cols 0-7 | 8-15)
+        const float2 v = bf2_to_f2(raw[ks][q]);
+        const float2 r = rot_pair(v.x, v.y, tab.c[j][k], tab.s[j][k]);
+        split2(r.x, r.y, xh[q], xl[q]);
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) xh[q] = raw[ks][q];
+    }
+#pragma unroll
+    for (int n2 = 0; n2 < R / 16; ++n2) {
+      const uint32_t off = swz((n2 * 16 + mr + 8 * (mi >> 1)) * 128 + (ks * 16 + 8 * (mi & 1)) * 2);
+      uint32_t bh[4], bl[4];
+      ldsm_x4(bh, hi_tile + off);
+      ldsm_x4(bl, lo_tile + off);
+      if (ROT) {
+        mma_bf16(acc[2 * n2], xl, bh[0], bh[1]);
+        mma_bf16(acc[2 * n2 + 1], xl, bh[2], bh[3]);
+      }
+      mma_bf16(acc[2 * n2], xh, bl[0], bl[1]);
+      mma_bf16(acc[2 * n2 + 1], xh, bl[2], bl[3]);
+      mma_bf16(acc[2 * n2], xh, bh[0], bh[1]);
+      mma_bf16(acc[2 * n2 + 1], xh, bh[2], bh[3]);
+    }
+  }
+}
+
+template <int R, bool ROT, class Cfg>
+__global__ void __launch_bounds__(Cfg::WARPS * 32)
 token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_c,
                           const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_w,
                           const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_s,
                           const __grid_constant__ CUtensorMap map_oa, const __grid_constant__ CUtensorMap map_oc,
                           const TokenBwdTmaParams p) {
-  using Cfg = TokenBwdTmaCfg<R>;
   constexpr int STAGES = Cfg::STAGES;
-  constexpr int PRE = STAGES - 2;
+  constexpr int PRE = Cfg::PRE;
+  constexpr int WARPS = Cfg::WARPS;
   constexpr int NR = R / 8;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -72,7 +118,7 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     if (blockIdx.y == 0 && blockIdx.z == 0)
       core_backward_device(p.base_raw, p.hmat, p.de_sys, p.eta_slope, p.core_map, R, blockIdx.x - p.work_ctas,
                            p.heads, p.batch, p.complement, p.grad_scale, p.d_base, p.d_eta_raw,
-                           smem_raw + (smem - smem_u32(smem_raw)), tid, kTbWarps * 32);
+                           smem_raw + (smem - smem_u32(smem_raw)), tid, WARPS * 32);
     return;
   }
 
@@ -82,11 +128,11 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   const uint32_t res_base = smem;
   const uint32_t ring = smem + p.group_heads * Cfg::HEAD_BYTES + warp * STAGES * Cfg::STAGE;
   const uint32_t bars = smem + p.group_heads * Cfg::HEAD_BYTES + Cfg::RING;
-  const uint32_t rbar = bars + kTbWarps * STAGES * 8;
+  const uint32_t rbar = bars + WARPS * STAGES * 8;
   const uint32_t mybar = bars + warp * STAGES * 8;
 
   if (tid == 0) {
-    for (int i = 0; i < kTbWarps * STAGES + 1; ++i) mbar_init(bars + i * 8, 1);
+    for (int i = 0; i < WARPS * STAGES + 1; ++i) mbar_init(bars + i * 8, 1);
     mbar_fence_init();
   }
   __syncthreads();
@@ -105,9 +151,9 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   }
 
   const int total = p.slices * gh;
-  const int nwarps = p.work_ctas * kTbWarps;
+  const int nwarps = p.work_ctas * WARPS;
   const int per = (total + nwarps - 1) / nwarps;
-  const int it0 = min(total, (blockIdx.x * kTbWarps + warp) * per);
+  const int it0 = min(total, (blockIdx.x * WARPS + warp) * per);
   const int n_items = min(total, it0 + per) - it0;
 
   const float n = p.counts ? p.counts[b] : (float)p.tokens;
@@ -139,7 +185,8 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 
   for (int k = 0; k < n_items && ok; ++k) {
     if (lane == 0 && k + PRE < n_items) {
-      tma_store_wait_read<1>();
+      // the buffer being refilled was the source of the stores of item k + PRE - STAGES
+      tma_store_wait_read<STAGES - PRE - 1>();
       issue(k + PRE);
     }
     const int e = it0 + k;
@@ -164,65 +211,28 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     ok = mbar_wait(mybar + (k % STAGES) * 8, (uint32_t)((k / STAGES) & 1));
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
+    if (p.probe != 0) {
+      fence_async_shared();
+      __syncwarp();
+      if (lane == 0) {
+        if (p.probe == 1) {
+          tma_store_3d(&map_oc, p.heads * R + h * 64, slice * 16, b, y_tile);
+          tma_store_3d(&map_oa, h * R, slice * 16, b, a_tile);
+        }
+        tma_store_commit();
+      }
+      continue;
+    }
 
     uint32_t af[R / 16][4];
 #pragma unroll
     for (int ks = 0; ks < R / 16; ++ks)
       ldsm_x4(af[ks], a_tile + swz_rows<R * 2>((mr + 8 * (mi & 1)) * (R * 2) + (ks * 16 + 8 * (mi >> 1)) * 2));
+    uint32_t xraw[4][4];
+    load_row_frags(xraw, y_tile, 0, lane);
+    __syncwarp();   // every lane has read the gradient box before dC is written over it
 
-    // s * A (dG + dG^T): symmetric matrix stored [n][k], residual word first
-    float acc_a[NR][4];
-#pragma unroll
-    for (int j = 0; j < NR; ++j)
-#pragma unroll
-      for (int q = 0; q < 4; ++q) acc_a[j][q] = 0.f;
-#pragma unroll
-    for (int word = 0; word < 2; ++word) {
-      const uint32_t st = word == 0 ? sl_tile : sh_tile;
-#pragma unroll
-      for (int ks = 0; ks < R / 16; ++ks) {
-#pragma unroll
-        for (int n2 = 0; n2 < R / 16; ++n2) {
-          uint32_t bf[4];
-          ldsm_x4(bf, st + swz_rows<R * 2>((n2 * 16 + mr + 8 * (mi >> 1)) * (R * 2) + (ks * 16 + 8 * (mi & 1)) * 2));
-          mma_bf16(acc_a[2 * n2], af[ks], bf[0], bf[1]);
-          mma_bf16(acc_a[2 * n2 + 1], af[ks], bf[2], bf[3]);
-        }
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < NR; ++j)
-#pragma unroll
-      for (int q = 0; q < 4; ++q) acc_a[j][q] *= inv_s;
-
-    // rot(dY) W^T and rot(C) dQ^T
-    uint32_t yraw[4][4];
-    load_row_frags(yraw, y_tile, 0, lane);
-    {
-      uint32_t xh[4][4], xl[4][4];
-      if (ROT) {
-        rotate_split(yraw, tab, xh, xl);
-        mma_rows_by_stored_nk<R>(acc_a, xl, wh_tile, lane);
-        mma_rows_by_stored_nk<R>(acc_a, xh, wl_tile, lane);
-        mma_rows_by_stored_nk<R>(acc_a, xh, wh_tile, lane);
-      } else {
-        mma_rows_by_stored_nk<R>(acc_a, yraw, wl_tile, lane);
-        mma_rows_by_stored_nk<R>(acc_a, yraw, wh_tile, lane);
-      }
-      uint32_t craw[4][4];
-      load_row_frags(craw, c_tile, 0, lane);
-      if (ROT) {
-        rotate_split(craw, tab, xh, xl);
-        mma_rows_by_stored_nk<R>(acc_a, xl, qh_tile, lane);
-        mma_rows_by_stored_nk<R>(acc_a, xh, ql_tile, lane);
-        mma_rows_by_stored_nk<R>(acc_a, xh, qh_tile, lane);
-      } else {
-        mma_rows_by_stored_nk<R>(acc_a, craw, ql_tile, lane);
-        mma_rows_by_stored_nk<R>(acc_a, craw, qh_tile, lane);
-      }
-    }
-
-    // dC = eta*dY + s * rot^-1(A dQ), written over the content box
+    // dC = eta*dY + s * rot^-1(A dQ), written over the upstream-gradient box
     {
       float acc[8][4];
 #pragma unroll
@@ -249,12 +259,41 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         for (int kk = 0; kk < 2; ++kk) {
           float2 corr = make_float2(acc[j][2 * kk], acc[j][2 * kk + 1]);
           if (ROT) corr = rot_pair(corr.x, corr.y, tab.c[j][kk], -tab.s[j][kk]);
-          const float2 yv = bf2_to_f2(yraw[j >> 1][2 * (j & 1) + kk]);
-          st_shared_u32(c_tile + swz((g + 8 * kk) * 128 + (8 * j + 2 * tq) * 2),
+          const float2 yv = bf2_to_f2(xraw[j >> 1][2 * (j & 1) + kk]);
+          st_shared_u32(y_tile + swz((g + 8 * kk) * 128 + (8 * j + 2 * tq) * 2),
                         f2_to_bf2(fmaf(corr.x, inv_s, eta * yv.x), fmaf(corr.y, inv_s, eta * yv.y)));
         }
       }
     }
+
+    // dA = s*( s*A (dG + dG^T) + rot(dY) W^T + rot(C) dQ^T ): the symmetric matrix is stored [n][k],
+    // residual word first
+    float acc_a[NR][4];
+#pragma unroll
+    for (int j = 0; j < NR; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc_a[j][q] = 0.f;
+#pragma unroll
+    for (int word = 0; word < 2; ++word) {
+      const uint32_t st = word == 0 ? sl_tile : sh_tile;
+#pragma unroll
+      for (int ks = 0; ks < R / 16; ++ks) {
+#pragma unroll
+        for (int n2 = 0; n2 < R / 16; ++n2) {
+          uint32_t bf[4];
+          ldsm_x4(bf, st + swz_rows<R * 2>((n2 * 16 + mr + 8 * (mi >> 1)) * (R * 2) + (ks * 16 + 8 * (mi & 1)) * 2));
+          mma_bf16(acc_a[2 * n2], af[ks], bf[0], bf[1]);
+          mma_bf16(acc_a[2 * n2 + 1], af[ks], bf[2], bf[3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NR; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc_a[j][q] *= inv_s;
+    mma_rotated_rows<R, ROT>(acc_a, xraw, tab, wh_tile, wl_tile, lane);
+    load_row_frags(xraw, c_tile, 0, lane);
+    mma_rotated_rows<R, ROT>(acc_a, xraw, tab, qh_tile, ql_tile, lane);
     // dA over the relation box
 #pragma unroll
     for (int j = 0; j < NR; ++j) {
@@ -267,7 +306,7 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     fence_async_shared();
     __syncwarp();
     if (lane == 0) {
-      tma_store_3d(&map_oc, p.heads * R + h * 64, slice * 16, b, c_tile);
+      tma_store_3d(&map_oc, p.heads * R + h * 64, slice * 16, b, y_tile);
       tma_store_3d(&map_oa, h * R, slice * 16, b, a_tile);
       tma_store_commit();
     }
@@ -278,12 +317,12 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   }
 }
 
-template <int R>
-static int launch_token_bwd_tma_r(const ms_shape& s, const Plan& plan, const void* projected, const void* dy,
-                                  const float* cos, const float* sin, const float* counts, const ms_tape& t,
-                                  const void* gram_grad, const void* cross_grad, void* dprojected,
-                                  const CoreAdjoint* core, cudaStream_t st) {
-  using Cfg = TokenBwdTmaCfg<R>;
+template <int R, class Cfg>
+static int launch_token_bwd_tma_cfg(const ms_shape& s, const Plan& plan, const void* projected, const void* dy,
+                                    const float* cos, const float* sin, const float* counts, const ms_tape& t,
+                                    const void* gram_grad, const void* cross_grad, void* dprojected,
+                                    const CoreAdjoint* core, cudaStream_t st) {
+  constexpr int kTbWarps = Cfg::WARPS;
   const int heads = s.heads, width = heads * (R + 64), dmodel = heads * 64;
   int group = Cfg::RESIDENT_BUDGET / Cfg::HEAD_BYTES;
   if (group < 1) return -1;
@@ -328,6 +367,7 @@ static int launch_token_bwd_tma_r(const ms_shape& s, const Plan& plan, const voi
   if (!p.error) return MS_ERR_LAUNCH;
   p.tokens = s.tokens; p.heads = heads; p.rotary_rows = s.rotary_rows; p.group_heads = group;
   p.slices = (s.tokens + 15) / 16; p.batch = s.batch;
+  p.probe = tuning_variant("MEMSOLVE_TOKEN_BWD_PROBE");
   p.base_raw = nullptr; p.hmat = nullptr; p.de_sys = nullptr; p.eta_slope = t.eta_slope; p.core_map = t.core_map;
   p.d_base = nullptr; p.d_eta_raw = nullptr; p.grad_scale = 1.f; p.complement = s.complement;
   if (core) {
@@ -335,9 +375,11 @@ static int launch_token_bwd_tma_r(const ms_shape& s, const Plan& plan, const voi
     p.d_base = core->d_base; p.d_eta_raw = core->d_eta_raw; p.grad_scale = core->grad_scale;
   }
   const long total = (long)p.slices * group;
-  long ctas = sm_count() / ((long)s.batch * groups);
+  // one CTA per SM: leave SMs for the per-head CTAs that ride along, so that the whole grid is
+  // resident at once (a CTA that has to wait for a free SM would run after all the others)
+  long ctas = (sm_count() - (core ? heads : 0)) / ((long)s.batch * groups);
   if (ctas < 1) ctas = 1;
-  const long need = (total + kTbWarps * 8 - 1) / (kTbWarps * 8);
+  const long need = (total + kTbWarps * 6 - 1) / (kTbWarps * 6);
   if (ctas > need) ctas = need < 1 ? 1 : need;
   p.work_ctas = (int)ctas;
   dim3 grid((unsigned)ctas + (core ? heads : 0), s.batch, groups);
@@ -345,15 +387,34 @@ static int launch_token_bwd_tma_r(const ms_shape& s, const Plan& plan, const voi
   const int core_bytes = (int)core_backward_smem_bytes(R) + 1024;
   if (core && smem_bytes < core_bytes) smem_bytes = core_bytes;
   if (s.rotary_rows > 0) {
-    auto kern = token_backward_tma_kernel<R, true>;
+    auto kern = token_backward_tma_kernel<R, true, Cfg>;
     if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
     kern<<<grid, kTbWarps * 32, smem_bytes, st>>>(map_a, map_c, map_y, map_w, map_q, map_s, map_oa, map_oc, p);
   } else {
-    auto kern = token_backward_tma_kernel<R, false>;
+    auto kern = token_backward_tma_kernel<R, false, Cfg>;
     if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
     kern<<<grid, kTbWarps * 32, smem_bytes, st>>>(map_a, map_c, map_y, map_w, map_q, map_s, map_oa, map_oc, p);
   }
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
+}
+
+template <int R>
+static int launch_token_bwd_tma_r(const ms_shape& s, const Plan& plan, const void* projected, const void* dy,
+                                  const float* cos, const float* sin, const float* counts, const ms_tape& t,
+                                  const void* gram_grad, const void* cross_grad, void* dprojected,
+                                  const CoreAdjoint* core, cudaStream_t st) {
+#define MS_TB_ARGS s, plan, projected, dy, cos, sin, counts, t, gram_grad, cross_grad, dprojected, core, st
+  switch (tuning_variant("MEMSOLVE_TOKEN_BWD_VARIANT")) {
+    case 1: return launch_token_bwd_tma_cfg<R, TokenBwdTmaCfg<R, 16, 2, 1>>(MS_TB_ARGS);
+    case 2: return launch_token_bwd_tma_cfg<R, TokenBwdTmaCfg<R, 12, 3, 1>>(MS_TB_ARGS);
+    case 3: return launch_token_bwd_tma_cfg<R, TokenBwdTmaCfg<R, 12, 2, 1>>(MS_TB_ARGS);
+    case 4: return launch_token_bwd_tma_cfg<R, TokenBwdTmaCfg<R, 8, 3, 2>>(MS_TB_ARGS);
+    case 5: return launch_token_bwd_tma_cfg<R, TokenBwdTmaCfg<R, 8, 3, 1>>(MS_TB_ARGS);
+  }
+  // rank 64: the resident matrices of one head take 48 KB, eight warps leave room for them
+  if (R == 64) return launch_token_bwd_tma_cfg<R, TokenBwdTmaCfg<R, 8, 3, 1>>(MS_TB_ARGS);
+  return launch_token_bwd_tma_cfg<R, TokenBwdTmaCfg<R, 12, 2, 1>>(MS_TB_ARGS);
+#undef MS_TB_ARGS
 }
 
 // MS_OK / error, or -1 when the shape is outside this kernel's envelope.
