@@ -152,15 +152,13 @@ Plan make_plan(const ms_shape& s) {
   }();
   // the TMA statistics kernels (rank 16/32, head dimension a multiple of 64) run one 8-warp CTA
   // per SM; the generic kernels two 4-warp CTAs
-  const bool tma_stats = !no_tma_env && (s.head_dim % 64) == 0 && (s.rank == 16 || s.rank == 32);
-  p.stats_cb = (tma_stats && s.rank == 32 && tuning_variant("MEMSOLVE_STATS_VARIANT") > 0) ? 32 : 64;
+  const bool wide_ctas = !no_tma_env && (s.head_dim % 64) == 0 && (s.rank == 16 || s.rank == 32);
   p.de_slots = 2 * p.dblocks;
-  const bool wide_ctas = tma_stats && p.stats_cb == 64;
   const long want = (wide_ctas ? 1L : 2L) * sm_count();
-  long per = (long)p.systems * (p.stats_cb == 32 ? s.head_dim / 32 : p.dblocks);
+  long per = (long)p.systems * p.dblocks;
   // rounded down so that the whole grid (plus the per-head CTAs that ride along with the forward
   // statistics of the TMA kernels) is resident in one wave
-  long chunks = (want - (tma_stats ? s.heads : 0)) / per;
+  long chunks = (want - (wide_ctas ? s.heads : 0)) / per;
   if (chunks < 1) chunks = 1;
   if (chunks > tiles) chunks = tiles;
   const int tiles_per_chunk = (int)((tiles + chunks - 1) / chunks);

@@ -5,7 +5,6 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
-#include <stdlib.h>
 
 #include "../../include/memsolve_b200.h"
 
@@ -17,9 +16,22 @@ static __device__ long long g_ms_ticks[64];
     if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)   \
       g_ms_ticks[i] = clock64();                                                     \
   } while (0)
+// per-warp start / end times in nanoseconds (slot = any index below 8192)
+static __device__ unsigned long long g_ms_stamps[8192][2];
+#define MS_STAMP(slot, which)                                                          \
+  do {                                                                                 \
+    if ((threadIdx.x & 31) == 0) {                                                     \
+      unsigned long long t_;                                                           \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                           \
+      g_ms_stamps[(slot) & 8191][which] = t_;                                          \
+    }                                                                                  \
+  } while (0)
 #else
 #define MS_TICK(i) \
   do {             \
+  } while (0)
+#define MS_STAMP(slot, which) \
+  do {                        \
   } while (0)
 #endif
 
@@ -34,7 +46,6 @@ constexpr int kChanBlock = 64;    // content channels handled per pass (one 128-
 struct Plan {
   int systems;       // B*H
   int dblocks;       // ceil(d / 64)
-  int stats_cb;      // channels per CTA of the token reductions (64, or 32 for two CTAs per SM)
   int de_slots;      // <dY,C> partial entries per (system, chunk): two per 64-channel block
   int dpad;          // d rounded up to a multiple of 8 (pitch of split coefficient tensors)
   int chunks;        // token chunks per system in the reductions
@@ -63,14 +74,6 @@ struct CoreAdjoint {
 Plan make_plan(const ms_shape& s);
 int check_shape(const ms_shape* s);
 int sm_count();
-// Developer switch: integer value of an environment variable (0 when unset) selecting one of the
-// compiled launch configurations of a kernel.
-inline int tuning_variant(const char* name) {
-  const char* v = getenv(name);
-  return v ? atoi(v) : 0;
-}
-// Raise a kernel's dynamic shared-memory limit once per (kernel, device); later calls are a
-// table lookup, so no function attribute is touched while a stream is being captured.
 int ensure_dynamic_smem(const void* kernel, int bytes);
 
 // ---------------------------------------------------------------------------------------

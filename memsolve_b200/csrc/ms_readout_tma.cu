@@ -43,8 +43,6 @@ struct ReadoutTmaParams {
   int tokens, heads, head_dim, rotary_rows, dblocks;
   int group_heads;   // heads per CTA group
   int slices;        // ceil(tokens / 16)
-  int probe;         // developer probe: 1 = no arithmetic, 2 = no arithmetic and no stores
-  int order;         // 1 = the warps of a CTA take the heads of one slice side by side
 };
 
 template <int R, bool ROT, class Cfg>
@@ -88,17 +86,8 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const int total = p.slices * mats;
   const int nwarps = gridDim.x * kRtWarps;
   const int per = (total + nwarps - 1) / nwarps;
-  int it0 = min(total, (blockIdx.x * kRtWarps + warp) * per);
-  int n_items = min(total, it0 + per) - it0;
-  int it_step = 1;
-  if (p.order == 1 && (kRtWarps % mats) == 0) {
-    // warp -> (head, block) pair warp % mats; slices strided over (CTA, warp / mats)
-    const int lanes = kRtWarps / mats;
-    const int first = blockIdx.x * lanes + warp / mats, stride = gridDim.x * lanes;
-    it0 = first * mats + warp % mats;
-    it_step = stride * mats;
-    n_items = first < p.slices ? (p.slices - first + stride - 1) / stride : 0;
-  }
+  const int it0 = min(total, (blockIdx.x * kRtWarps + warp) * per);
+  const int n_items = min(total, it0 + per) - it0;
 
   const int d = p.head_dim, half = d >> 1;
   const float n = p.counts ? p.counts[b] : (float)p.tokens;
@@ -108,22 +97,12 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const int mi = lane >> 3, mr = lane & 7;
 
   auto issue = [&](int k) {
-    const int e = it0 + k * it_step;
+    const int e = it0 + k;
     const int slice = e / mats, m = e - slice * mats;
     const int hl = m / p.dblocks, jb = m - hl * p.dblocks;
     const int h = h0 + hl;
     const uint32_t st = ring + (k % STAGES) * Cfg::STAGE;
     const uint32_t bar = mybar + (k % STAGES) * 8;
-    if (p.probe == 3) {          // content only
-      mbar_expect_tx(bar, Cfg::C_SLICE);
-      tma_load_3d(st, &map_c, p.heads * R + h * d + jb * 64, slice * 16, b, bar);
-      return;
-    }
-    if (p.probe == 4) {          // relation only
-      mbar_expect_tx(bar, Cfg::A_SLICE);
-      tma_load_3d(st + Cfg::C_SLICE, &map_a, h * R, slice * 16, b, bar);
-      return;
-    }
     mbar_expect_tx(bar, Cfg::A_SLICE + Cfg::C_SLICE);
     tma_load_3d(st, &map_c, p.heads * R + h * d + jb * 64, slice * 16, b, bar);
     tma_load_3d(st + Cfg::C_SLICE, &map_a, h * R, slice * 16, b, bar);
@@ -144,7 +123,7 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       tma_store_wait_read<STAGES - PRE - 1>();
       issue(k + PRE);
     }
-    const int e = it0 + k * it_step;
+    const int e = it0 + k;
     const int slice = e / mats, m = e - slice * mats;
     const int hl = m / p.dblocks, jb = m - hl * p.dblocks;
     const int h = h0 + hl;
@@ -153,7 +132,7 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const uint32_t wh_tile = w_base + (m * 2) * Cfg::W_BYTES;
     const uint32_t wl_tile = wh_tile + Cfg::W_BYTES;
 
-    if (ROT && (slice != tab_slice || jb != tab_jb) && p.probe == 0) {
+    if (ROT && (slice != tab_slice || jb != tab_jb)) {
       const int row0 = slice * 16;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -179,20 +158,6 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
 
-    if (p.probe != 0) {
-      if (p.probe == 1) {
-        fence_async_shared();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_3d(&map_y, h * d + jb * 64, slice * 16, b, c_tile);
-          tma_store_commit();
-        }
-      } else {
-        __syncwarp();
-        if (lane == 0) tma_store_commit();   // empty group keeps the wait bookkeeping uniform
-      }
-      continue;
-    }
     float acc[8][4];
 #pragma unroll
     for (int j = 0; j < 8; ++j)
@@ -282,8 +247,6 @@ static int launch_readout_tma_cfg(const ms_shape& s, const Plan& plan, const voi
   if (!p.error) return MS_ERR_LAUNCH;
   p.tokens = s.tokens; p.heads = heads; p.head_dim = d; p.rotary_rows = s.rotary_rows;
   p.dblocks = plan.dblocks; p.group_heads = group; p.slices = (s.tokens + 15) / 16;
-  p.probe = tuning_variant("MEMSOLVE_READOUT_PROBE");
-  p.order = tuning_variant("MEMSOLVE_READOUT_ORDER");
 
   const long total = (long)p.slices * group * plan.dblocks;
   long ctas = sm_count() / ((long)s.batch * groups);
@@ -309,15 +272,10 @@ template <int R>
 static int launch_readout_tma_r(const ms_shape& s, const Plan& plan, const void* projected, const float* cos,
                                 const float* sin, const float* counts, const ms_tape& t, void* mixed,
                                 cudaStream_t st) {
-  switch (tuning_variant("MEMSOLVE_READOUT_VARIANT")) {
-    case 1: return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 16, 3, 1>>(s, plan, projected, cos, sin, counts, t, mixed, st);
-    case 2: return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 16, 3, 2>>(s, plan, projected, cos, sin, counts, t, mixed, st);
-    case 3: return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 16, 2, 1>>(s, plan, projected, cos, sin, counts, t, mixed, st);
-    case 4: return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 12, 3, 1>>(s, plan, projected, cos, sin, counts, t, mixed, st);
-    case 5: return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 12, 4, 2>>(s, plan, projected, cos, sin, counts, t, mixed, st);
-    case 6: return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 8, 4, 2>>(s, plan, projected, cos, sin, counts, t, mixed, st);
-    case 7: return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 8, (R == 64 ? 3 : 4), (R == 64 ? 1 : 2)>>(s, plan, projected, cos, sin, counts, t, mixed, st);
-  }
+  // sixteen warps hide the fixed latencies of the epilogue; rank 64 keeps eight (its coefficient
+  // matrices take twice the shared memory)
+  if (R == 64)
+    return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 8, 3, 1>>(s, plan, projected, cos, sin, counts, t, mixed, st);
   return launch_readout_tma_cfg<R, ReadoutTmaCfg<R, 16, 3, 1>>(s, plan, projected, cos, sin, counts, t, mixed, st);
 }
 

@@ -56,7 +56,6 @@ struct StatsTmaParams {
   float* core_map;
   int* core_info;
   int complement;
-  int probe;   // developer probe: 1 = loads only
 };
 
 template <int R, bool GRAD, bool ROT, int CB, int STAGES_>
@@ -161,11 +160,6 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     ok = mbar_wait(mybar + (k % STAGES) * 8, (uint32_t)((k / STAGES) & 1));
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
-    if (p.probe != 0) {
-      __syncwarp();
-      if (k + STAGES < n_items && lane == 0) issue(k + STAGES);
-      continue;
-    }
 
     if (ROT || GRAD) {
       // elementwise pass over the 16 x CB slice, one 16-byte chunk (8 channels) at a time
@@ -385,15 +379,6 @@ int launch_stats_tma(const ms_shape& s, const Plan& plan, bool grad, const void*
   p.core_map = fuse_core ? core_tape->core_map : nullptr;
   p.core_info = fuse_core ? core_tape->core_info : nullptr;
   p.complement = s.complement;
-  p.probe = tuning_variant("MEMSOLVE_STATS_PROBE");
-  if (plan.stats_cb == 32) {
-    // two CTAs per SM, 32 channels each (rank 32 only; make_plan chooses)
-    if (s.rank != 32) return -1;
-    if (grad) return launch_stats_tma_r<32, true, 32, 2>(s, plan, projected, dy, cos, sin, p, false, st);
-    if (tuning_variant("MEMSOLVE_STATS_VARIANT") == 2)
-      return launch_stats_tma_r<32, false, 32, 2>(s, plan, projected, dy, cos, sin, p, fuse_core, st);
-    return launch_stats_tma_r<32, false, 32, 3>(s, plan, projected, dy, cos, sin, p, fuse_core, st);
-  }
   if (grad) {
     switch (s.rank) {
       case 16: return launch_stats_tma_r<16, true, 64, 2>(s, plan, projected, dy, cos, sin, p, false, st);

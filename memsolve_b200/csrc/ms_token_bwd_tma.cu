@@ -54,7 +54,6 @@ struct TokenBwdTmaParams {
   float* d_eta_raw;
   float grad_scale;
   int complement;
-  int probe;   // developer probe: 1 = no arithmetic, 2 = no arithmetic and no stores
 };
 
 // acc += rot(X) M^T for the 16 x 64 row operand `raw` (BF16 fragments of one warp) and a matrix
@@ -174,6 +173,7 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     tma_load_3d(st + 4096, &map_a, h * R, slice * 16, b, bar);
   };
 
+  MS_STAMP((blockIdx.z * gridDim.x + blockIdx.x) * WARPS + warp, 0);
   if (lane == 0) {
     for (int k = 0; k < PRE && k < n_items; ++k) issue(k);
   }
@@ -211,19 +211,6 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     ok = mbar_wait(mybar + (k % STAGES) * 8, (uint32_t)((k / STAGES) & 1));
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
-    if (p.probe != 0) {
-      fence_async_shared();
-      __syncwarp();
-      if (lane == 0) {
-        if (p.probe == 1) {
-          tma_store_3d(&map_oc, p.heads * R + h * 64, slice * 16, b, y_tile);
-          tma_store_3d(&map_oa, h * R, slice * 16, b, a_tile);
-        }
-        tma_store_commit();
-      }
-      continue;
-    }
-
     uint32_t af[R / 16][4];
 #pragma unroll
     for (int ks = 0; ks < R / 16; ++ks)
@@ -315,6 +302,7 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     tma_store_wait_all<0>();
     if (!ok) atomicExch(p.error, kErrBarrierTimeout);
   }
+  MS_STAMP((blockIdx.z * gridDim.x + blockIdx.x) * WARPS + warp, 1);
 }
 
 template <int R, class Cfg>
@@ -367,7 +355,6 @@ static int launch_token_bwd_tma_cfg(const ms_shape& s, const Plan& plan, const v
   if (!p.error) return MS_ERR_LAUNCH;
   p.tokens = s.tokens; p.heads = heads; p.rotary_rows = s.rotary_rows; p.group_heads = group;
   p.slices = (s.tokens + 15) / 16; p.batch = s.batch;
-  p.probe = tuning_variant("MEMSOLVE_TOKEN_BWD_PROBE");
   p.base_raw = nullptr; p.hmat = nullptr; p.de_sys = nullptr; p.eta_slope = t.eta_slope; p.core_map = t.core_map;
   p.d_base = nullptr; p.d_eta_raw = nullptr; p.grad_scale = 1.f; p.complement = s.complement;
   if (core) {
@@ -404,13 +391,6 @@ static int launch_token_bwd_tma_r(const ms_shape& s, const Plan& plan, const voi
                                   const void* gram_grad, const void* cross_grad, void* dprojected,
                                   const CoreAdjoint* core, cudaStream_t st) {
 #define MS_TB_ARGS s, plan, projected, dy, cos, sin, counts, t, gram_grad, cross_grad, dprojected, core, st
-  switch (tuning_variant("MEMSOLVE_TOKEN_BWD_VARIANT")) {
-    case 1: return launch_token_bwd_tma_cfg<R, TokenBwdTmaCfg<R, 16, 2, 1>>(MS_TB_ARGS);
-    case 2: return launch_token_bwd_tma_cfg<R, TokenBwdTmaCfg<R, 12, 3, 1>>(MS_TB_ARGS);
-    case 3: return launch_token_bwd_tma_cfg<R, TokenBwdTmaCfg<R, 12, 2, 1>>(MS_TB_ARGS);
-    case 4: return launch_token_bwd_tma_cfg<R, TokenBwdTmaCfg<R, 8, 3, 2>>(MS_TB_ARGS);
-    case 5: return launch_token_bwd_tma_cfg<R, TokenBwdTmaCfg<R, 8, 3, 1>>(MS_TB_ARGS);
-  }
   // rank 64: the resident matrices of one head take 48 KB, eight warps leave room for them
   if (R == 64) return launch_token_bwd_tma_cfg<R, TokenBwdTmaCfg<R, 8, 3, 1>>(MS_TB_ARGS);
   return launch_token_bwd_tma_cfg<R, TokenBwdTmaCfg<R, 12, 2, 1>>(MS_TB_ARGS);
