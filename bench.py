@@ -265,8 +265,8 @@ def time_kernels(layer, cfg, tokens, device, reps=10, warm=3):
 
 # DRAM bytes (read + write) of one launch at 32768 tokens, rank 32, from the ncu capture summarised in
 # profiles/mixer_kernels_c3_ncu_full.md.  Traffic of these streaming kernels grows in proportion to tokens.
-_NCU_DRAM_BYTES_C3 = {"stats_forward": 87.5e6, "readout": 101.2e6, "stats_backward": 138.2e6,
-                      "token_backward": 180.3e6}
+_NCU_DRAM_BYTES_C3 = {"stats_forward": 87.7e6, "readout": 104.9e6, "stats_backward": 138.6e6,
+                      "token_backward": 177.3e6}
 
 
 def _ncu_traffic(workload, kernel, tokens):
