@@ -157,8 +157,8 @@ Plan make_plan(const ms_shape& s) {
   const long want = (wide_ctas ? 1L : 2L) * sm_count();
   long per = (long)p.systems * p.dblocks;
   // rounded down so that the whole grid (plus the per-head CTAs that ride along with the forward
-  // statistics of the TMA kernels) is resident in one wave
-  long chunks = (want - (wide_ctas ? s.heads : 0)) / per;
+  // statistics) is resident in one wave
+  long chunks = (want - s.heads) / per;
   if (chunks < 1) chunks = 1;
   if (chunks > tiles) chunks = tiles;
   const int tiles_per_chunk = (int)((tiles + chunks - 1) / chunks);

@@ -676,9 +676,9 @@ __global__ void __launch_bounds__(kCompactThreads)
 core_forward_kernel(const float* __restrict__ base_raw, const float* __restrict__ eta_raw, int complement,
                     float* __restrict__ eta_out, float* __restrict__ slope_out, float* __restrict__ core_map,
                     int* __restrict__ core_info) {
-  extern __shared__ double dsm[];
-  core_forward_device<R>(base_raw, eta_raw, blockIdx.x, complement, eta_out, slope_out, core_map, core_info,
-                         reinterpret_cast<unsigned char*>(dsm), threadIdx.x, kCompactThreads);
+  extern __shared__ __align__(16) double dsm[];
+  core_forward_device<R, kCompactThreads>(base_raw, eta_raw, blockIdx.x, complement, eta_out, slope_out, core_map,
+                                          core_info, reinterpret_cast<unsigned char*>(dsm), threadIdx.x);
 }
 
 __global__ void __launch_bounds__(kCompactThreads)

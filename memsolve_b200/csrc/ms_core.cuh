@@ -10,10 +10,10 @@
 //
 // Replaces the reference's `complement`, `core_forward`, `compact_lu`, `compact_getrs`,
 // `eta_trace` and `core_backward` (memsolve/ball/cuda.py:2281-2360, 2517-2527;
-// csrc/ball/solvers.cuh:227-560).  The inverse of I+J is a Gauss-Jordan elimination with partial
-// pivoting in FP32, one matrix row per lane held in registers (rows are never moved between
-// lanes, the pivot order is recorded instead), polished by two Newton-Schulz steps
-// X <- X + X (I - A X) in FP64 carried out by the whole CTA; the generator J itself is FP64.
+// csrc/ball/solvers.cuh:227-560).  The inverse of I+J is a Gauss-Jordan elimination in FP32 by the
+// whole CTA (no pivoting: the symmetric part of I+J is positive definite), polished by one
+// Newton-Schulz step X <- X + X (I - A X) in FP64; the generator J itself is FP64.  All matrix
+// products run on 4 x 2 register tiles with vector loads from shared memory.
 #pragma once
 
 #include "ms_common.cuh"
@@ -27,30 +27,6 @@ __device__ __forceinline__ double softplus_shifted(float u) {
   return (double)(x > 20.f ? x : log1pf(expf(x)));
 }
 
-// L -> lc, J -> jm (FP64, pitch r+1).  All threads of the CTA take part.
-__device__ __forceinline__ void build_generator(const float* __restrict__ base, int r, double* lc, double* jm,
-                                                int tid, int nthreads) {
-  const int p = r + 1;
-  for (int i = tid; i < r * r; i += nthreads) {
-    const int row = i / r, col = i - row * r;
-    double v = 0.0;
-    if (row > col) v = (double)base[i];
-    else if (row == col) v = softplus_shifted(base[i]);
-    lc[row * p + col] = v;
-  }
-  __syncthreads();
-  for (int i = tid; i < r * r; i += nthreads) {
-    const int row = i / r, col = i - row * r;
-    const int kmax = row < col ? row : col;
-    double acc = 0.0;
-    for (int k = 0; k <= kmax; ++k) acc = fma(lc[row * p + k], lc[col * p + k], acc);
-    if (row < col) acc += (double)base[row * r + col];
-    if (row > col) acc -= (double)base[col * r + row];
-    jm[row * p + col] = acc;
-  }
-  __syncthreads();
-}
-
 __device__ __forceinline__ void eta_maps(float raw, float& eta, float& slope) {
   const float scale = 1.0f - 1.1920928955078125e-7f;  // 1 - FP32 epsilon
   eta = scale * tanhf(raw);
@@ -58,167 +34,224 @@ __device__ __forceinline__ void eta_maps(float raw, float& eta, float& slope) {
   slope = scale * 4.0f * q / ((1.0f + q) * (1.0f + q));
 }
 
-struct GjShared {
-  float* rowbuf;    // 2 * R floats
-  float* cand_v;    // 2 floats    (cross-warp pivot candidates)
-  int* cand_i;      // 2 ints
-  int* piv;         // R ints      pivot lane of step k
+// ---------------------------------------------------------------------------------------
+// small products on shared-memory operands, 4 x 2 register tiles, FP64 accumulation
+// ---------------------------------------------------------------------------------------
+// acc[r][c] += sum_{k < K} X[i0 + r][k] * Y[j(c)][k],  j(0) = j0, j(1) = j1   (K even)
+template <class TY>
+__device__ __forceinline__ void core_mm_nt(double (&acc)[4][2], const double* X, int ldx, const TY* Y, int ldy,
+                                           int i0, int j0, int j1, int K) {
+#pragma unroll 2
+  for (int k = 0; k < K; k += 2) {
+    double2 x[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) x[r] = *reinterpret_cast<const double2*>(X + (i0 + r) * ldx + k);
+    double y0[2], y1[2];
+    y0[0] = (double)Y[j0 * ldy + k]; y0[1] = (double)Y[j0 * ldy + k + 1];
+    y1[0] = (double)Y[j1 * ldy + k]; y1[1] = (double)Y[j1 * ldy + k + 1];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      acc[r][0] = fma(x[r].x, y0[0], acc[r][0]);
+      acc[r][0] = fma(x[r].y, y0[1], acc[r][0]);
+      acc[r][1] = fma(x[r].x, y1[0], acc[r][1]);
+      acc[r][1] = fma(x[r].y, y1[1], acc[r][1]);
+    }
+  }
+}
+
+// acc[r][c] += sum_{k < K} At[k][i0 + r] * B[k][j0 + c]     (At FP32, B FP64)
+__device__ __forceinline__ void core_mm_tn(double (&acc)[4][2], const float* At, int lda, const double* B, int ldb,
+                                           int i0, int j0, int K) {
+#pragma unroll 4
+  for (int k = 0; k < K; ++k) {
+    const float4 a = *reinterpret_cast<const float4*>(At + k * lda + i0);
+    const double2 b = *reinterpret_cast<const double2*>(B + k * ldb + j0);
+    const double av[4] = {(double)a.x, (double)a.y, (double)a.z, (double)a.w};
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      acc[r][0] = fma(av[r], b.x, acc[r][0]);
+      acc[r][1] = fma(av[r], b.y, acc[r][1]);
+    }
+  }
+}
+
+// layout of the core forward: NT threads, TPR neighbouring threads share one matrix row
+template <int R, int NT>
+struct CoreDims {
+  static constexpr int Q = NT / R;
+  static constexpr int TPR = Q >= 16 ? 16 : (Q >= 8 ? 8 : (Q >= 4 ? 4 : (Q >= 2 ? 2 : 1)));
+  static constexpr int CPT = R / TPR;
+  static constexpr int P2 = R + 2;    // pitch in doubles of the FP64 matrices (16-byte aligned rows)
+  static constexpr int RP = R + 4;    // pitch in floats of the FP32 matrix
+  static_assert(R * TPR <= NT && CPT * TPR == R, "core layout");
 };
 
-// Run-time loop over the elimination steps; the row registers are rotated by one after every
-// step, so the pivot column is always register 0 and all register indices stay compile-time
-// constants while the loop body fits the instruction cache.
-template <int R>
-__device__ __forceinline__ void gj_eliminate(float (&a)[R], const GjShared& sh, int lane_id, bool live, bool& used,
-                                             int& my_step, int& info) {
-  constexpr int NW = (R + 31) / 32;
-#pragma unroll 1
-  for (int K = 0; K < R; ++K) {
-    float v = (live && !used) ? fabsf(a[0]) : -1.0f;
-    int best = lane_id;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
-      const int ob = __shfl_xor_sync(0xffffffffu, best, o);
-      if (ov > v || (ov == v && ob < best)) { v = ov; best = ob; }
-    }
-    if (NW > 1) {
-      const int w = lane_id >> 5;
-      if ((lane_id & 31) == 0) { sh.cand_v[w] = v; sh.cand_i[w] = best; }
-      asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32));
-      const float v0 = sh.cand_v[0], v1 = sh.cand_v[1];
-      const int i0 = sh.cand_i[0], i1 = sh.cand_i[1];
-      if (v1 > v0) { v = v1; best = i1; } else { v = v0; best = i0; }
-    }
-    if (v == 0.0f && info == 0) info = K + 1;
-    float* rb = sh.rowbuf + (K & 1) * R;
-    if (lane_id == best) {
-      const float inv = __frcp_rn(a[0]);
-      a[0] = 1.0f;
-#pragma unroll
-      for (int j = 0; j < R; ++j) {
-        a[j] *= inv;
-        rb[j] = a[j];
-      }
-      used = true;
-      my_step = K;
-      sh.piv[K] = lane_id;
-    }
-    if (NW == 1) __syncwarp();
-    else asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32));
-    if (live && lane_id != best) {
-      const float f = a[0];
-      a[0] = 0.0f;
-#pragma unroll
-      for (int j = 0; j < R; ++j) a[j] = fmaf(-f, rb[j], a[j]);
-    }
-    const float first = a[0];
-#pragma unroll
-    for (int j = 0; j + 1 < R; ++j) a[j] = a[j + 1];
-    a[R - 1] = first;
-  }
-}
-
-// Approximate (FP32) inverse of the R x R matrix `src` (FP64, pitch R+1) into `dst` (FP64, pitch
-// R+1); run by the first ceil(R/32) warps of the CTA (the other threads return at once).
-// Returns 0, or k+1 when the k-th pivot was exactly zero.
-template <int R>
-__device__ __noinline__ int gj_inverse(const double* src, double* dst, const GjShared sh, int tid) {
-  constexpr int NW = (R + 31) / 32;
-  if (tid >= NW * 32) return 0;
-  const bool live = tid < R;
-  float a[R];
-#pragma unroll
-  for (int j = 0; j < R; ++j) a[j] = live ? (float)src[tid * (R + 1) + j] : 0.0f;
-  bool used = false;
-  int my_step = 0, info = 0;
-  gj_eliminate<R>(a, sh, tid, live, used, my_step, info);
-  if (NW == 1) __syncwarp();
-  else asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32));
-  // this lane holds row `my_step` of (P A)^-1; column k of it is column piv[k] of A^-1
-  if (live) {
-#pragma unroll
-    for (int k = 0; k < R; ++k) dst[my_step * (R + 1) + sh.piv[k]] = (double)a[k];
-  }
-  return info;
-}
-
 __host__ __device__ constexpr size_t core_forward_smem_bytes(int r) {
-  // A = I+J, X, residual (FP64) + row buffers + pivot bookkeeping
-  return (size_t)(3 * r * (r + 1)) * sizeof(double) + (size_t)(2 * r + 2) * sizeof(float) +
-         (size_t)(r + 2) * sizeof(int) + 32;
+  // A = I+J and one scratch matrix (FP64), the FP32 inverse, two pivot rows, the pivot flag
+  return (size_t)(2 * r * (r + 2)) * sizeof(double) + (size_t)(r * (r + 4) + 2 * (r + 4) + 4) * sizeof(float);
 }
 
-// One CTA computes one head.  `smem` must provide core_forward_smem_bytes(R), 8-byte aligned.
-template <int R>
+// In-place Gauss-Jordan inverse in FP32 by the whole CTA, without pivoting: I + J has a positive
+// definite symmetric part (I + L L^T), for which elimination in the natural order is stable.
+// Row i lives in the registers of TPR neighbouring lanes (columns q, q + TPR, ...).  Per step the
+// owners of the pivot row scale and publish it (double buffered, one CTA barrier per step); the
+// entry of each row in the next pivot column reaches the row's lanes by a shuffle inside the
+// group, which also hands the next pivot to the owners of the next pivot row.
+// a[] holds (I+J) on entry and its inverse on return; *zero_pivot is set to k+1 if pivot k is zero.
+template <int R, int NT>
+__device__ __forceinline__ void gj_inverse_cta(float (&a)[CoreDims<R, NT>::CPT], float* rowbuf, int* zero_pivot,
+                                               int tid) {
+  using D = CoreDims<R, NT>;
+  constexpr int TPR = D::TPR, CPT = D::CPT;
+  const int i = tid / TPR, q = tid % TPR;
+  const bool active = i < R;
+  const int lane = tid & 31;
+  const int group_base = lane & ~(TPR - 1);
+
+  // scale and publish pivot row k: `pivot` is the row's entry in column k
+  auto publish = [&](int k, int cK, int buf, float pivot) {
+    if (active && i == k) {
+      if (pivot == 0.0f) atomicMin(zero_pivot, k + 1);
+      float r0;
+      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(pivot));
+      const float inv = fmaf(r0, fmaf(-pivot, r0, 1.0f), r0);
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        a[c] = (c == cK && q == k % TPR) ? inv : a[c] * inv;
+        rowbuf[buf * (R + 4) + q + TPR * c] = a[c];
+      }
+    }
+  };
+  float f = __shfl_sync(0xffffffffu, a[0], group_base);   // entry of this row in column 0
+  publish(0, 0, 0, f);
+#pragma unroll
+  for (int cK = 0; cK < CPT; ++cK) {
+    for (int qK = 0; qK < TPR; ++qK) {
+      const int K = cK * TPR + qK;
+      __syncthreads();
+      const float* rb = rowbuf + (K & 1) * (R + 4);
+      if (active && i != K) {
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          const float rv = rb[q + TPR * c];
+          a[c] = (c == cK && q == qK) ? -f * rv : fmaf(-f, rv, a[c]);
+        }
+      }
+      if (K + 1 < R) {
+        const float sel = (qK + 1 < TPR) ? a[cK] : a[cK + 1 < CPT ? cK + 1 : cK];
+        f = __shfl_sync(0xffffffffu, sel, group_base + (qK + 1) % TPR);
+        publish(K + 1, (qK + 1 < TPR) ? cK : cK + 1, (K + 1) & 1, f);
+      }
+    }
+  }
+}
+
+// One CTA of NT threads computes one head.  `smem` must provide core_forward_smem_bytes(R),
+// 16-byte aligned.
+template <int R, int NT>
 __device__ __forceinline__ void core_forward_device(const float* __restrict__ base_raw,
                                                     const float* __restrict__ eta_raw, int h, int complement,
                                                     float* __restrict__ eta_out, float* __restrict__ slope_out,
                                                     float* __restrict__ core_map, int* __restrict__ core_info,
-                                                    unsigned char* smem, int tid, int nthreads) {
-  if (tid == nthreads - 1) {
+                                                    unsigned char* smem, int tid) {
+  using D = CoreDims<R, NT>;
+  constexpr int P2 = D::P2, RP = D::RP, TPR = D::TPR, CPT = D::CPT;
+  if (tid == NT - 1) {
     float e, s;
     eta_maps(eta_raw[h], e, s);
     eta_out[h] = e;
     slope_out[h] = s;
-    core_info[h] = 0;
   }
-  if (complement) return;
-  constexpr int P = R + 1;
-  double* am = reinterpret_cast<double*>(smem);  // I + J
-  double* xm = am + R * P;                       // L, then the inverse
-  double* rm = xm + R * P;                       // Newton-Schulz residual
-  GjShared sh;
-  sh.rowbuf = reinterpret_cast<float*>(rm + R * P);
-  sh.cand_v = sh.rowbuf + 2 * R;
-  sh.cand_i = reinterpret_cast<int*>(sh.cand_v + 2);
-  sh.piv = sh.cand_i + 2;
+  if (complement) {
+    if (tid == 0) core_info[h] = 0;
+    return;
+  }
+  double* am = reinterpret_cast<double*>(smem);   // I + J
+  double* rm = am + R * P2;                       // L, then the Newton-Schulz residual
+  float* xt = reinterpret_cast<float*>(rm + R * P2);   // transpose of the FP32 inverse
+  float* rowbuf = xt + R * RP;                    // 2 * (R + 4)
+  int* zero_pivot = reinterpret_cast<int*>(rowbuf + 2 * (R + 4));
+  const float* base = base_raw + (size_t)h * R * R;
   MS_TICK(20);
-  build_generator(base_raw + (size_t)h * R * R, R, xm, am, tid, nthreads);
-  for (int i = tid; i < R; i += nthreads) am[i * P + i] += 1.0;   // I + J
+
+  // L = tril(U,-1) + diag(softplus(diag U + c0))
+  for (int idx = tid; idx < R * R; idx += NT) {
+    const int row = idx / R, col = idx - row * R;
+    double v = 0.0;
+    if (row > col) v = (double)base[idx];
+    else if (row == col) v = softplus_shifted(base[idx]);
+    rm[row * P2 + col] = v;
+  }
+  if (tid == 0) *zero_pivot = R + 1;
+  __syncthreads();
+  // A = I + L L^T + triu(U,1) - triu(U,1)^T
+  constexpr int RTILES = (R / 4) * (R / 2);
+  for (int tile = tid; tile < RTILES; tile += NT) {
+    const int i0 = (tile / (R / 2)) * 4, j0 = tile % (R / 2), j1 = j0 + R / 2;
+    double acc[4][2] = {};
+    // L is lower triangular: the inner index stops at the smaller of row and column
+    const int kend = min(R, (min(i0 + 3, j1) + 2) & ~1);
+    core_mm_nt(acc, rm, P2, rm, P2, i0, j0, j1, kend);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int row = i0 + r;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int col = c == 0 ? j0 : j1;
+        double v = acc[r][c];
+        if (row < col) v += (double)base[row * R + col];
+        if (row > col) v -= (double)base[col * R + row];
+        if (row == col) v += 1.0;
+        am[row * P2 + col] = v;
+      }
+    }
+  }
   __syncthreads();
   MS_TICK(21);
-  const int info = gj_inverse<R>(am, xm, sh, tid);   // xm <- FP32-accurate inverse
+
+  // FP32 inverse
+  {
+    const int i = tid / TPR, q = tid % TPR;
+    float a[CPT];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) a[c] = i < R ? (float)am[i * P2 + q + TPR * c] : 0.f;
+    gj_inverse_cta<R, NT>(a, rowbuf, zero_pivot, tid);
+    if (i < R) {
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) xt[(q + TPR * c) * RP + i] = a[c];
+    }
+  }
   __syncthreads();
   MS_TICK(22);
-#pragma unroll 1
-  for (int sweep = 0; sweep < 2; ++sweep) {
-    // residual = I - A X
-    for (int i = tid; i < R * R; i += nthreads) {
-      const int row = i / R, col = i - row * R;
-      double acc = row == col ? 1.0 : 0.0;
-      for (int k = 0; k < R; ++k) acc = fma(-am[row * P + k], xm[k * P + col], acc);
-      rm[row * P + col] = acc;
-    }
-    __syncthreads();
-    // X <- X + X residual   (each thread keeps its entries until all reads of X are done)
-    constexpr int PER = (R * R + 127) / 128;   // callers run at least 128 threads
-    double upd[PER];
+
+  // one Newton-Schulz step in FP64:  X <- X + X (I - A X)
+  for (int tile = tid; tile < RTILES; tile += NT) {
+    const int i0 = (tile / (R / 2)) * 4, j0 = tile % (R / 2), j1 = j0 + R / 2;
+    double acc[4][2] = {};
+    core_mm_nt(acc, am, P2, xt, RP, i0, j0, j1, R);
 #pragma unroll
-    for (int e = 0; e < PER; ++e) {
-      const int i = tid + e * nthreads;
-      double acc = 0.0;
-      if (i < R * R) {
-        const int row = i / R, col = i - row * R;
-        acc = xm[row * P + col];
-        for (int k = 0; k < R; ++k) acc = fma(xm[row * P + k], rm[k * P + col], acc);
+    for (int r = 0; r < 4; ++r) {
+      rm[(i0 + r) * P2 + j0] = (i0 + r == j0 ? 1.0 : 0.0) - acc[r][0];
+      rm[(i0 + r) * P2 + j1] = (i0 + r == j1 ? 1.0 : 0.0) - acc[r][1];
+    }
+  }
+  __syncthreads();
+  for (int tile = tid; tile < RTILES; tile += NT) {
+    const int i0 = (tile / (R / 2)) * 4, j0 = (tile % (R / 2)) * 2;
+    double acc[4][2] = {};
+    core_mm_tn(acc, xt, RP, rm, P2, i0, j0, R);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int row = i0 + r, col = j0 + c;
+        const double x = (double)xt[col * RP + row] + acc[r][c];
+        core_map[(size_t)h * R * R + row * R + col] = (float)(2.0 * x - (row == col ? 1.0 : 0.0));
       }
-      upd[e] = acc;
     }
-    __syncthreads();
-#pragma unroll
-    for (int e = 0; e < PER; ++e) {
-      const int i = tid + e * nthreads;
-      if (i < R * R) xm[(i / R) * P + (i % R)] = upd[e];
-    }
-    __syncthreads();
   }
   MS_TICK(23);
-  for (int i = tid; i < R * R; i += nthreads) {
-    const int row = i / R, col = i - row * R;
-    core_map[(size_t)h * R * R + i] = (float)(2.0 * xm[row * P + col] - (row == col ? 1.0 : 0.0));
-  }
-  if (tid == 0 && info) core_info[h] = info;
+  if (tid == 0) core_info[h] = *zero_pivot <= R ? *zero_pivot : 0;
 }
 
 __host__ __device__ constexpr size_t core_backward_smem_bytes(int r) {

@@ -84,8 +84,8 @@ stats_kernel(const StatsParams p) {
   if (!GRAD && chunk == p.chunks) {
     // spare column of the grid: the per-head core runs beside the token reduction
     if (dblk == 0 && sys < p.heads)
-      core_forward_device<R>(p.base_raw, p.eta_raw, sys, p.complement, p.eta, p.eta_slope, p.core_map,
-                             p.core_info, smem_gen, tid, NT);
+      core_forward_device<R, NT>(p.base_raw, p.eta_raw, sys, p.complement, p.eta, p.eta_slope, p.core_map,
+                                 p.core_info, smem_gen, tid);
     return;
   }
   const int b = sys / p.heads, h = sys - b * p.heads;
