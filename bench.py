@@ -302,6 +302,7 @@ def run_ours(args, cfg):
     if world > 1:
         sp = SequenceParallel.create(tokens)
         counts = sp.valid_counts(None, batch_size=1, device=device)
+        sp.overlap_gradient_sum(layer)   # parameter-gradient SUMs overlap the rest of the backward pass
 
     def step(xin, grad_out):
         layer.zero_grad(set_to_none=True)

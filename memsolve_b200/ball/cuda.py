@@ -568,9 +568,10 @@ def _linear_forward(value, weight_bf16, bias, output_dtype, output_mask, input_m
 
 
 def _linear_backward(grad_output, value, weight_bf16, output_mask, input_mask, needs, value_dtype,
-                     weight_dtype, bias):
+                     weight_dtype, bias, out_features=None):
     need_dx, need_dw, need_db = needs
-    out_features = weight_bf16.shape[0]
+    if out_features is None:
+        out_features = weight_bf16.shape[0]
     flat_g = grad_output.reshape(-1, out_features)
     flat_g = _masked_rows(flat_g, None if output_mask is None else output_mask.reshape(-1))
     g_bf16 = flat_g if flat_g.dtype == torch.bfloat16 else flat_g.to(torch.bfloat16)
@@ -592,23 +593,50 @@ def _linear_backward(grad_output, value, weight_bf16, output_mask, input_mask, n
 
 
 class _TensorCoreLinear(torch.autograd.Function):
-    """Projection with BF16 multiplicands, FP32 accumulation and dtype-aware stores."""
+    """Projection with BF16 multiplicands, FP32 accumulation and dtype-aware stores.
+
+    This node owns the data path only (forward GEMM, input gradient); the gradients of weight
+    and bias come from `_ParameterGradients`, a node of its own that autograd runs first, so a
+    hook on the weight (a sequence-parallel gradient SUM, say) starts while the input-gradient
+    GEMM still runs.
+    """
 
     @staticmethod
-    def forward(ctx, value, weight, bias, output_dtype, fuse_weight_bias_grad, output_mask, input_mask):
+    def forward(ctx, value, weight, bias, output_dtype, output_mask, input_mask):
         weight_bf16 = weight.to(torch.bfloat16)
-        ctx.save_for_backward(value, weight_bf16, output_mask, input_mask, bias)
-        ctx.value_dtype, ctx.weight_dtype = value.dtype, weight.dtype
+        ctx.save_for_backward(weight_bf16, output_mask, input_mask)
+        ctx.value_dtype = value.dtype
         return _linear_forward(value, weight_bf16, bias, output_dtype, output_mask, input_mask)
 
     @staticmethod
     @once_differentiable
     def backward(ctx, grad_output):
-        value, weight_bf16, output_mask, input_mask, bias = ctx.saved_tensors
-        needs = (ctx.needs_input_grad[0], ctx.needs_input_grad[1], bias is not None and ctx.needs_input_grad[2])
-        gv, gw, gb = _linear_backward(grad_output, value, weight_bf16, output_mask, input_mask, needs,
-                                      ctx.value_dtype, ctx.weight_dtype, bias)
-        return gv, gw, gb, None, None, None, None
+        weight_bf16, output_mask, input_mask = ctx.saved_tensors
+        gv = None
+        if ctx.needs_input_grad[0]:
+            gv = _linear_backward(grad_output, None, weight_bf16, output_mask, input_mask, (True, False, False),
+                                  ctx.value_dtype, None, None)[0]
+        return gv, None, None, None, None, None
+
+
+class _ParameterGradients(torch.autograd.Function):
+    """Identity on a projection's output; its backward forms dW = dY^T X and db = sum dY."""
+
+    @staticmethod
+    def forward(ctx, out, value, weight, bias, output_mask, input_mask):
+        ctx.save_for_backward(value, output_mask, input_mask, bias)
+        ctx.weight_dtype = weight.dtype
+        ctx.out_features = weight.shape[0]
+        return out.view_as(out)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output):
+        value, output_mask, input_mask, bias = ctx.saved_tensors
+        needs = (False, ctx.needs_input_grad[2], bias is not None and ctx.needs_input_grad[3])
+        _, gw, gb = _linear_backward(grad_output, value, None, output_mask, input_mask, needs, None,
+                                     ctx.weight_dtype, bias, out_features=ctx.out_features)
+        return grad_output, None, gw, gb, None, None
 
 
 def tensor_core_linear(value, weight, bias=None, *, output_dtype=None, fuse_weight_bias_grad=False,
@@ -617,7 +645,11 @@ def tensor_core_linear(value, weight, bias=None, *, output_dtype=None, fuse_weig
     if value.shape[-1] != weight.shape[-1]:
         raise ValueError(
             f"tensor_core_linear input and weight features must agree, got {value.shape[-1]} and {weight.shape[-1]}")
-    return _TensorCoreLinear.apply(value, weight, bias, output_dtype, fuse_weight_bias_grad, output_mask, input_mask)
+    out = _TensorCoreLinear.apply(value, weight.detach(), None if bias is None else bias.detach(), output_dtype,
+                                  output_mask, input_mask)
+    if torch.is_grad_enabled() and (weight.requires_grad or (bias is not None and bias.requires_grad)):
+        out = _ParameterGradients.apply(out, value.detach(), weight, bias, output_mask, input_mask)
+    return out
 
 
 class _RecomputeOutputLinear(torch.autograd.Function):

@@ -1,41 +1,97 @@
-"""Exact sequence parallelism for the MemSolve layer.
+"""Sequence parallelism for the MemSolve layer: the token axis is split over the ranks of a
+process group, every rank keeps a full copy of the weights.
 
-Each rank owns a contiguous slice of the token axis of the same samples and a
-full copy of the weights.  Because the Gram/moment statistics ``(G, Q)`` and the
-adjoint statistics ``(E, de)`` are sums over tokens, one SUM all-reduce of
-``O(B*H*(r*r + r*d))`` floats per direction makes every rank's compact solve
-identical to the unsharded one; nothing of size N crosses the interconnect.
+Why it is exact: the Gram/moment statistics ``(G, Q)`` of the forward pass and the adjoint
+statistics ``(E, de)`` of the backward pass are plain sums over tokens.  One SUM all-reduce of
+``O(B*H*(r*r + r*d))`` floats per direction therefore gives every rank the statistics of the
+whole sequence, the r x r solves that follow are identical on all ranks, and nothing of size N
+ever crosses NVLink.
 
-API and semantics follow the reference's ``integrations.distributed.SequenceParallel``
-(integrations/distributed.py:14-99): ``create``, ``world_size``, ``global_length``,
-``offset``, ``validate``, ``sum_``, ``sum_tensors``, ``valid_counts``,
-``reduce_gradients_``.  The collective is ``torch.distributed.all_reduce`` (NCCL
-over NVLink on GPUs, gloo in CPU tests).
+The public surface is the one of the reference's ``integrations.distributed.SequenceParallel``
+(integrations/distributed.py:14-99): the constructor fields ``group``, ``shard_lengths``,
+``rank``; ``create``, ``world_size``, ``global_length``, ``offset``, ``validate``, ``sum_``,
+``sum_tensors``, ``valid_counts`` and ``reduce_gradients_`` with the same arguments, results and
+exceptions.  Added here: ``overlap_gradient_sum``, which starts the SUM of each parameter
+gradient from an autograd hook, on NCCL's own stream, while the rest of the backward pass still
+runs.  Collectives are ``torch.distributed`` calls (NCCL over NVLink on GPUs, gloo in CPU tests).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+import itertools
+from typing import Iterable, Sequence
 
 import torch
 import torch.distributed as dist
 
+_SUM = dist.ReduceOp.SUM
 
-@dataclass(frozen=True)
+
+class _GradientOverlap:
+    """Hooks of one module that launch asynchronous gradient SUMs; returned by
+    ``SequenceParallel.overlap_gradient_sum``.  ``remove()`` detaches the hooks."""
+
+    def __init__(self, owner: "SequenceParallel", module: torch.nn.Module):
+        self._owner = owner
+        self._works: dict[int, object] = {}
+        self._handles = [p.register_post_accumulate_grad_hook(self._launch)
+                         for p in module.parameters() if p.requires_grad]
+
+    def _launch(self, parameter: torch.Tensor) -> None:
+        self._works[id(parameter)] = dist.all_reduce(parameter.grad, op=_SUM, group=self._owner.group,
+                                                     async_op=True)
+
+    def finish(self, parameters: Sequence[torch.Tensor]) -> None:
+        """Sum what no hook has started (a gradient written without autograd), then wait for all."""
+        for parameter in parameters:
+            if id(parameter) not in self._works:
+                self._launch(parameter)
+        works, self._works = self._works, {}
+        for work in works.values():
+            work.wait()
+
+    def remove(self) -> None:
+        for handle in self._handles:
+            handle.remove()
+        self._handles = []
+        self._works = {}
+
+
 class SequenceParallel:
-    group: object
-    shard_lengths: tuple[int, ...]
-    rank: int
+    """Layout of one sharded sequence: the process group, every rank's shard length, this rank."""
 
+    __slots__ = ("group", "shard_lengths", "rank", "_starts", "_overlaps")
+
+    def __init__(self, group, shard_lengths: Iterable[int], rank: int):
+        self.group = group
+        self.shard_lengths = tuple(int(length) for length in shard_lengths)
+        self.rank = int(rank)
+        self._starts = (0, *itertools.accumulate(self.shard_lengths))
+        self._overlaps: dict[int, _GradientOverlap] = {}
+
+    def __repr__(self) -> str:
+        return f"SequenceParallel(shard_lengths={self.shard_lengths}, rank={self.rank})"
+
+    def __eq__(self, other: object) -> bool:
+        if not isinstance(other, SequenceParallel):
+            return NotImplemented
+        return (self.group, self.shard_lengths, self.rank) == (other.group, other.shard_lengths, other.rank)
+
+    def __hash__(self) -> int:
+        return hash((id(self.group), self.shard_lengths, self.rank))
+
+    # ---------------------------------------------------------------- layout
     @classmethod
     def create(cls, local_length: int, group=None) -> "SequenceParallel":
-        """Exchange shard lengths once per layout (host-side object gather)."""
+        """Collect the shard lengths of all ranks (one host-side object gather; call it once per
+        layout and outside CUDA-graph capture)."""
         if not dist.is_initialized():
             raise RuntimeError("initialize torch.distributed before sequence parallelism")
-        lengths: list = [None] * dist.get_world_size(group)
-        dist.all_gather_object(lengths, int(local_length), group=group)
-        if any(length < 1 for length in lengths):
+        world = dist.get_world_size(group)
+        gathered: list = [None for _ in range(world)]
+        dist.all_gather_object(gathered, int(local_length), group=group)
+        if min(gathered) < 1:
             raise ValueError("sequence shards must be nonempty")
-        return cls(group, tuple(int(v) for v in lengths), dist.get_rank(group))
+        return cls(group, gathered, dist.get_rank(group))
 
     @property
     def world_size(self) -> int:
@@ -43,67 +99,116 @@ class SequenceParallel:
 
     @property
     def global_length(self) -> int:
-        return sum(self.shard_lengths)
+        return self._starts[-1]
 
     @property
     def offset(self) -> int:
-        """Global index of this rank's first token (start of its rotary positions)."""
-        return sum(self.shard_lengths[: self.rank])
+        """Global index of this rank's first token (where its rotary positions start)."""
+        return self._starts[self.rank]
+
+    @property
+    def local_length(self) -> int:
+        return self.shard_lengths[self.rank]
 
     def validate(self, local_length: int, operator_rank: int) -> None:
-        if local_length != self.shard_lengths[self.rank]:
+        if local_length != self.local_length:
             raise ValueError("local sequence length differs from the sequence-parallel layout")
         if self.global_length <= operator_rank:
             raise ValueError(
                 "sequence parallelism requires global sequence length > rank; use an unsharded short sequence")
 
+    # ---------------------------------------------------------------- collectives
     def sum_(self, tensor: torch.Tensor) -> torch.Tensor:
-        if self.world_size > 1:
-            dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=self.group)
+        """In-place SUM over the group (a no-op for a single rank)."""
+        if self.world_size != 1:
+            dist.all_reduce(tensor, op=_SUM, group=self.group)
         return tensor
 
     def sum_tensors(self, *tensors: torch.Tensor):
-        """One collective for several tensors; returns views of the summed buffer."""
+        """SUM several tensors with one collective.  A single contiguous tensor is summed in place;
+        otherwise the values travel in one packed buffer and views of it are returned."""
         if self.world_size == 1:
             return tensors
         if len(tensors) == 1 and tensors[0].is_contiguous():
             self.sum_(tensors[0].view(-1))
             return tensors
-        flat = torch.cat([t.reshape(-1) for t in tensors])
-        self.sum_(flat)
-        parts = flat.split([t.numel() for t in tensors])
-        return tuple(part.view_as(t) for part, t in zip(parts, tensors))
+        sizes = [t.numel() for t in tensors]
+        packed = torch.empty(sum(sizes), dtype=tensors[0].dtype, device=tensors[0].device)
+        slots = packed.split(sizes)
+        for slot, t in zip(slots, tensors):
+            slot.copy_(t.reshape(-1))
+        self.sum_(packed)
+        return tuple(slot.view_as(t) for slot, t in zip(slots, tensors))
 
     def valid_counts(self, mask, *, batch_size=None, device=None) -> torch.Tensor:
-        """Global max(valid tokens, 1) per sample as FP32 [B]; the clamp follows the SUM."""
-        local = self.shard_lengths[self.rank]
-        if mask is None:
-            if batch_size is None or device is None:
-                raise ValueError("unmasked counts require batch_size and device")
-            counts = torch.full((batch_size,), float(local), device=device, dtype=torch.float32)
-        else:
-            if mask.dtype != torch.bool or mask.ndim != 2 or mask.shape[1] != local:
+        """Valid tokens per sample over the whole sequence, FP32 ``[B]``, at least 1.
+
+        Every rank must call this, also one whose own shard has no padding and passes
+        ``mask=None``: the SUM is a collective.  The lower bound is applied after the SUM.
+        """
+        if mask is not None:
+            if mask.dtype != torch.bool or mask.ndim != 2 or mask.shape[1] != self.local_length:
                 raise ValueError("mask must be boolean [batch, local_length]")
-            counts = mask.sum(-1, dtype=torch.float32)
-        return self.sum_(counts).clamp_min_(1)
+            local = mask.sum(dim=-1, dtype=torch.float32)
+        elif batch_size is None or device is None:
+            raise ValueError("unmasked counts require batch_size and device")
+        else:
+            local = torch.full((batch_size,), float(self.local_length), dtype=torch.float32, device=device)
+        return self.sum_(local).clamp_min_(1)
+
+    # ---------------------------------------------------------------- parameter gradients
+    def overlap_gradient_sum(self, module: torch.nn.Module) -> _GradientOverlap:
+        """Start the SUM of each parameter gradient of `module` as soon as autograd has written it.
+
+        The all-reduces run on the communication stream of the process group and overlap the
+        remaining backward kernels; ``reduce_gradients_(module)`` then only waits for them.  Use it
+        when every ``reduce_gradients_`` follows exactly one backward pass: with gradient
+        accumulation over several backward passes an early SUM would count the earlier passes once
+        per rank.  Returns the handle whose ``remove()`` restores the plain behaviour.
+        """
+        overlap = self._overlaps.get(id(module))
+        if overlap is None:
+            overlap = self._overlaps[id(module)] = _GradientOverlap(self, module)
+        return overlap
 
     @torch.no_grad()
     def reduce_gradients_(self, module: torch.nn.Module) -> None:
-        """SUM the gradients of replicated parameters, one flat collective per (device, dtype)."""
-        params = [p for p in module.parameters() if p.requires_grad]
-        if self.world_size == 1 or not params:
+        """SUM the gradients of the replicated parameters over the group, in place.
+
+        Call it once after the (accumulated) backward pass and before clipping or the optimizer
+        step, and do not average over this group as well.  Every trainable parameter must have a
+        gradient: the set of collectives is then the same on all ranks without any host check, and
+        the call can be captured in a CUDA graph together with forward and backward.
+        """
+        trainable = [p for p in module.parameters() if p.requires_grad]
+        if self.world_size == 1 or not trainable:
             return
-        if any(p.grad is None for p in params):
+        if not all(p.grad is not None for p in trainable):
             raise ValueError(
                 "sequence gradient SUM requires a gradient for every trainable parameter; freeze unused parameters")
-        buckets: dict = {}
-        for p in params:
-            buckets.setdefault((p.device, p.dtype), []).append(p.grad)
-        for grads in buckets.values():
-            flat = torch.cat([g.reshape(-1) for g in grads])
-            self.sum_(flat)
-            parts = flat.split([g.numel() for g in grads])
-            torch._foreach_copy_(grads, [part.view_as(g) for g, part in zip(grads, parts)])
+        overlap = self._overlaps.get(id(module))
+        if overlap is not None and overlap._handles:
+            overlap.finish(trainable)
+            return
+        self._sum_in_place([p.grad for p in trainable])
+
+    def _sum_in_place(self, tensors: Sequence[torch.Tensor]) -> None:
+        """One coalesced collective over all tensors (no packing copies) where the backend offers
+        it, else one packed buffer per (device, dtype)."""
+        manager = getattr(dist, "_coalescing_manager", None)
+        if manager is not None and tensors[0].is_cuda:
+            with manager(group=self.group, device=tensors[0].device, async_ops=False):
+                for t in tensors:
+                    dist.all_reduce(t, op=_SUM, group=self.group)
+            return
+        groups: dict = {}
+        for t in tensors:
+            groups.setdefault((t.device, t.dtype), []).append(t)
+        for members in groups.values():
+            summed = self.sum_tensors(*members)
+            for target, value in zip(members, summed):
+                if target.data_ptr() != value.data_ptr():
+                    target.copy_(value)
 
 
 __all__ = ["SequenceParallel"]

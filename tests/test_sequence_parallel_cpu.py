@@ -70,6 +70,30 @@ def _worker(rank: int, world: int, path: str, lengths, results):
         with pytest.raises(ValueError, match="requires a gradient for every trainable parameter"):
             sp.reduce_gradients_(lin)
 
+        # overlapped SUM: hooks launch the all-reduce of each gradient during backward, the call
+        # afterwards only waits; a gradient written by hand (no hook) is summed by the call itself
+        net = torch.nn.Sequential(torch.nn.Linear(4, 3), torch.nn.Tanh(), torch.nn.Linear(3, 2))
+        with torch.no_grad():
+            for k, p in enumerate(net.parameters()):
+                p.copy_(torch.linspace(-1, 1, p.numel()).reshape(p.shape) * (k + 1) / 4)
+        data = torch.arange(8.0).reshape(2, 4) * (rank + 1)
+        net(data).square().sum().backward()
+        local = [p.grad.clone() for p in net.parameters()]
+        net.zero_grad(set_to_none=True)
+        handle = sp.overlap_gradient_sum(net)
+        assert sp.overlap_gradient_sum(net) is handle
+        net(data).square().sum().backward()
+        sp.reduce_gradients_(net)
+        for p, mine in zip(net.parameters(), local):
+            both = [torch.zeros_like(mine) for _ in range(world)]
+            dist.all_gather(both, mine)
+            assert torch.allclose(p.grad, sum(both), rtol=1e-6, atol=1e-6)
+        for p in net.parameters():
+            p.grad = torch.full_like(p, float(rank + 1))
+        sp.reduce_gradients_(net)
+        assert all(torch.equal(p.grad, torch.full_like(p, float(tot))) for p in net.parameters())
+        handle.remove()
+
         # algebra of the sharded mixer (CPU oracle stages): statistics scaled by the global count add up
         heads, rank_r, d = 2, 16, 8
         gen = torch.Generator().manual_seed(7)

@@ -36,10 +36,12 @@ def _worker(rank, path, results):
         cuda.load()
         cases = [(16, (97, 100), False, False), (32, (512, 480), True, False), (64, (200, 184), True, True),
                  (32, (19, 22), False, True)]
-        for rank_r, lengths, rotary, masked in cases:
+        for case, (rank_r, lengths, rotary, masked) in enumerate(cases):
             sp = SequenceParallel.create(lengths[rank])
             torch.manual_seed(913 + rank_r)
             layer = MemSolve(MemSolveConfig(128, 2, rank=rank_r, bias=True, rotary=rotary)).cuda()
+            if case % 2 == 0:
+                sp.overlap_gradient_sum(layer)   # gradient SUMs start from autograd hooks
             with torch.no_grad():
                 layer.core_base_raw.normal_(std=0.1)
             total = sum(lengths)
