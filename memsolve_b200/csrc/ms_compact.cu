@@ -193,29 +193,37 @@ __device__ __forceinline__ void stage_partials(uint32_t dst, const float* src, i
   }
 }
 
-// out[e] = sum over chunks, in chunk order, of src[c * stride + off[e]] for four entries at a time
-// (independent chains); entries with ok[e] false stay zero
-template <class PTR>
-__device__ __forceinline__ void sum_chunks4(PTR src, size_t stride, int nch, const int (&off)[4], const bool (&ok)[4],
-                                            float (&acc)[4]) {
+// acc[e] = sum over chunks, in chunk order, of src[c * stride + off[e]] for four entries at a time
+// (independent chains, pointers advanced by the stride); entries with ok[e] false give zero
+template <class T>
+__device__ __forceinline__ void sum_chunks4(const T* src, int stride, int nch, const int (&off)[4],
+                                            const bool (&ok)[4], float (&acc)[4]) {
+  const T* ptr[4];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) acc[e] = 0.f;
+  for (int e = 0; e < 4; ++e) {
+    ptr[e] = src + (ok[e] ? off[e] : 0);
+    acc[e] = 0.f;
+  }
   int c = 0;
   for (; c + 2 <= nch; c += 2) {
     float v[2][4];
 #pragma unroll
-    for (int k = 0; k < 2; ++k)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) v[k][e] = ok[e] ? src[(size_t)(c + k) * stride + off[e]] : 0.f;
+    for (int e = 0; e < 4; ++e) {
+      v[0][e] = ptr[e][0];
+      v[1][e] = ptr[e][stride];
+      ptr[e] += 2 * stride;
+    }
 #pragma unroll
     for (int k = 0; k < 2; ++k)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[e] += v[k][e];
   }
-  for (; c < nch; ++c) {
+  if (c < nch) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) acc[e] += ok[e] ? src[(size_t)c * stride + off[e]] : 0.f;
+    for (int e = 0; e < 4; ++e) acc[e] += ptr[e][0];
   }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) acc[e] = ok[e] ? acc[e] : 0.f;
 }
 
 // acc[r][c] += sum_{k0 <= k < k1} At[k][i0 + r] * B[k][j(c)],  j(0) = j0, j(1) = j1
@@ -318,8 +326,8 @@ compact_forward_kernel(const CompactFwdParams p) {
       off[e] = i0 + e * kCompactThreads;
       valid[e] = off[e] < R * R;
     }
-    if (staged) sum_chunks4(stage, (size_t)p.pf, nch, off, valid, acc);
-    else sum_chunks4(src, (size_t)p.pf, nch, off, valid, acc);
+    if (staged) sum_chunks4(stage, p.pf, nch, off, valid, acc);
+    else sum_chunks4(src, p.pf, nch, off, valid, acc);
 #pragma unroll
     for (int e = 0; e < 4; ++e)
       if (valid[e]) gs[off[e]] = acc[e] * inv_n;
@@ -337,7 +345,9 @@ compact_forward_kernel(const CompactFwdParams p) {
   constexpr int TILES = (R / 4) * 32;   // 4 x 2 tiles of an r x 64 block
   for (int jb = 0; jb < p.dblocks; ++jb) {
     const int d0 = jb * 64, dv = min(64, d - d0);
+    MS_TICK(30);
     if (staged && jb == 0) ok = mbar_wait(smem_u32(bar) + 8, 0) && ok;
+    MS_TICK(31);
     for (int i0 = tid; i0 < R * 64; i0 += 4 * kCompactThreads) {
       int off[4];
       bool valid[4];
@@ -348,8 +358,8 @@ compact_forward_kernel(const CompactFwdParams p) {
         valid[e] = c < dv;
         off[e] = R * R + row * d + d0 + (valid[e] ? c : 0);
       }
-      if (staged) sum_chunks4(stage, (size_t)p.pf, nch, off, valid, acc);
-      else sum_chunks4(src, (size_t)p.pf, nch, off, valid, acc);
+      if (staged) sum_chunks4(stage, p.pf, nch, off, valid, acc);
+      else sum_chunks4(src, p.pf, nch, off, valid, acc);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = i0 + e * kCompactThreads;
@@ -527,8 +537,8 @@ compact_backward_kernel(const CompactBwdParams p) {
         off[e] = row * d + d0 + (valid[e] ? c : 0);
         zv[e] = valid[e] ? p.state[(size_t)sys * R * d + off[e]] : 0.f;
       }
-      if (staged) sum_chunks4(stage, (size_t)p.pf, nch, off, valid, acc);
-      else sum_chunks4(src, (size_t)p.pf, nch, off, valid, acc);
+      if (staged) sum_chunks4(stage, p.pf, nch, off, valid, acc);
+      else sum_chunks4(src, p.pf, nch, off, valid, acc);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = i0 + e * kCompactThreads;
