@@ -96,20 +96,40 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const int g = lane >> 2, tq = lane & 3;
   const int mi = lane >> 3, mr = lane & 7;
 
-  auto issue = [&](int k) {
-    const int e = it0 + k;
-    const int slice = e / mats, m = e - slice * mats;
-    const int hl = m / p.dblocks, jb = m - hl * p.dblocks;
-    const int h = h0 + hl;
-    const uint32_t st = ring + (k % STAGES) * Cfg::STAGE;
-    const uint32_t bar = mybar + (k % STAGES) * 8;
+  // position of an item: (slice, head in group, channel block); advanced without divisions
+  struct Cursor {
+    int slice, hl, jb, stage;
+  };
+  auto advance = [&](Cursor& c) {
+    if (++c.jb == p.dblocks) {
+      c.jb = 0;
+      if (++c.hl == gh) {
+        c.hl = 0;
+        ++c.slice;
+      }
+    }
+    c.stage = c.stage + 1 == STAGES ? 0 : c.stage + 1;
+  };
+  Cursor ahead;   // next item to load
+  ahead.slice = it0 / mats;
+  ahead.hl = (it0 - ahead.slice * mats) / p.dblocks;
+  ahead.jb = it0 - ahead.slice * mats - ahead.hl * p.dblocks;
+  ahead.stage = 0;
+  Cursor cur = ahead;   // item being computed
+  uint32_t parity = 0;
+
+  auto issue = [&](const Cursor& c) {
+    const int h = h0 + c.hl;
+    const uint32_t st = ring + c.stage * Cfg::STAGE;
+    const uint32_t bar = mybar + c.stage * 8;
     mbar_expect_tx(bar, Cfg::A_SLICE + Cfg::C_SLICE);
-    tma_load_3d(st, &map_c, p.heads * R + h * d + jb * 64, slice * 16, b, bar);
-    tma_load_3d(st + Cfg::C_SLICE, &map_a, h * R, slice * 16, b, bar);
+    tma_load_3d(st, &map_c, p.heads * R + h * d + c.jb * 64, c.slice * 16, b, bar);
+    tma_load_3d(st + Cfg::C_SLICE, &map_a, h * R, c.slice * 16, b, bar);
   };
 
-  if (lane == 0) {
-    for (int k = 0; k < PRE && k < n_items; ++k) issue(k);
+  for (int k = 0; k < PRE && k < n_items; ++k) {
+    if (lane == 0) issue(ahead);
+    advance(ahead);
   }
   bool ok = mbar_wait(wbar, 0);
   ok = __all_sync(0xffffffffu, ok);
@@ -118,16 +138,18 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   int tab_slice = -1, tab_jb = -1;
 
   for (int k = 0; k < n_items && ok; ++k) {
-    if (lane == 0 && k + PRE < n_items) {
-      // the buffer being refilled was the source of the store of item k + PRE - STAGES
-      tma_store_wait_read<STAGES - PRE - 1>();
-      issue(k + PRE);
+    if (k + PRE < n_items) {
+      if (lane == 0) {
+        // the buffer being refilled was the source of the store of item k + PRE - STAGES
+        tma_store_wait_read<STAGES - PRE - 1>();
+        issue(ahead);
+      }
+      advance(ahead);
     }
-    const int e = it0 + k;
-    const int slice = e / mats, m = e - slice * mats;
-    const int hl = m / p.dblocks, jb = m - hl * p.dblocks;
+    const int slice = cur.slice, hl = cur.hl, jb = cur.jb;
+    const int m = hl * p.dblocks + jb;
     const int h = h0 + hl;
-    const uint32_t c_tile = ring + (k % STAGES) * Cfg::STAGE;
+    const uint32_t c_tile = ring + cur.stage * Cfg::STAGE;
     const uint32_t a_tile = c_tile + Cfg::C_SLICE;
     const uint32_t wh_tile = w_base + (m * 2) * Cfg::W_BYTES;
     const uint32_t wl_tile = wh_tile + Cfg::W_BYTES;
@@ -145,8 +167,8 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             cv = __ldg(p.cos + idx);
             sv = __ldg(p.sin + idx);
           }
-          tc[j][kk] = cv;
-          ts[j][kk] = sv;
+          tc[j][kk] = cv * inv_s;    // the 1/sqrt(n) of the correction rides on the rotary factors
+          ts[j][kk] = -sv * inv_s;   // inverse rotation
         }
       }
       tab_slice = slice;
@@ -154,7 +176,7 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
     const float eta = __ldg(p.eta + h);
 
-    ok = mbar_wait(mybar + (k % STAGES) * 8, (uint32_t)((k / STAGES) & 1));
+    ok = mbar_wait(mybar + cur.stage * 8, parity);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
 
@@ -185,9 +207,10 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       for (int kk = 0; kk < 2; ++kk) {
         const uint32_t addr = c_tile + swz_rows<128>((g + 8 * kk) * 128 + (8 * j + 2 * tq) * 2);
         float2 corr = make_float2(acc[j][2 * kk], acc[j][2 * kk + 1]);
-        if (ROT) corr = rot_pair(corr.x, corr.y, tc[j][kk], -ts[j][kk]);
+        if (ROT) corr = rot_pair(corr.x, corr.y, tc[j][kk], ts[j][kk]);
+        else corr = make_float2(corr.x * inv_s, corr.y * inv_s);
         const float2 cv = bf2_to_f2(ld_shared_u32(addr));
-        st_shared_u32(addr, f2_to_bf2(fmaf(corr.x, inv_s, eta * cv.x), fmaf(corr.y, inv_s, eta * cv.y)));
+        st_shared_u32(addr, f2_to_bf2(fmaf(eta, cv.x, corr.x), fmaf(eta, cv.y, corr.y)));
       }
     }
     fence_async_shared();
@@ -196,6 +219,8 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       tma_store_3d(&map_y, h * d + jb * 64, slice * 16, b, c_tile);
       tma_store_commit();
     }
+    advance(cur);
+    if (cur.stage == 0) parity ^= 1u;
   }
   if (lane == 0) {
     tma_store_wait_all<0>();

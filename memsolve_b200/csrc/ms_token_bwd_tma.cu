@@ -161,21 +161,38 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   const int g = lane >> 2, tq = lane & 3;
   const int mi = lane >> 3, mr = lane & 7;
 
-  auto issue = [&](int k) {
-    const int e = it0 + k;
-    const int slice = e / gh, hl = e - slice * gh;
-    const int h = h0 + hl;
-    const uint32_t st = ring + (k % STAGES) * Cfg::STAGE;
-    const uint32_t bar = mybar + (k % STAGES) * 8;
+  // position of an item: (slice, head in group) and its ring stage; advanced without divisions
+  struct Cursor {
+    int slice, hl, stage;
+  };
+  auto advance = [&](Cursor& c) {
+    if (++c.hl == gh) {
+      c.hl = 0;
+      ++c.slice;
+    }
+    c.stage = c.stage + 1 == STAGES ? 0 : c.stage + 1;
+  };
+  Cursor ahead;   // next item to load
+  ahead.slice = it0 / gh;
+  ahead.hl = it0 - ahead.slice * gh;
+  ahead.stage = 0;
+  Cursor cur = ahead;   // item being computed
+  uint32_t parity = 0;
+
+  auto issue = [&](const Cursor& c) {
+    const int h = h0 + c.hl;
+    const uint32_t st = ring + c.stage * Cfg::STAGE;
+    const uint32_t bar = mybar + c.stage * 8;
     mbar_expect_tx(bar, 4096 + Cfg::A_SLICE);
-    tma_load_3d(st, &map_c, p.heads * R + h * 64, slice * 16, b, bar);
-    tma_load_3d(st + 2048, &map_y, h * 64, slice * 16, b, bar);
-    tma_load_3d(st + 4096, &map_a, h * R, slice * 16, b, bar);
+    tma_load_3d(st, &map_c, p.heads * R + h * 64, c.slice * 16, b, bar);
+    tma_load_3d(st + 2048, &map_y, h * 64, c.slice * 16, b, bar);
+    tma_load_3d(st + 4096, &map_a, h * R, c.slice * 16, b, bar);
   };
 
   MS_STAMP((blockIdx.z * gridDim.x + blockIdx.x) * WARPS + warp, 0);
-  if (lane == 0) {
-    for (int k = 0; k < PRE && k < n_items; ++k) issue(k);
+  for (int k = 0; k < PRE && k < n_items; ++k) {
+    if (lane == 0) issue(ahead);
+    advance(ahead);
   }
   bool ok = mbar_wait(rbar, 0);
   ok = __all_sync(0xffffffffu, ok);
@@ -184,15 +201,17 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   int tab_slice = -1;
 
   for (int k = 0; k < n_items && ok; ++k) {
-    if (lane == 0 && k + PRE < n_items) {
-      // the buffer being refilled was the source of the stores of item k + PRE - STAGES
-      tma_store_wait_read<STAGES - PRE - 1>();
-      issue(k + PRE);
+    if (k + PRE < n_items) {
+      if (lane == 0) {
+        // the buffer being refilled was the source of the stores of item k + PRE - STAGES
+        tma_store_wait_read<STAGES - PRE - 1>();
+        issue(ahead);
+      }
+      advance(ahead);
     }
-    const int e = it0 + k;
-    const int slice = e / gh, hl = e - slice * gh;
+    const int slice = cur.slice, hl = cur.hl;
     const int h = h0 + hl;
-    const uint32_t c_tile = ring + (k % STAGES) * Cfg::STAGE;
+    const uint32_t c_tile = ring + cur.stage * Cfg::STAGE;
     const uint32_t y_tile = c_tile + 2048;
     const uint32_t a_tile = c_tile + 4096;
     const uint32_t wh_tile = res_base + hl * Cfg::HEAD_BYTES;
@@ -208,7 +227,7 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     }
     const float eta = __ldg(p.eta + h);
 
-    ok = mbar_wait(mybar + (k % STAGES) * 8, (uint32_t)((k / STAGES) & 1));
+    ok = mbar_wait(mybar + cur.stage * 8, parity);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
     uint32_t af[R / 16][4];
@@ -297,6 +316,8 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       tma_store_3d(&map_oa, h * R, slice * 16, b, a_tile);
       tma_store_commit();
     }
+    advance(cur);
+    if (cur.stage == 0) parity ^= 1u;
   }
   if (lane == 0) {
     tma_store_wait_all<0>();
