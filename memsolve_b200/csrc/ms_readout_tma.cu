@@ -201,6 +201,13 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         mma_bf16(acc[2 * n2 + 1], af, bf[2], bf[3]);
       }
     }
+    // the content box as row-operand fragments: the same (row, channel pair) per thread as the
+    // accumulators, four ldmatrix instead of sixteen 4-byte loads
+    uint32_t craw[4][4];
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+      ldsm_x4(craw[ks], c_tile + swz_rows<128>((mr + 8 * (mi & 1)) * 128 + (ks * 16 + 8 * (mi >> 1)) * 2));
+    __syncwarp();   // every lane has read the box before the result is written over it
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
 #pragma unroll
@@ -209,7 +216,7 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         float2 corr = make_float2(acc[j][2 * kk], acc[j][2 * kk + 1]);
         if (ROT) corr = rot_pair(corr.x, corr.y, tc[j][kk], ts[j][kk]);
         else corr = make_float2(corr.x * inv_s, corr.y * inv_s);
-        const float2 cv = bf2_to_f2(ld_shared_u32(addr));
+        const float2 cv = bf2_to_f2(craw[j >> 1][2 * (j & 1) + kk]);
         st_shared_u32(addr, f2_to_bf2(fmaf(eta, cv.x, corr.x), fmaf(eta, cv.y, corr.y)));
       }
     }
