@@ -19,12 +19,12 @@
 
 namespace ms {
 
-constexpr int kStWarps = 8;
 
 // CB: channels of one CTA (64, or 32 so that two CTAs with half the accumulators share an SM; the
 // Gram columns are then divided between the first two channel blocks of a head).
-template <int R, bool GRAD, bool ROT, int CB, int STAGES_>
+template <int R, bool GRAD, bool ROT, int CB, int STAGES_, int WARPS_>
 struct StatsTmaCfg {
+  static constexpr int kStWarps = WARPS_;
   static constexpr int A_SLICE = 16 * R * 2;
   static constexpr int X_BYTES = 16 * CB * 2;
   static constexpr int T_BYTES = 16 * (CB / 2) * 4;   // one table (cos or sin), 16 rows x CB/2 floats
@@ -58,13 +58,14 @@ struct StatsTmaParams {
   int complement;
 };
 
-template <int R, bool GRAD, bool ROT, int CB, int STAGES_>
-__global__ void __launch_bounds__(kStWarps * 32, CB == 32 ? 2 : 1)
+template <int R, bool GRAD, bool ROT, int CB, int STAGES_, int WARPS_>
+__global__ void __launch_bounds__(WARPS_ * 32, CB == 32 ? 2 : 1)
 stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_c,
                  const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_cos,
                  const __grid_constant__ CUtensorMap map_sin, const StatsTmaParams p) {
-  using Cfg = StatsTmaCfg<R, GRAD, ROT, CB, STAGES_>;
+  using Cfg = StatsTmaCfg<R, GRAD, ROT, CB, STAGES_, WARPS_>;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int kStWarps = WARPS_;
   constexpr int MT = R / 16, NG = Cfg::GCOLS / 8, NQ = CB / 8;
   constexpr int NT = kStWarps * 32;
   constexpr int XP = CB * 2;   // row pitch in bytes of the content / gradient / table tiles
@@ -309,18 +310,18 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
-template <int R, bool GRAD, bool ROT, int CB, int STAGES>
+template <int R, bool GRAD, bool ROT, int CB, int STAGES, int WARPS>
 static int launch_stats_tma_one(const ms_shape& s, const Plan& plan, const CUtensorMap* maps, const StatsTmaParams& p,
                                 bool fuse_core, cudaStream_t st) {
-  using Cfg = StatsTmaCfg<R, GRAD, ROT, CB, STAGES>;
-  auto kern = stats_tma_kernel<R, GRAD, ROT, CB, STAGES>;
+  using Cfg = StatsTmaCfg<R, GRAD, ROT, CB, STAGES, WARPS>;
+  auto kern = stats_tma_kernel<R, GRAD, ROT, CB, STAGES, WARPS>;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Cfg::TOTAL)) return MS_ERR_LAUNCH;
   dim3 grid(plan.chunks + (fuse_core ? 1 : 0), plan.systems, s.head_dim / CB);
-  kern<<<grid, kStWarps * 32, Cfg::TOTAL, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+  kern<<<grid, WARPS * 32, Cfg::TOTAL, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
 
-template <int R, bool GRAD, int CB, int STAGES>
+template <int R, bool GRAD, int CB, int STAGES, int WARPS = 8>
 static int launch_stats_tma_r(const ms_shape& s, const Plan& plan, const void* projected, const void* dy,
                               const float* cos, const float* sin, StatsTmaParams& p, bool fuse_core,
                               cudaStream_t st) {
@@ -355,8 +356,8 @@ static int launch_stats_tma_r(const ms_shape& s, const Plan& plan, const void* p
     if (encode_tensor_map(&maps[3], const_cast<float*>(cos), 4, 3, dims, str, box, Swizzle::None)) return MS_ERR_LAUNCH;
     if (encode_tensor_map(&maps[4], const_cast<float*>(sin), 4, 3, dims, str, box, Swizzle::None)) return MS_ERR_LAUNCH;
   }
-  return rot ? launch_stats_tma_one<R, GRAD, true, CB, STAGES>(s, plan, maps, p, fuse_core, st)
-             : launch_stats_tma_one<R, GRAD, false, CB, STAGES>(s, plan, maps, p, fuse_core, st);
+  return rot ? launch_stats_tma_one<R, GRAD, true, CB, STAGES, WARPS>(s, plan, maps, p, fuse_core, st)
+             : launch_stats_tma_one<R, GRAD, false, CB, STAGES, WARPS>(s, plan, maps, p, fuse_core, st);
 }
 
 // MS_OK / error, or -1 when the shape is outside this kernel's envelope.
@@ -389,7 +390,8 @@ int launch_stats_tma(const ms_shape& s, const Plan& plan, bool grad, const void*
   }
   switch (s.rank) {
     case 16: return launch_stats_tma_r<16, false, 64, 3>(s, plan, projected, dy, cos, sin, p, fuse_core, st);
-    case 32: return launch_stats_tma_r<32, false, 64, 3>(s, plan, projected, dy, cos, sin, p, fuse_core, st);
+    // rank 32: twelve warps with two stages each fit the register file and hide more latency
+    case 32: return launch_stats_tma_r<32, false, 64, 2, 12>(s, plan, projected, dy, cos, sin, p, fuse_core, st);
   }
   return -1;
 }
