@@ -110,10 +110,11 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   constexpr int OFF_A = OFF_T + (ROT ? 2 * Cfg::T_BYTES : 0);
   constexpr uint32_t TX = Cfg::X_BYTES + (GRAD ? Cfg::X_BYTES : 0) + (ROT ? 2 * Cfg::T_BYTES : 0) + Cfg::A_SLICE;
 
-  auto issue = [&](int k) {
+  // item k of this warp refills ring stage k % STAGES
+  auto issue = [&](int k, int stage) {
     const int row = (slice0 + warp + k * kStWarps) * 16;
-    const uint32_t st = ring + (k % STAGES) * Cfg::STAGE;
-    const uint32_t bar = mybar + (k % STAGES) * 8;
+    const uint32_t st = ring + stage * Cfg::STAGE;
+    const uint32_t bar = mybar + stage * 8;
     mbar_expect_tx(bar, TX);
     const int ccol = p.heads * R + h * p.head_dim + d0;
     if (GRAD) {
@@ -143,22 +144,24 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     for (int j = 0; j < NQ; ++j)
 #pragma unroll
       for (int q = 0; q < 4; ++q) accQ[i][j][q] = 0.f;
-  float de_acc = 0.f;
+  float de_part[4] = {0.f, 0.f, 0.f, 0.f};
 
   if (lane == 0) {
-    for (int k = 0; k < STAGES && k < n_items; ++k) issue(k);
+    for (int k = 0; k < STAGES && k < n_items; ++k) issue(k, k);
   }
   bool ok = true;
   const int mi = lane >> 3, mr = lane & 7;
 
+  int stage = 0;
+  uint32_t parity = 0;
   for (int k = 0; k < n_items; ++k) {
-    const uint32_t st = ring + (k % STAGES) * Cfg::STAGE;
+    const uint32_t st = ring + stage * Cfg::STAGE;
     const uint32_t x_tile = st;
     const uint32_t c_tile = st + OFF_C;
     const uint32_t cos_tile = st + OFF_T;
     const uint32_t sin_tile = cos_tile + Cfg::T_BYTES;
     const uint32_t a_tile = st + OFF_A;
-    ok = mbar_wait(mybar + (k % STAGES) * 8, (uint32_t)((k / STAGES) & 1));
+    ok = mbar_wait(mybar + stage * 8, parity);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
 
@@ -177,8 +180,8 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const float2 xf = bf2_to_f2(xs[q]), cf = bf2_to_f2(cs[q]);
-            de_acc = fmaf(xf.x, cf.x, de_acc);
-            de_acc = fmaf(xf.y, cf.y, de_acc);
+            de_part[q] = fmaf(xf.x, cf.x, de_part[q]);   // four independent chains
+            de_part[q] = fmaf(xf.y, cf.y, de_part[q]);
           }
         }
         if (ROT) {
@@ -244,7 +247,11 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (k + STAGES < n_items) {
       fence_async_shared();
       __syncwarp();
-      if (lane == 0) issue(k + STAGES);
+      if (lane == 0) issue(k + STAGES, stage);
+    }
+    if (++stage == STAGES) {
+      stage = 0;
+      parity ^= 1u;
     }
   }
   if (!ok && lane == 0) atomicExch(p.error, kErrBarrierTimeout);
@@ -291,6 +298,8 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
   if (GRAD) {
     __syncthreads();
+#pragma unroll
+    float de_acc = (de_part[0] + de_part[1]) + (de_part[2] + de_part[3]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) de_acc += __shfl_xor_sync(0xffffffffu, de_acc, o);
     if (lane == 0) red[warp] = de_acc;
