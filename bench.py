@@ -292,7 +292,7 @@ def time_kernels(layer, cfg, tokens, device, reps=10, warm=3, with_graph=True):
 
 
 # DRAM bytes (read + write) of one launch at 32768 tokens, rank 32, from the ncu capture summarised in
-# profiles/mixer_kernels_c3_ncu_full.md.  Traffic of these streaming kernels grows in proportion to tokens.
+# profiles/ (full ncu capture of the mixer kernels).  Traffic of these streaming kernels grows in proportion to tokens.
 _NCU_DRAM_BYTES_C3 = {"stats_forward": 87.7e6, "readout": 104.9e6, "stats_backward": 138.6e6,
                       "token_backward": 177.3e6}
 
@@ -498,7 +498,7 @@ def run_ours(args, cfg):
             "bound": "hbm", "kernel": name, "achieved": achieved, "peak": hbm, "unit": "GB/s",
             "frac": achieved / hbm, "traffic": _ncu_traffic(args.workload, name, tokens),
             "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 32768 tokens "
-                              "(profiles/mixer_kernels_c3_ncu_full.md), scaled by tokens",
+                              "(summary under profiles/), scaled by tokens",
             "peak_source": f"of {which}",
             "per_kernel_us": {k: round(v["s"] * 1e6, 2) for k, v in kern.items()},
             "per_kernel_gbs": {k: round(v["bytes"] / v["s"] / 1e9, 1) for k, v in kern.items() if v["bytes"]},
