@@ -19,7 +19,7 @@ import re
 from contextlib import contextmanager
 from pathlib import Path
 from threading import Lock, local
-from typing import Literal, NamedTuple
+from typing import List, Literal, NamedTuple, Optional
 
 import torch
 from torch.autograd.function import once_differentiable
@@ -441,6 +441,84 @@ class _NoFrameMix(torch.autograd.Function):
 
 
 # --------------------------------------------------------------------------------------
+# operator registration (memsolve/ball/cuda.py:4164-5003 of the reference): the mixer as
+# torch.library operators with fake (shape-only) kernels and an autograd formula, so that
+# torch.compile(fullgraph=True) and other tracers see one opaque call per direction
+# --------------------------------------------------------------------------------------
+def _dims_of(projected, base, cos) -> tuple:
+    batch, length, width = projected.shape
+    heads, rank, columns = base.shape
+    head_dim = (width - heads * rank) // heads
+    return (batch, length, heads, rank, head_dim, int(columns == 0), 0 if cos is None else int(cos.shape[0]))
+
+
+@torch.library.custom_op("memsolve_b200::fast_mix_fwd", mutates_args=(), device_types="cuda")
+def _fast_mix_fwd_op(projected: torch.Tensor, core_base_raw: torch.Tensor, eta_raw: torch.Tensor,
+                     valid_counts: Optional[torch.Tensor], rotary_cos: Optional[torch.Tensor],
+                     rotary_sin: Optional[torch.Tensor]) -> List[torch.Tensor]:
+    """mixed plus the compact tape (eta, eta_slope, core_map, core_info, inverse, state, coeff)."""
+    require_available()
+    _validate_no_frame_inputs(projected, core_base_raw, eta_raw, valid_counts)
+    mixed, tape, _ = _mix_forward(projected, core_base_raw, eta_raw, valid_counts, None, rotary_cos, rotary_sin)
+    return [mixed, *tape]
+
+
+@_fast_mix_fwd_op.register_fake
+def _fast_mix_fwd_fake(projected, core_base_raw, eta_raw, valid_counts, rotary_cos, rotary_sin):
+    batch, length, heads, rank, head_dim, _comp, _rows = _dims_of(projected, core_base_raw, rotary_cos)
+    dpad = (head_dim + 7) // 8 * 8
+    f32 = eta_raw.new_empty
+    return [projected.new_empty((batch, length, heads * head_dim)), f32((heads,)), f32((heads,)),
+            f32((heads, rank, rank)), eta_raw.new_empty((heads,), dtype=torch.int32),
+            f32((batch, heads, rank, rank)), f32((batch, heads, rank, head_dim)),
+            projected.new_empty((batch, heads, 2, rank, dpad))]
+
+
+@torch.library.custom_op("memsolve_b200::fast_mix_bwd", mutates_args=(), device_types="cuda")
+def _fast_mix_bwd_op(projected: torch.Tensor, gradient: torch.Tensor, core_base_raw: torch.Tensor,
+                     eta_raw: torch.Tensor, valid_counts: Optional[torch.Tensor],
+                     rotary_cos: Optional[torch.Tensor], rotary_sin: Optional[torch.Tensor],
+                     tape: List[torch.Tensor]) -> List[torch.Tensor]:
+    """Gradients of projected, core_base_raw and eta_raw."""
+    dims = _dims_of(projected, core_base_raw, rotary_cos)
+    gradient = gradient.contiguous()
+    if gradient.dtype != torch.bfloat16:
+        gradient = gradient.to(torch.bfloat16)
+    d_projected, d_base, d_raw = _mix_backward(projected, gradient, core_base_raw, eta_raw, valid_counts, None,
+                                               rotary_cos, rotary_sin, _TapeTensors(*tape), dims)
+    if d_base is None:
+        d_base = torch.zeros_like(core_base_raw)
+    return [d_projected, d_base, d_raw]
+
+
+@_fast_mix_bwd_op.register_fake
+def _fast_mix_bwd_fake(projected, gradient, core_base_raw, eta_raw, valid_counts, rotary_cos, rotary_sin, tape):
+    return [torch.empty_like(projected), torch.empty_like(core_base_raw), torch.empty_like(eta_raw)]
+
+
+def _fast_mix_setup_context(ctx, inputs, output):
+    projected, base, raw, counts, cos, sin = inputs
+    ctx.has_counts, ctx.has_rotary = counts is not None, cos is not None
+    extra = ([counts] if counts is not None else []) + ([cos, sin] if cos is not None else [])
+    ctx.save_for_backward(projected, base, raw, *output[1:], *extra)
+
+
+def _fast_mix_autograd(ctx, grads):
+    saved = list(ctx.saved_tensors)
+    projected, base, raw = saved[:3]
+    tape, rest = saved[3:10], saved[10:]
+    counts = rest.pop(0) if ctx.has_counts else None
+    cos, sin = (rest[0], rest[1]) if ctx.has_rotary else (None, None)
+    d_projected, d_base, d_raw = torch.ops.memsolve_b200.fast_mix_bwd(
+        projected, grads[0], base, raw, counts, cos, sin, tape)
+    return d_projected, d_base, d_raw, None, None, None
+
+
+torch.library.register_autograd("memsolve_b200::fast_mix_fwd", _fast_mix_autograd,
+                                setup_context=_fast_mix_setup_context)
+
+
+# --------------------------------------------------------------------------------------
 # public mixer entry (memsolve/ball/cuda.py:5175-5278)
 # --------------------------------------------------------------------------------------
 def _validate_no_frame_inputs(projected, base, raw, counts) -> None:
@@ -487,6 +565,10 @@ def fast_mix(
     """
     if valid_counts is not None and valid_counts.requires_grad:
         raise ValueError("the MemSolve CUDA fast path does not support gradients for valid_counts")
+    if torch.compiler.is_compiling() and sequence_parallel is None:
+        # traced: one registered operator (its kernel repeats the checks below when it runs)
+        return torch.ops.memsolve_b200.fast_mix_fwd(projected, core_base_raw, eta_raw, valid_counts,
+                                                    rotary_cos, rotary_sin)[0]
     require_available()
     _validate_no_frame_inputs(projected, core_base_raw, eta_raw, valid_counts)
     if (rotary_cos is None) != (rotary_sin is None):

@@ -265,6 +265,8 @@ class MemSolve(nn.Module):
         )
         if policy == "auto":
             policy = length > 512
+        if torch.compiler.is_compiling():
+            policy = False   # traced graphs keep `mixed`; the readout is recomputed on the eager path only
         core_base = (self.core_base_raw if self.core_base_raw is not None
                      else self.eta_raw.new_empty((config.num_heads, config.rank, 0)))
         mix_kwargs = dict(sequence_parallel=sequence_parallel, rotary_cos=rotary_cos, rotary_sin=rotary_sin)
