@@ -331,6 +331,8 @@ def run_ours(args, cfg):
         sp = SequenceParallel.create(tokens)
         counts = sp.valid_counts(None, batch_size=1, device=device)
         sp.overlap_gradient_sum(layer)   # parameter-gradient SUMs overlap the rest of the backward pass
+        if os.environ.get("MEMSOLVE_BENCH_COLLECTIVE_STATS", "0") != "1":
+            sp.use_peer_exchange()       # statistics summed by one kernel over NVLink peer memory
 
     def step(xin, grad_out):
         layer.zero_grad(set_to_none=True)

@@ -243,6 +243,28 @@ int ms_mix_backward(const ms_shape* shape, const void* projected, const void* dy
                     void* cross_grad, void* dprojected, float* d_base_raw, float* d_eta_raw,
                     void* stream);
 
+/*
+ * Sequence-parallel exchange of the token statistics through peer memory: reduces the per-chunk
+ * partials that ms_stats_forward / ms_stats_backward left in `workspace` (pass packed == NULL
+ * there), publishes them in this rank's exchange area, waits for the peers and writes the SUM over
+ * all ranks, added in rank order (bit-identical on every rank), to `packed` in the layout of
+ * ms_packed_stats_floats.  It replaces pack + all-reduce + unpack of the collective path: the
+ * reference issues one NCCL all-reduce here (integrations/distributed.py:47-50, called from
+ * memsolve/ball/cuda.py:3165-3215).
+ *
+ * areas[r], r < world_size <= 8: device address, valid on THIS GPU, of rank r's exchange area
+ * (peer-accessible memory of `area_bytes` bytes, e.g. one symmetric-memory allocation per rank;
+ * same size on all ranks; >= ms_exchange_area_bytes(shape); 16-byte aligned).  The areas must be
+ * zero before the first call and must only be touched by this function afterwards; every rank
+ * has to make the same sequence of calls.  A peer that does not arrive within a few seconds sets
+ * the device error word (ms_device_error) instead of hanging the GPU.  Only plain peer loads and
+ * stores are used.
+ */
+size_t ms_exchange_area_bytes(const ms_shape* shape);
+int ms_stats_exchange(const ms_shape* shape, int backward, const void* workspace,
+                      size_t workspace_bytes, const float* counts, void* const* areas,
+                      size_t area_bytes, int world_size, int rank, float* packed, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -79,6 +79,10 @@ _SIGNATURES = {
                                               _P, _P, _P, _P, _P, ctypes.c_size_t, ctypes.c_float, _P, _P, _P]),
     "ms_mix_backward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t,
                                        ctypes.POINTER(_Tape), _P, _P, _P, _P, _P, _P]),
+    "ms_exchange_area_bytes": (ctypes.c_size_t, [ctypes.POINTER(_Shape)]),
+    "ms_stats_exchange": (ctypes.c_int, [ctypes.POINTER(_Shape), ctypes.c_int, _P, ctypes.c_size_t, _P,
+                                         ctypes.POINTER(ctypes.c_void_p), ctypes.c_size_t, ctypes.c_int,
+                                         ctypes.c_int, _P, _P]),
 }
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 
@@ -310,6 +314,19 @@ def _sp_active(sequence_parallel) -> bool:
     return sequence_parallel is not None and getattr(sequence_parallel, "world_size", 2) > 1
 
 
+def _sum_statistics(sequence_parallel, shape, backward: int, ws, counts, device, stream) -> torch.Tensor:
+    """SUM over the ranks of the statistics whose per-chunk partials are in `ws`, by one kernel through
+    the peer-memory exchange areas of the layout (`SequenceParallel.use_peer_exchange`)."""
+    packed = torch.empty(_LIB.ms_packed_stats_floats(ctypes.byref(shape), backward), device=device,
+                         dtype=torch.float32)
+    exchange = sequence_parallel.peer_exchange
+    areas, area_bytes = exchange.areas(int(_LIB.ms_exchange_area_bytes(ctypes.byref(shape))), device)
+    _check(_LIB.ms_stats_exchange(ctypes.byref(shape), backward, ws.data_ptr(), ws.numel(), _ptr(counts), areas,
+                                  area_bytes, sequence_parallel.world_size, sequence_parallel.rank,
+                                  packed.data_ptr(), stream), "statistics exchange")
+    return packed
+
+
 def _mix_forward(projected, base, raw, counts, sequence_parallel, cos, sin):
     """Launch the forward kernels; returns (mixed, tape, dims)."""
     shape, dims = _make_shape(projected, base, cos)
@@ -328,14 +345,18 @@ def _mix_forward(projected, base, raw, counts, sequence_parallel, cos, sin):
                 _ptr(counts), ws.data_ptr(), ws.numel(), ctypes.byref(tape_c), mixed.data_ptr(), stream),
                 "forward")
         else:
-            packed = torch.empty(_LIB.ms_packed_stats_floats(ctypes.byref(shape), 0), device=device,
-                                 dtype=torch.float32)
+            peer = getattr(sequence_parallel, "peer_exchange", None) is not None
+            packed = None if peer else torch.empty(_LIB.ms_packed_stats_floats(ctypes.byref(shape), 0),
+                                                   device=device, dtype=torch.float32)
             _check(_LIB.ms_stats_forward_core(ctypes.byref(shape), projected.data_ptr(), base_ptr, raw.data_ptr(),
                                               _ptr(cos), _ptr(sin), _ptr(counts), ws.data_ptr(), ws.numel(),
-                                              packed.data_ptr(), ctypes.byref(tape_c), stream),
+                                              _ptr(packed), ctypes.byref(tape_c), stream),
                    "statistics")
             # the only cross-GPU step of the forward: SUM of the packed (G, Q) statistics
-            (packed,) = sequence_parallel.sum_tensors(packed)
+            if peer:
+                packed = _sum_statistics(sequence_parallel, shape, 0, ws, counts, device, stream)
+            else:
+                (packed,) = sequence_parallel.sum_tensors(packed)
             _check(_LIB.ms_compact_forward(ctypes.byref(shape), _ptr(counts), None, 0, packed.data_ptr(),
                                            ctypes.byref(tape_c), stream), "compact forward")
             _check(_LIB.ms_readout(ctypes.byref(shape), projected.data_ptr(), _ptr(cos), _ptr(sin),
@@ -377,12 +398,16 @@ def _mix_backward(projected, gradient, base, raw, counts, sequence_parallel, cos
                 gram_grad.data_ptr(), cross_grad.data_ptr(), d_projected.data_ptr(), _ptr(d_base),
                 d_raw.data_ptr(), stream), "backward")
         else:
-            packed = torch.empty(_LIB.ms_packed_stats_floats(ctypes.byref(shape), 1), device=device,
-                                 dtype=torch.float32)
+            peer = getattr(sequence_parallel, "peer_exchange", None) is not None
+            packed = None if peer else torch.empty(_LIB.ms_packed_stats_floats(ctypes.byref(shape), 1),
+                                                   device=device, dtype=torch.float32)
             _check(_LIB.ms_stats_backward(ctypes.byref(shape), projected.data_ptr(), gradient.data_ptr(),
                                           _ptr(cos), _ptr(sin), _ptr(counts), ws.data_ptr(), ws.numel(),
-                                          packed.data_ptr(), stream), "adjoint statistics")
-            (packed,) = sequence_parallel.sum_tensors(packed)
+                                          _ptr(packed), stream), "adjoint statistics")
+            if peer:
+                packed = _sum_statistics(sequence_parallel, shape, 1, ws, counts, device, stream)
+            else:
+                (packed,) = sequence_parallel.sum_tensors(packed)
             # replicated parameters: every rank holds the full adjoint, a later SUM must count it once
             scale = 1.0 / float(sequence_parallel.world_size)
             _check(_LIB.ms_compact_backward(

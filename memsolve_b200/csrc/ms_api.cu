@@ -13,6 +13,10 @@ namespace ms {
 int launch_stats(const ms_shape&, const Plan&, bool grad, const void* projected, const void* dy,
                  const float* cos, const float* sin, float* partials, float* de_partials,
                  const float* base_raw, const float* eta_raw, const ms_tape* core_tape, cudaStream_t);
+size_t exchange_area_bytes(size_t capacity_floats);
+int launch_exchange(const ms_shape&, const Plan&, bool grad, const float* partials, const float* de_partials,
+                    const float* counts, void* const* areas, int world, int rank, size_t capacity_floats,
+                    float* out, cudaStream_t);
 int launch_pack_stats(const ms_shape&, const Plan&, bool grad, const float* partials, const float* de_partials,
                       const float* counts, float* packed, cudaStream_t);
 int launch_core_forward(const ms_shape&, const float* base_raw, const float* eta_raw, const ms_tape&, cudaStream_t);
@@ -454,6 +458,34 @@ int ms_stats_forward_core(const ms_shape* shape, const void* projected, const fl
                       tape, st));
   if (packed) MS_TRY(launch_pack_stats(*shape, plan, false, w.partials, nullptr, counts, packed, st));
   return MS_OK;
+}
+
+static size_t exchange_capacity(const ms_shape* shape) {
+  const size_t fwd = ms_packed_stats_floats(shape, 0), bwd = ms_packed_stats_floats(shape, 1);
+  return ((fwd > bwd ? fwd : bwd) + 3) & ~size_t(3);
+}
+
+size_t ms_exchange_area_bytes(const ms_shape* shape) {
+  if (check_shape(shape) != MS_OK) return 0;
+  return exchange_area_bytes(exchange_capacity(shape));
+}
+
+int ms_stats_exchange(const ms_shape* shape, int backward, const void* workspace, size_t workspace_bytes,
+                      const float* counts, void* const* areas, size_t area_bytes, int world_size, int rank,
+                      float* packed, void* stream) {
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  if (!packed || !areas) return MS_ERR_INVALID_ARGUMENT;
+  const Plan plan = make_plan(*shape);
+  if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+  // the layout of an area follows from its size: the largest capacity (a multiple of four values)
+  // whose area fits; every rank must pass the same size
+  const size_t fixed = exchange_area_bytes(0);
+  if (area_bytes < fixed + 32) return MS_ERR_WORKSPACE;
+  const size_t capacity = ((area_bytes - fixed) / (2 * sizeof(float))) & ~size_t(3);
+  const Workspace w = carve(const_cast<void*>(workspace), plan);
+  return launch_exchange(*shape, plan, backward != 0, w.partials, w.de_partials, counts, areas, world_size, rank,
+                         capacity, packed, static_cast<cudaStream_t>(stream));
 }
 
 int ms_token_backward(const ms_shape* shape, const void* projected, const void* dy, const float* cos,

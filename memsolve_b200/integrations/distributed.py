@@ -13,7 +13,9 @@ The public surface is the one of the reference's ``integrations.distributed.Sequ
 ``sum_tensors``, ``valid_counts`` and ``reduce_gradients_`` with the same arguments, results and
 exceptions.  Added here: ``overlap_gradient_sum``, which starts the SUM of each parameter
 gradient from an autograd hook, on NCCL's own stream, while the rest of the backward pass still
-runs.  Collectives are ``torch.distributed`` calls (NCCL over NVLink on GPUs, gloo in CPU tests).
+runs, and ``use_peer_exchange``, which replaces the all-reduce of the statistics by one kernel
+that reads the peers' values over NVLink.  Collectives are ``torch.distributed`` calls (NCCL over
+NVLink on GPUs, gloo in CPU tests).
 """
 from __future__ import annotations
 
@@ -56,10 +58,47 @@ class _GradientOverlap:
         self._works = {}
 
 
+class _PeerExchange:
+    """Exchange areas in symmetric memory (one allocation per rank that every peer can address) for
+    the kernel that sums the token statistics over the ranks without a collective library call."""
+
+    MINIMUM_BYTES = 1 << 20
+
+    def __init__(self, owner: "SequenceParallel"):
+        self._owner = owner
+        self._areas: dict[int, tuple] = {}
+
+    def areas(self, nbytes: int, device: torch.device):
+        """(array of the ranks' area addresses, bytes per area) with at least `nbytes` per area.
+        The first call for a device (or a larger size) allocates and is a collective host operation:
+        make it on every rank, outside CUDA-graph capture."""
+        entry = self._areas.get(device.index)
+        if entry is None or entry[3] < nbytes:
+            import ctypes
+            import torch.distributed._symmetric_memory as symmetric
+            size = self.MINIMUM_BYTES
+            while size < nbytes:
+                size *= 2
+            group = self._owner.group if self._owner.group is not None else dist.group.WORLD
+            enable = getattr(symmetric, "enable_symm_mem_for_group", None)
+            if enable is not None:
+                try:
+                    enable(group.group_name)
+                except Exception:  # noqa: BLE001 - newer releases enable groups on rendezvous
+                    pass
+            buffer = symmetric.empty(size // 4, dtype=torch.float32, device=device)
+            buffer.zero_()
+            handle = symmetric.rendezvous(buffer, group)
+            handle.barrier()   # every area is zero before any rank's kernel can touch it
+            pointers = (ctypes.c_void_p * self._owner.world_size)(*[int(p) for p in handle.buffer_ptrs])
+            entry = self._areas[device.index] = (buffer, handle, pointers, size)
+        return entry[2], entry[3]
+
+
 class SequenceParallel:
     """Layout of one sharded sequence: the process group, every rank's shard length, this rank."""
 
-    __slots__ = ("group", "shard_lengths", "rank", "_starts", "_overlaps")
+    __slots__ = ("group", "shard_lengths", "rank", "_starts", "_overlaps", "peer_exchange")
 
     def __init__(self, group, shard_lengths: Iterable[int], rank: int):
         self.group = group
@@ -67,6 +106,7 @@ class SequenceParallel:
         self.rank = int(rank)
         self._starts = (0, *itertools.accumulate(self.shard_lengths))
         self._overlaps: dict[int, _GradientOverlap] = {}
+        self.peer_exchange: _PeerExchange | None = None
 
     def __repr__(self) -> str:
         return f"SequenceParallel(shard_lengths={self.shard_lengths}, rank={self.rank})"
@@ -155,6 +195,15 @@ class SequenceParallel:
         else:
             local = torch.full((batch_size,), float(self.local_length), dtype=torch.float32, device=device)
         return self.sum_(local).clamp_min_(1)
+
+    def use_peer_exchange(self, enabled: bool = True) -> None:
+        """Sum the token statistics of the CUDA layer with one kernel over NVLink peer memory instead
+        of reduce + all-reduce (single node, at most 8 ranks, every GPU able to address its peers).
+        Call it on every rank; the first layer call afterwards allocates the exchange areas and must
+        run eagerly (not under CUDA-graph capture)."""
+        if enabled and self.world_size > 8:
+            raise ValueError("the peer-memory exchange supports at most 8 ranks")
+        self.peer_exchange = _PeerExchange(self) if enabled and self.world_size > 1 else None
 
     # ---------------------------------------------------------------- parameter gradients
     def overlap_gradient_sum(self, module: torch.nn.Module) -> _GradientOverlap:

@@ -42,6 +42,8 @@ def _worker(rank, path, results):
             layer = MemSolve(MemSolveConfig(128, 2, rank=rank_r, bias=True, rotary=rotary)).cuda()
             if case % 2 == 0:
                 sp.overlap_gradient_sum(layer)   # gradient SUMs start from autograd hooks
+            if case in (1, 2):
+                sp.use_peer_exchange()           # statistics summed by one kernel over peer memory
             with torch.no_grad():
                 layer.core_base_raw.normal_(std=0.1)
             total = sum(lengths)
