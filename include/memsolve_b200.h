@@ -265,6 +265,19 @@ int ms_stats_exchange(const ms_shape* shape, int backward, const void* workspace
                       size_t workspace_bytes, const float* counts, void* const* areas,
                       size_t area_bytes, int world_size, int rank, float* packed, void* stream);
 
+/*
+ * In-place SUM of `count` FP32 values (count a multiple of 4, `values` 16-byte aligned) over the
+ * ranks through peer memory, bit-identical on every rank: reduce-scatter and all-gather in one
+ * kernel with plain peer loads, two flag rounds.  It serves the SUM of the replicated parameters'
+ * gradients that the reference does with one NCCL all-reduce (`SequenceParallel.reduce_gradients_`,
+ * integrations/distributed.py:77-99).  `areas` as for ms_stats_exchange, but areas of their own
+ * (the two functions lay their areas out differently): ms_peer_sum_area_bytes(count) bytes or
+ * more, the same size on all ranks, zero before the first call.
+ */
+size_t ms_peer_sum_area_bytes(size_t count);
+int ms_peer_sum(float* values, size_t count, void* const* areas, size_t area_bytes, int world_size,
+                int rank, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -79,6 +79,9 @@ _SIGNATURES = {
                                               _P, _P, _P, _P, _P, ctypes.c_size_t, ctypes.c_float, _P, _P, _P]),
     "ms_mix_backward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t,
                                        ctypes.POINTER(_Tape), _P, _P, _P, _P, _P, _P]),
+    "ms_peer_sum_area_bytes": (ctypes.c_size_t, [ctypes.c_size_t]),
+    "ms_peer_sum": (ctypes.c_int, [_P, ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.c_size_t,
+                                   ctypes.c_int, ctypes.c_int, _P]),
     "ms_exchange_area_bytes": (ctypes.c_size_t, [ctypes.POINTER(_Shape)]),
     "ms_stats_exchange": (ctypes.c_int, [ctypes.POINTER(_Shape), ctypes.c_int, _P, ctypes.c_size_t, _P,
                                          ctypes.POINTER(ctypes.c_void_p), ctypes.c_size_t, ctypes.c_int,

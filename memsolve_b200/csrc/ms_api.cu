@@ -14,6 +14,9 @@ int launch_stats(const ms_shape&, const Plan&, bool grad, const void* projected,
                  const float* cos, const float* sin, float* partials, float* de_partials,
                  const float* base_raw, const float* eta_raw, const ms_tape* core_tape, cudaStream_t);
 size_t exchange_area_bytes(size_t capacity_floats);
+size_t peer_sum_area_bytes(size_t capacity_floats);
+int launch_peer_sum(float* values, size_t count, void* const* areas, size_t area_bytes, int world, int rank,
+                    cudaStream_t);
 int launch_exchange(const ms_shape&, const Plan&, bool grad, const float* partials, const float* de_partials,
                     const float* counts, void* const* areas, int world, int rank, size_t capacity_floats,
                     float* out, cudaStream_t);
@@ -486,6 +489,14 @@ int ms_stats_exchange(const ms_shape* shape, int backward, const void* workspace
   const Workspace w = carve(const_cast<void*>(workspace), plan);
   return launch_exchange(*shape, plan, backward != 0, w.partials, w.de_partials, counts, areas, world_size, rank,
                          capacity, packed, static_cast<cudaStream_t>(stream));
+}
+
+size_t ms_peer_sum_area_bytes(size_t count) { return peer_sum_area_bytes((count + 3) & ~size_t(3)) + 64; }
+
+int ms_peer_sum(float* values, size_t count, void* const* areas, size_t area_bytes, int world_size, int rank,
+                void* stream) {
+  MS_TRY(device_status());
+  return launch_peer_sum(values, count, areas, area_bytes, world_size, rank, static_cast<cudaStream_t>(stream));
 }
 
 int ms_token_backward(const ms_shape* shape, const void* projected, const void* dy, const float* cos,

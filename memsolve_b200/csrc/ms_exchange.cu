@@ -192,6 +192,163 @@ __global__ void __launch_bounds__(kExThreads) exchange_kernel(const ExchangePara
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// in-place SUM of a vector over the ranks (parameter gradients of the replicated weights)
+// ---------------------------------------------------------------------------------------
+// Same areas and flag protocol as above, two rounds per call: the vector is cut into `world`
+// slices, rank r adds slice r of all ranks (round 1) and every rank then collects the summed slices
+// from their owners (round 2), so each value crosses NVLink twice instead of world-1 times.
+// Thread block c handles portion c of every slice on every rank.  Area layout for this use:
+//
+//   float   data[2][capacity]      this rank's values                 (double buffered by call parity)
+//   float   summed[2][capacity]    slice `rank` after round 1, at its position in the vector
+//   uint32  flags[2][kMaxRanks][kSumCtas], call, done
+// few thread blocks, many loads in flight per thread: the SUM runs beside GEMMs that want every SM
+constexpr int kSumCtas = 16;
+constexpr int kSumBatch = 8;   // vectors per thread whose peer loads are in flight together
+
+struct PeerSumParams {
+  float* values;
+  float* areas[kExMaxRanks];
+  int* error;
+  int world, rank, capacity, total4;   // total4: vector length in units of four values
+};
+
+__device__ __forceinline__ bool flag_round(const PeerSumParams& p, unsigned* my_flags, int round, unsigned call, int c,
+                                           int tid, int* s_ok) {
+  // values written by the block before this point are published by the release store of the flag
+  __syncthreads();
+  if (tid < p.world && tid != p.rank) {
+    unsigned* theirs = reinterpret_cast<unsigned*>(p.areas[tid] + 4 * (size_t)p.capacity) +
+                       round * kExMaxRanks * kSumCtas;
+    st_flag(theirs + p.rank * kSumCtas + c, call);
+    const unsigned* flag = my_flags + round * kExMaxRanks * kSumCtas + tid * kSumCtas + c;
+    int polls = 0;
+    while ((int)(ld_flag(flag) - call) < 0) {
+      if (++polls > kExWaitLimit) {
+        *s_ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return *s_ok != 0;
+}
+
+__global__ void __launch_bounds__(kExThreads) peer_sum_kernel(const PeerSumParams p) {
+  __shared__ int s_ok;
+  const int tid = threadIdx.x, c = blockIdx.x;
+  float* mine = p.areas[p.rank];
+  unsigned* my_flags = reinterpret_cast<unsigned*>(mine + 4 * (size_t)p.capacity);
+  unsigned* state = my_flags + 2 * kExMaxRanks * kSumCtas;
+  const unsigned call = *reinterpret_cast<volatile unsigned*>(state) + 1u;
+  const size_t data = (size_t)(call & 1u) * p.capacity;
+  const size_t summed = (size_t)(2 + (call & 1u)) * p.capacity;
+  if (tid == 0) s_ok = 1;
+
+  // slice s = vectors [s * slice4, (s+1) * slice4); portion c of a slice = [c * part4, (c+1) * part4) within it
+  const int slice4 = (p.total4 + p.world - 1) / p.world;
+  const int part4 = (slice4 + kSumCtas - 1) / kSumCtas;
+  const int plo = min(slice4, c * part4), phi = min(slice4, plo + part4);
+
+  // 0. copy this rank's values into its area
+  for (int s = 0; s < p.world; ++s) {
+    for (int j = plo + tid; j < phi; j += kExThreads) {
+      const int i4 = s * slice4 + j;
+      if (i4 < p.total4)
+        *reinterpret_cast<float4*>(mine + data + 4 * (size_t)i4) =
+            *reinterpret_cast<const float4*>(p.values + 4 * (size_t)i4);
+    }
+  }
+  flag_round(p, my_flags, 0, call, c, tid, &s_ok);
+
+  // 1. slice `rank`: add the values of all ranks in rank order (kSumBatch vectors per thread at a time)
+  for (int base = plo + tid; base < phi; base += kExThreads * kSumBatch) {
+    float4 acc[kSumBatch];
+#pragma unroll
+    for (int v = 0; v < kSumBatch; ++v) acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < p.world; ++r) {
+      float4 t[kSumBatch];
+#pragma unroll
+      for (int v = 0; v < kSumBatch; ++v) {
+        const int j = base + v * kExThreads, i4 = p.rank * slice4 + j;
+        t[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (j < phi && i4 < p.total4) {
+          const float* src = p.areas[r] + data + 4 * (size_t)i4;
+          t[v] = r == p.rank ? *reinterpret_cast<const float4*>(src) : ld_peer4(src);
+        }
+      }
+#pragma unroll
+      for (int v = 0; v < kSumBatch; ++v) {
+        acc[v].x += t[v].x; acc[v].y += t[v].y; acc[v].z += t[v].z; acc[v].w += t[v].w;
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < kSumBatch; ++v) {
+      const int j = base + v * kExThreads, i4 = p.rank * slice4 + j;
+      if (j < phi && i4 < p.total4) {
+        *reinterpret_cast<float4*>(mine + summed + 4 * (size_t)i4) = acc[v];
+        *reinterpret_cast<float4*>(p.values + 4 * (size_t)i4) = acc[v];
+      }
+    }
+  }
+  flag_round(p, my_flags, 1, call, c, tid, &s_ok);
+  if (!s_ok && tid == 0) atomicExch(p.error, kErrPeerTimeout);
+
+  // 2. collect the other slices from their owners
+  for (int s = 0; s < p.world; ++s) {
+    if (s == p.rank) continue;
+    for (int base = plo + tid; base < phi; base += kExThreads * kSumBatch) {
+      float4 t[kSumBatch];
+#pragma unroll
+      for (int v = 0; v < kSumBatch; ++v) {
+        const int j = base + v * kExThreads, i4 = s * slice4 + j;
+        if (j < phi && i4 < p.total4) t[v] = ld_peer4(p.areas[s] + summed + 4 * (size_t)i4);
+      }
+#pragma unroll
+      for (int v = 0; v < kSumBatch; ++v) {
+        const int j = base + v * kExThreads, i4 = s * slice4 + j;
+        if (j < phi && i4 < p.total4) *reinterpret_cast<float4*>(p.values + 4 * (size_t)i4) = t[v];
+      }
+    }
+  }
+
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(state + 1, 1u) == gridDim.x - 1) {
+      state[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned*>(state) = call;
+    }
+  }
+}
+
+size_t peer_sum_area_bytes(size_t capacity_floats) {
+  return (4 * capacity_floats + 2 * (size_t)kExMaxRanks * kSumCtas + 4) * sizeof(float);
+}
+
+int launch_peer_sum(float* values, size_t count, void* const* areas, size_t area_bytes, int world, int rank,
+                    cudaStream_t st) {
+  if (world < 1 || world > kExMaxRanks || rank < 0 || rank >= world || !areas || !values) return MS_ERR_INVALID_ARGUMENT;
+  if ((count & 3u) != 0 || (reinterpret_cast<uintptr_t>(values) & 15u) != 0) return MS_ERR_INVALID_ARGUMENT;
+  const size_t fixed = peer_sum_area_bytes(0);
+  if (area_bytes < fixed + 64) return MS_ERR_WORKSPACE;
+  const size_t capacity = ((area_bytes - fixed) / (4 * sizeof(float))) & ~size_t(3);
+  if (count > capacity || count > 0x7ffffff0u) return MS_ERR_WORKSPACE;
+  PeerSumParams p;
+  p.values = values;
+  for (int r = 0; r < kExMaxRanks; ++r) p.areas[r] = r < world ? static_cast<float*>(areas[r]) : nullptr;
+  for (int r = 0; r < world; ++r)
+    if (!p.areas[r] || (reinterpret_cast<uintptr_t>(p.areas[r]) & 15u)) return MS_ERR_INVALID_ARGUMENT;
+  p.error = device_error_word();
+  if (!p.error) return MS_ERR_LAUNCH;
+  p.world = world; p.rank = rank; p.capacity = (int)capacity; p.total4 = (int)(count >> 2);
+  if (count == 0) return MS_OK;
+  peer_sum_kernel<<<kSumCtas, kExThreads, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
+}
+
 size_t exchange_area_bytes(size_t capacity_floats) {
   return (2 * capacity_floats + (size_t)kExMaxRanks * kExCtas + 4) * sizeof(float);
 }

@@ -39,8 +39,12 @@ class _GradientOverlap:
                          for p in module.parameters() if p.requires_grad]
 
     def _launch(self, parameter: torch.Tensor) -> None:
-        self._works[id(parameter)] = dist.all_reduce(parameter.grad, op=_SUM, group=self._owner.group,
-                                                     async_op=True)
+        gradient = parameter.grad
+        exchange = self._owner.peer_exchange
+        if exchange is not None and exchange.can_sum(gradient):
+            self._works[id(parameter)] = exchange.sum_async(gradient)
+        else:
+            self._works[id(parameter)] = dist.all_reduce(gradient, op=_SUM, group=self._owner.group, async_op=True)
 
     def finish(self, parameters: Sequence[torch.Tensor]) -> None:
         """Sum what no hook has started (a gradient written without autograd), then wait for all."""
@@ -66,7 +70,28 @@ class _PeerExchange:
 
     def __init__(self, owner: "SequenceParallel"):
         self._owner = owner
-        self._areas: dict[int, tuple] = {}
+        self._areas: dict[int, tuple] = {}       # per device: areas of the statistics exchange
+        self._sum_areas: dict[int, tuple] = {}   # per device: areas of the gradient SUM (other layout)
+        self._streams: dict[int, torch.cuda.Stream] = {}
+
+    def _allocate(self, nbytes: int, device: torch.device) -> tuple:
+        """One zeroed symmetric-memory area per rank: (tensor, handle, address array, bytes)."""
+        import ctypes
+        import torch.distributed._symmetric_memory as symmetric
+        size = 1 << max(nbytes - 1, 1).bit_length()   # the same power of two on every rank
+        group = self._owner.group if self._owner.group is not None else dist.group.WORLD
+        enable = getattr(symmetric, "enable_symm_mem_for_group", None)
+        if enable is not None:
+            try:
+                enable(group.group_name)
+            except Exception:  # noqa: BLE001 - newer releases enable groups on rendezvous
+                pass
+        buffer = symmetric.empty(size // 4, dtype=torch.float32, device=device)
+        buffer.zero_()
+        handle = symmetric.rendezvous(buffer, group)
+        handle.barrier()   # every area is zero before any rank's kernel can touch it
+        pointers = (ctypes.c_void_p * self._owner.world_size)(*[int(p) for p in handle.buffer_ptrs])
+        return buffer, handle, pointers, size
 
     def areas(self, nbytes: int, device: torch.device):
         """(array of the ranks' area addresses, bytes per area) with at least `nbytes` per area.
@@ -74,25 +99,49 @@ class _PeerExchange:
         make it on every rank, outside CUDA-graph capture."""
         entry = self._areas.get(device.index)
         if entry is None or entry[3] < nbytes:
-            import ctypes
-            import torch.distributed._symmetric_memory as symmetric
-            size = self.MINIMUM_BYTES
-            while size < nbytes:
-                size *= 2
-            group = self._owner.group if self._owner.group is not None else dist.group.WORLD
-            enable = getattr(symmetric, "enable_symm_mem_for_group", None)
-            if enable is not None:
-                try:
-                    enable(group.group_name)
-                except Exception:  # noqa: BLE001 - newer releases enable groups on rendezvous
-                    pass
-            buffer = symmetric.empty(size // 4, dtype=torch.float32, device=device)
-            buffer.zero_()
-            handle = symmetric.rendezvous(buffer, group)
-            handle.barrier()   # every area is zero before any rank's kernel can touch it
-            pointers = (ctypes.c_void_p * self._owner.world_size)(*[int(p) for p in handle.buffer_ptrs])
-            entry = self._areas[device.index] = (buffer, handle, pointers, size)
+            entry = self._areas[device.index] = self._allocate(max(nbytes, self.MINIMUM_BYTES), device)
         return entry[2], entry[3]
+
+    # ---- in-place SUM of a gradient over the ranks, on a stream of its own
+    SUM_MINIMUM_NUMEL = 1 << 18   # smaller gradients are latency-bound either way: leave them to NCCL
+
+    def can_sum(self, tensor: torch.Tensor) -> bool:
+        return (tensor.is_cuda and tensor.dtype == torch.float32 and tensor.is_contiguous()
+                and tensor.numel() >= self.SUM_MINIMUM_NUMEL and tensor.numel() % 4 == 0
+                and tensor.data_ptr() % 16 == 0)
+
+    def sum_async(self, tensor: torch.Tensor) -> "_StreamWork":
+        """Launch the peer-memory SUM of `tensor` on the exchange's side stream, ordered after the
+        work already queued on the current stream; the returned object's wait() makes the current
+        stream wait for it.  The first call on a device allocates (see `areas`)."""
+        from ..ball import cuda as backend
+        device = tensor.device
+        backend.require_available()
+        lib = backend._LIB
+        entry = self._sum_areas.get(device.index)
+        need = int(lib.ms_peer_sum_area_bytes(tensor.numel()))
+        if entry is None or entry[3] < need:
+            entry = self._sum_areas[device.index] = self._allocate(max(need, 16 << 20), device)
+            self._streams[device.index] = torch.cuda.Stream(device)
+        side = self._streams[device.index]
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            status = lib.ms_peer_sum(tensor.data_ptr(), tensor.numel(), entry[2], entry[3], self._owner.world_size,
+                                     self._owner.rank, side.cuda_stream)
+            if status != 0:
+                raise RuntimeError(f"peer-memory gradient SUM failed: {lib.ms_status_string(status).decode()}")
+            # the gradient stays alive in `parameter.grad` until the caller has waited for this work
+            return _StreamWork(side.record_event(), device)
+
+
+class _StreamWork:
+    """Completion of work queued on a side stream (same role as a collective's Work object)."""
+
+    def __init__(self, event: torch.cuda.Event, device: torch.device):
+        self._event, self._device = event, device
+
+    def wait(self) -> None:
+        torch.cuda.current_stream(self._device).wait_event(self._event)
 
 
 class SequenceParallel:
