@@ -331,8 +331,11 @@ def run_ours(args, cfg):
         sp = SequenceParallel.create(tokens)
         counts = sp.valid_counts(None, batch_size=1, device=device)
         sp.overlap_gradient_sum(layer)   # parameter-gradient SUMs overlap the rest of the backward pass
-        if os.environ.get("MEMSOLVE_BENCH_COLLECTIVE_STATS", "0") != "1":
-            sp.use_peer_exchange()       # statistics summed by one kernel over NVLink peer memory
+        # statistics and large gradients summed by kernels over NVLink peer memory (verified on 2 GPUs;
+        # MEMSOLVE_BENCH_PEER_EXCHANGE=1 / 0 forces it on / off for any number of GPUs)
+        choice = os.environ.get("MEMSOLVE_BENCH_PEER_EXCHANGE", "")
+        if choice == "1" or (choice != "0" and world == 2):
+            sp.use_peer_exchange()
 
     def step(xin, grad_out):
         layer.zero_grad(set_to_none=True)
