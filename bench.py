@@ -293,8 +293,8 @@ def time_kernels(layer, cfg, tokens, device, reps=10, warm=3, with_graph=True):
 
 # DRAM bytes (read + write) of one launch at 32768 tokens, rank 32, from the ncu capture summarised in
 # profiles/ (full ncu capture of the mixer kernels).  Traffic of these streaming kernels grows in proportion to tokens.
-_NCU_DRAM_BYTES_C3 = {"stats_forward": 87.7e6, "readout": 104.9e6, "stats_backward": 138.6e6,
-                      "token_backward": 177.3e6}
+_NCU_DRAM_BYTES_C3 = {"stats_forward": 87.4e6, "readout": 104.4e6, "stats_backward": 137.9e6,
+                      "token_backward": 176.8e6}
 
 
 def _ncu_traffic(workload, kernel, tokens):
@@ -557,7 +557,7 @@ def main():
         kern = time_kernels(build_layer(cfg, device), cfg, tokens, device, reps=args.reps, warm=args.kernel_warmup,
                             with_graph=args.reps > 1)
         print(json.dumps({k: {"us": round(v["s"] * 1e6, 2), "gbs": round(v["bytes"] / v["s"] / 1e9, 1)}
-                          for k, v in kern.items()}))
+                          for k, v in kern.items() if v["s"] > 0}))
         return
     if args.impl == "reference":
         run_reference(args, cfg)
