@@ -245,6 +245,55 @@ def test_stagewise_forward(cuda_mod, rank, head_dim, length, rot):
     assert torch.equal(tape2.inverse, tape.inverse) and torch.equal(tape2.coeff, tape.coeff)
 
 
+@pytest.mark.parametrize("rank,head_dim,length", [(32, 64, 5000), (64, 64, 777), (16, 24, 130)])
+def test_exchange_entry_points_single_rank(cuda_mod, rank, head_dim, length):
+    """ms_stats_exchange with one rank (no peer) must give the library's own reduction of the partials
+    bit for bit, forward and adjoint, call after call (both parities of the double buffer);
+    ms_peer_sum with one rank leaves the values unchanged."""
+    lib = cuda_mod._LIB
+    heads, batch = 2, 2
+    proj, base, eta_raw, counts, cos, sin, dy = _random_case(70 + rank, batch, length, heads, rank, head_dim, rot=True)
+    dp, db, ddy = proj.cuda(), base.cuda(), dy.bfloat16().cuda().contiguous()
+    dcos, dsin = _dev(cos), _dev(sin)
+    shape, dims, tape, ws = _stage_buffers(cuda_mod, dp, db, dcos)
+    stream = torch.cuda.current_stream().cuda_stream
+    area_bytes = int(lib.ms_exchange_area_bytes(ctypes.byref(shape)))
+    assert area_bytes > 0
+    area = torch.zeros(area_bytes // 4 + 64, device="cuda")
+    areas = (ctypes.c_void_p * 1)(area.data_ptr())
+    for backward in (0, 1, 0, 1, 1, 0):
+        want = torch.empty(lib.ms_packed_stats_floats(ctypes.byref(shape), backward), device="cuda")
+        got = torch.full_like(want, float("nan"))
+        if backward:
+            assert lib.ms_stats_backward(ctypes.byref(shape), dp.data_ptr(), ddy.data_ptr(), dcos.data_ptr(),
+                                         dsin.data_ptr(), None, ws.data_ptr(), ws.numel(), want.data_ptr(),
+                                         stream) == 0
+        else:
+            assert lib.ms_stats_forward(ctypes.byref(shape), dp.data_ptr(), dcos.data_ptr(), dsin.data_ptr(), None,
+                                        ws.data_ptr(), ws.numel(), want.data_ptr(), stream) == 0
+        assert lib.ms_stats_exchange(ctypes.byref(shape), backward, ws.data_ptr(), ws.numel(), None, areas,
+                                     area_bytes, 1, 0, got.data_ptr(), stream) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    # argument checks
+    assert lib.ms_stats_exchange(ctypes.byref(shape), 0, ws.data_ptr(), ws.numel(), None, areas, 64, 1, 0,
+                                 got.data_ptr(), stream) != 0
+    assert lib.ms_stats_exchange(ctypes.byref(shape), 0, ws.data_ptr(), ws.numel(), None, areas, area_bytes, 9, 0,
+                                 got.data_ptr(), stream) != 0
+
+    values = torch.randn(4096 + 4 * rank, device="cuda")
+    keep = values.clone()
+    sum_bytes = int(lib.ms_peer_sum_area_bytes(values.numel()))
+    sum_area = torch.zeros(sum_bytes // 4 + 64, device="cuda")
+    sum_areas = (ctypes.c_void_p * 1)(sum_area.data_ptr())
+    for _ in range(3):
+        assert lib.ms_peer_sum(values.data_ptr(), values.numel(), sum_areas, sum_bytes, 1, 0, stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(values, keep)
+    assert lib.ms_peer_sum(values.data_ptr(), values.numel() - 1, sum_areas, sum_bytes, 1, 0, stream) != 0
+    assert lib.ms_device_error() == 0
+
+
 def test_fp32_readout_before_rounding(cuda_mod):
     """On an identical BF16 projection the coefficients W in FP32 reproduce the reference's
     frame formulation to <= 1e-4 (the FP32 criterion), checked before the BF16 store by
