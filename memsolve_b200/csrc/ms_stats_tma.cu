@@ -8,12 +8,12 @@
 // warp fit its registers (forward: rank 16 or 32; adjoint: rank 16, 32 or 64).
 //
 // A CTA owns one (system, token chunk, 64-channel block) and produces one partial, exactly like
-// the generic kernel, but its eight warps never meet at a barrier while streaming: each warp
-// takes every eighth 16-token slice of the chunk, lane 0 brings the slice's relation / content /
+// the generic kernel, but its warps (eight to twelve) never meet at a barrier while streaming: warp w
+// of W takes the 16-token slices w, w + W, ... of the chunk, lane 0 brings the slice's relation / content /
 // gradient boxes and its rotary table rows into the warp's own ring of shared-memory stages
 // with TMA (one mbarrier per stage), the warp rotates the content in FP32, splits it into two
 // BF16 words and feeds mma.sync with the full r x (r + 64) accumulator held in registers.
-// At the end the eight accumulators are added in warp order through shared memory.
+// At the end the warps' accumulators are added in warp order through shared memory.
 #include "ms_core.cuh"
 #include "ms_tma.cuh"
 
@@ -257,7 +257,7 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (!ok && lane == 0) atomicExch(p.error, kErrBarrierTimeout);
   __syncthreads();
 
-  // ---- add the eight warp accumulators in warp order, write one partial ---------------
+  // ---- add the warp accumulators in warp order, write one partial ---------------------
   constexpr int RCOLS = Cfg::RCOLS;
   float* red = reinterpret_cast<float*>(smem_gen);
   {
