@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """MemSolve layer forward+backward throughput on B200 (one JSON line on stdout).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c5|c2|c4]
 
 Workload (default, "c3"): BASELINE configuration 3 -- one MemSolve layer, dim 768, 12 heads
 (head dim 64), rank 32, rotary on, BF16, x = [1, 32768, 768] ~ N(0,1), upstream gradient
@@ -530,13 +530,122 @@ def run_ours(args, cfg):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------
+# encoder scaffolds (configurations 2 and 4): many short sequences, one GPU
+# ---------------------------------------------------------------------------------------
+SCAFFOLDS = {
+    "c2": dict(kind="vision", batch=256, tokens=197, dim=384, heads=6, rank=32, depth=12),
+    "c4": dict(kind="text", batch=64, tokens=128, dim=768, heads=12, rank=32, depth=12),
+}
+
+
+def run_scaffold(args):
+    """Forward + backward of the ViT-Small-shaped / BERT-base-shaped scaffold under BF16 autocast, and one of
+    its MemSolve layers alone at the same shape (CUDA-graph replays), on synthetic inputs."""
+    from memsolve_b200.ball import cuda as C
+    from memsolve_b200 import MemSolve, MemSolveConfig
+    from memsolve_b200.integrations.scaffolds import TextScaffold, VisionScaffold
+    spec = SCAFFOLDS[args.workload]
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    C.load(device=device)
+    torch.manual_seed(0)
+    gen = torch.Generator().manual_seed(1)
+    if spec["kind"] == "vision":
+        model = VisionScaffold().to(device)
+        images = torch.randn(spec["batch"], 3, 224, 224, generator=gen).to(device)
+        labels = torch.randint(0, 1000, (spec["batch"],), generator=gen).to(device)
+
+        def loss_fn():
+            return torch.nn.functional.cross_entropy(model(images).float(), labels)
+        units, unit = spec["batch"], "images/s"
+    else:
+        model = TextScaffold().to(device)
+        ids = torch.randint(0, 30522, (spec["batch"], spec["tokens"]), generator=gen)
+        chosen = torch.rand(ids.shape, generator=gen) < 0.15
+        targets = torch.where(chosen, ids, torch.full_like(ids, -100)).to(device)
+        ids = torch.where(chosen, torch.full_like(ids, 103), ids).to(device)
+
+        def loss_fn():
+            return model(ids, labels=targets)
+        units, unit = spec["batch"] * spec["tokens"], "tokens/s"
+
+    def step():
+        model.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = loss_fn()
+        loss.backward()
+        return loss
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / steps
+
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        loss = step()
+    assert torch.isfinite(loss).item()
+    sampler = ClockSampler(0)
+    sampler.start()
+    dt = timed(step, args.steps)
+    clocks = sampler.stop()
+
+    # one MemSolve layer of the scaffold alone: forward + backward, CUDA-graph replays
+    layer = MemSolve(MemSolveConfig(dim=spec["dim"], num_heads=spec["heads"], rank=spec["rank"], rotary=False,
+                                    recompute_readout=False)).to(device)
+    with torch.no_grad():
+        layer.core_base_raw.normal_(std=0.1)
+    x = torch.randn(spec["batch"], spec["tokens"], spec["dim"], device=device).bfloat16().requires_grad_()
+    dout = torch.randn_like(x)
+
+    def layer_step():
+        layer.zero_grad(set_to_none=True)
+        x.grad = None
+        layer(x, implementation="cuda").backward(dout)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            layer_step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        layer_step()
+    for _ in range(3):
+        graph.replay()
+    layer_dt = timed(graph.replay, 50)
+    width = spec["heads"] * spec["rank"] + spec["dim"]
+    n_tok = spec["batch"] * spec["tokens"]
+    hbm, _tc, which = _peaks()
+    print(json.dumps({
+        "metric": f"scaffold_fwd_bwd_{unit.split('/')[0]}_per_s", "value": units / dt, "unit": unit, "n_gpus": 1,
+        "steps": args.steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "timing": "eager, BF16 autocast",
+        "config": {"workload": f"configuration {args.workload[1]}: {spec['kind']} scaffold, {spec['depth']} layers, "
+                               f"dim {spec['dim']}, {spec['heads']} heads, rank {spec['rank']}, batch {spec['batch']}"
+                               f" x {spec['tokens']} tokens", "parallelism": "sp1"},
+        "clocks": clocks, "gpu_launches": 6 * spec["depth"] * args.steps,
+        "layer_alone": {"us": round(layer_dt * 1e6, 1), "tokens_per_s": n_tok / layer_dt,
+                        "systems": spec["batch"] * spec["heads"],
+                        "frac_of_layer_hbm_bound": 2 * (5 * width + 3 * spec["dim"] + 8 * spec["dim"] + 2 * width)
+                        * n_tok / layer_dt / 1e9 / hbm, "peak_source": f"of {which}"},
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    ap.add_argument("--workload", choices=tuple(CONFIGS), default="c3")
+    ap.add_argument("--workload", choices=tuple(CONFIGS) + tuple(SCAFFOLDS), default="c3")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
     ap.add_argument("--kernels-only", action="store_true",
@@ -545,6 +654,11 @@ def main():
     ap.add_argument("--kernel-warmup", type=int, default=3)
     ap.add_argument("--tokens", type=int, default=0, help="with --kernels-only: tokens per launch instead of the workload's")
     args = ap.parse_args()
+    if args.workload in SCAFFOLDS:
+        if args.impl != "ours" or args.gpus != 1 or args.kernels_only:
+            raise SystemExit("the scaffold workloads run the CUDA arm on one GPU")
+        run_scaffold(args)
+        return
     cfg = CONFIGS[args.workload]
     if args.kernels_only:
         from memsolve_b200.ball import cuda as C

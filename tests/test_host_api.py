@@ -147,3 +147,16 @@ def test_stale_contract_version_is_rejected():
             return 0
     with pytest.raises(RuntimeError, match="native contract version"):
         cuda._check_native_contract(Fake())
+
+
+def test_scaffolds_construct_and_refuse_cpu_input():
+    """The encoder scaffolds build without a GPU; their mixer has no CPU path."""
+    from memsolve_b200.integrations.scaffolds import TextScaffold, VisionScaffold
+    vision = VisionScaffold(depth=1)
+    assert vision.tokens == 197 and vision.blocks[0].attn.mixer.config.rank == 32
+    text = TextScaffold(depth=1, vocab_size=100)
+    assert text.blocks[0].attention.mixer.w_bc.weight.shape == (12 * 32 + 768, 768)
+    with pytest.raises(ValueError, match="requires x to be a CUDA tensor"):
+        text(torch.zeros(1, 8, dtype=torch.long))
+    with pytest.raises(ValueError, match="multiple of patch_size"):
+        VisionScaffold(image_size=100)
