@@ -195,7 +195,7 @@ def workload_config(args, cfg, world):
 # ---------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------
-def time_kernels(layer, cfg, tokens, device, reps=10, warm=3, with_graph=True):
+def time_kernels(layer, cfg, tokens, device, reps=10, warm=3, with_graph=True, batch=1, rotary=True):
     """Each mixer kernel alone, CUDA events on the launching stream, L2 flushed before each launch."""
     import ctypes
     from memsolve_b200.ball import cuda as C
@@ -204,41 +204,45 @@ def time_kernels(layer, cfg, tokens, device, reps=10, warm=3, with_graph=True):
     d = dim // heads
     width = heads * rank + dim
     g = torch.Generator(device="cpu").manual_seed(1)
-    proj = (torch.randn(1, tokens, width, generator=g) * 0.5).bfloat16().to(device)
-    dy = torch.randn(1, tokens, dim, generator=g).bfloat16().to(device)
+    proj = (torch.randn(batch, tokens, width, generator=g) * 0.5).bfloat16().to(device)
+    dy = torch.randn(batch, tokens, dim, generator=g).bfloat16().to(device)
     pos = torch.arange(tokens, device=device)[None]
     from memsolve_b200.ball.rotary import rotary_position_factors
-    cos, sin = rotary_position_factors(pos, head_dim=d, base=10000.0, train_length=128, context_length=tokens,
-                                       scaling="yarn")
+    cos = sin = None
+    if rotary:
+        cos, sin = rotary_position_factors(pos, head_dim=d, base=10000.0, train_length=128,
+                                           context_length=tokens, scaling="yarn")
     base, raw = layer.core_base_raw.detach(), layer.eta_raw.detach()
     shape, dims = C._make_shape(proj, base, cos)
     tape = C._alloc_tape(dims, device)
     tc = tape.as_struct()
     ws = C._workspace(shape, device)
     dpad = lib.ms_padded_head_dim(d)
-    mixed = torch.empty(1, tokens, dim, device=device, dtype=torch.bfloat16)
-    gg = torch.empty(1, heads, 2, rank, rank, device=device, dtype=torch.bfloat16)
-    cg = torch.empty(1, heads, 2, rank, dpad, device=device, dtype=torch.bfloat16)
+    mixed = torch.empty(batch, tokens, dim, device=device, dtype=torch.bfloat16)
+    gg = torch.empty(batch, heads, 2, rank, rank, device=device, dtype=torch.bfloat16)
+    cg = torch.empty(batch, heads, 2, rank, dpad, device=device, dtype=torch.bfloat16)
     dproj = torch.empty_like(proj)
     dbase = torch.empty_like(base)
     draw = torch.empty_like(raw)
     st = torch.cuda.current_stream(device).cuda_stream
     S = ctypes.byref(shape)
     T = ctypes.byref(tc)
+    cos_p = cos.data_ptr() if rotary else None
+    sin_p = sin.data_ptr() if rotary else None
     calls = {
         "core_forward": lambda: lib.ms_core_forward(S, base.data_ptr(), raw.data_ptr(), T, st),
-        "stats_forward": lambda: lib.ms_stats_forward(S, proj.data_ptr(), cos.data_ptr(), sin.data_ptr(), None,
+        "stats_forward": lambda: lib.ms_stats_forward(S, proj.data_ptr(), cos_p, sin_p, None,
                                                       ws.data_ptr(), ws.numel(), None, st),
         "compact_forward": lambda: lib.ms_compact_forward(S, None, ws.data_ptr(), ws.numel(), None, T, st),
-        "readout": lambda: lib.ms_readout(S, proj.data_ptr(), cos.data_ptr(), sin.data_ptr(), None, T,
+        "readout": lambda: lib.ms_readout(S, proj.data_ptr(), cos_p, sin_p, None, T,
                                           mixed.data_ptr(), st),
-        "stats_backward": lambda: lib.ms_stats_backward(S, proj.data_ptr(), dy.data_ptr(), cos.data_ptr(),
-                                                        sin.data_ptr(), None, ws.data_ptr(), ws.numel(), None, st),
+        "stats_backward": lambda: lib.ms_stats_backward(S, proj.data_ptr(), dy.data_ptr(), cos_p,
+                                                        sin_p, None, ws.data_ptr(), ws.numel(), None, st),
         "compact_backward": lambda: lib.ms_compact_backward(S, None, ws.data_ptr(), ws.numel(), None, T,
                                                             base.data_ptr(), raw.data_ptr(), 1.0, gg.data_ptr(),
                                                             cg.data_ptr(), dbase.data_ptr(), draw.data_ptr(), st),
-        "token_backward": lambda: lib.ms_token_backward(S, proj.data_ptr(), dy.data_ptr(), cos.data_ptr(),
-                                                        sin.data_ptr(), None, T, gg.data_ptr(), cg.data_ptr(),
+        "token_backward": lambda: lib.ms_token_backward(S, proj.data_ptr(), dy.data_ptr(), cos_p,
+                                                        sin_p, None, T, gg.data_ptr(), cg.data_ptr(),
                                                         dproj.data_ptr(), st),
     }
     bpt = {  # algorithmic bytes per token (BF16): packed row = 2*width, mixed row = 2*dim
@@ -248,11 +252,11 @@ def time_kernels(layer, cfg, tokens, device, reps=10, warm=3, with_graph=True):
     # the whole mix core (ms_mix_forward + ms_mix_backward: six launches) as one CUDA graph, replayed
     # back to back; its tensors (projected, mixed, dy, dprojected: 250 MB at 32768 tokens) exceed L2
     def mix_core():
-        assert lib.ms_mix_forward(S, proj.data_ptr(), base.data_ptr(), raw.data_ptr(), cos.data_ptr(),
-                                  sin.data_ptr(), None, ws.data_ptr(), ws.numel(), T, mixed.data_ptr(),
+        assert lib.ms_mix_forward(S, proj.data_ptr(), base.data_ptr(), raw.data_ptr(), cos_p,
+                                  sin_p, None, ws.data_ptr(), ws.numel(), T, mixed.data_ptr(),
                                   torch.cuda.current_stream(device).cuda_stream) == 0
         assert lib.ms_mix_backward(S, proj.data_ptr(), dy.data_ptr(), base.data_ptr(), raw.data_ptr(),
-                                   cos.data_ptr(), sin.data_ptr(), None, ws.data_ptr(), ws.numel(), T,
+                                   cos_p, sin_p, None, ws.data_ptr(), ws.numel(), T,
                                    gg.data_ptr(), cg.data_ptr(), dproj.data_ptr(), dbase.data_ptr(),
                                    draw.data_ptr(), torch.cuda.current_stream(device).cuda_stream) == 0
 
@@ -287,7 +291,7 @@ def time_kernels(layer, cfg, tokens, device, reps=10, warm=3, with_graph=True):
             e1.record()
             e1.synchronize()
             ts.append(e0.elapsed_time(e1) * 1e-3)
-        out[name] = {"s": sum(ts) / len(ts), "bytes": bpt.get(name, 0) * tokens}
+        out[name] = {"s": sum(ts) / len(ts), "bytes": bpt.get(name, 0) * tokens * batch}
     return out
 
 
@@ -655,8 +659,20 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="with --kernels-only: tokens per launch instead of the workload's")
     args = ap.parse_args()
     if args.workload in SCAFFOLDS:
-        if args.impl != "ours" or args.gpus != 1 or args.kernels_only:
+        if args.impl != "ours" or args.gpus != 1:
             raise SystemExit("the scaffold workloads run the CUDA arm on one GPU")
+        if args.kernels_only:
+            from memsolve_b200.ball import cuda as C
+            spec = SCAFFOLDS[args.workload]
+            device = torch.device("cuda", 0)
+            torch.cuda.set_device(device)
+            C.load(device=device)
+            cfg = dict(dim=spec["dim"], heads=spec["heads"], rank=spec["rank"])
+            kern = time_kernels(build_layer(cfg, device), cfg, spec["tokens"], device, reps=args.reps,
+                                warm=args.kernel_warmup, with_graph=args.reps > 1, batch=spec["batch"], rotary=False)
+            print(json.dumps({k: {"us": round(v["s"] * 1e6, 2), "gbs": round(v["bytes"] / v["s"] / 1e9, 1)}
+                              for k, v in kern.items() if v["s"] > 0}))
+            return
         run_scaffold(args)
         return
     cfg = CONFIGS[args.workload]

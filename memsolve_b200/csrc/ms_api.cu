@@ -51,6 +51,16 @@ int sm_count() {
   return v;
 }
 
+thread_local bool g_chain_launches = false;
+
+bool chaining_allowed() {
+  static const bool allowed = [] {
+    const char* v = std::getenv("MEMSOLVE_NO_CHAIN");
+    return !(v && v[0] == '1');
+  }();
+  return allowed;
+}
+
 int ensure_dynamic_smem(const void* kernel, int bytes) {
   struct Entry { const void* kernel; int device; int bytes; };
   static std::mutex mu;
@@ -376,6 +386,8 @@ int ms_mix_forward(const ms_shape* shape, const void* projected, const float* ba
   // the per-head core (eta, F) is computed by spare CTAs of the statistics grid
   MS_TRY(launch_stats(*shape, stats_plan, false, projected, nullptr, cos, sin, w.partials, nullptr, base_raw,
                       eta_raw, tape, st));
+  // the two launches below start while the kernel ahead of them drains (see launch_kernel)
+  ChainScope chain(chaining_allowed());
   MS_TRY(launch_compact_forward(*shape, plan, counts, w.partials, false, *tape, st));
   Plan read_plan = plan;
   read_plan.aligned = plan.aligned && is16(projected) && is16(mixed);
@@ -525,6 +537,7 @@ int ms_mix_backward(const ms_shape* shape, const void* projected, const void* dy
   const Plan plan = make_plan(*shape);
   const Workspace w = carve(workspace, plan);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ChainScope chain(chaining_allowed());
   MS_TRY(launch_compact_backward(*shape, plan, counts, w.partials, w.de_partials, false, *tape, w.hmat,
                                  w.de_sys, gram_grad, cross_grad, st));
   // the token pass needs only dG and dQ; the per-head core adjoint rides in spare CTAs of its grid

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #include "../../include/memsolve_b200.h"
 
 // Phase time stamps for development builds (-DMS_PROFILE_TICKS); compiled out of the library.
@@ -71,6 +73,46 @@ struct CoreAdjoint {
   float grad_scale;
 };
 
+// ---------------------------------------------------------------------------------------
+// chained launches (programmatic dependent launch)
+// ---------------------------------------------------------------------------------------
+// While this flag is set on the calling thread, launch_kernel() lets the new grid start as soon as
+// every block of the previous kernel in the stream has passed grid_launch_dependents(): its blocks
+// become resident and set up their shared memory while the previous grid drains.  Every kernel of this
+// library calls grid_dependency_wait() before its first access to global memory; that call returns
+// once the previous grid has completed and its writes are visible (at once for a normal launch).
+// The statistics and compact kernels signal after their main loop: signalling at the start of the
+// kernel parks the next grid's blocks on the SMs for the whole kernel and measured slower than no
+// chaining at all (189 us against 179 us for the six launches at 32768 tokens; 174 us signalling late).
+// Only the second and third launch of ms_mix_forward / ms_mix_backward are chained, so the kernel
+// ahead of a chained launch is always one of this library's (chaining the first launch to the
+// caller's kernel ahead of it measured no gain).
+extern thread_local bool g_chain_launches;
+struct ChainScope {
+  bool before;
+  explicit ChainScope(bool on) : before(g_chain_launches) { g_chain_launches = on; }
+  ~ChainScope() { g_chain_launches = before; }
+};
+bool chaining_allowed();   // false when the environment sets MEMSOLVE_NO_CHAIN=1
+
+template <typename... Expected, typename... Actual>
+inline void launch_kernel(void (*kernel)(Expected...), dim3 grid, dim3 block, size_t smem_bytes, cudaStream_t st,
+                          Actual&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem_bytes;
+  config.stream = st;
+  cudaLaunchAttribute chain;
+  chain.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  chain.val.programmaticStreamSerializationAllowed = 1;
+  if (g_chain_launches) {
+    config.attrs = &chain;
+    config.numAttrs = 1;
+  }
+  cudaLaunchKernelEx(&config, kernel, std::forward<Actual>(args)...);
+}
+
 Plan make_plan(const ms_shape& s);
 int check_shape(const ms_shape* s);
 int sm_count();
@@ -81,6 +123,12 @@ int ensure_dynamic_smem(const void* kernel, int bytes);
 // ---------------------------------------------------------------------------------------
 // XOR the 16-byte-chunk bits [4,7) of a byte offset with bits [7,10): conflict-free ldmatrix
 // for densely packed rows of 32/64/128 bytes.
+// see launch_kernel(): both are no-ops for a grid that was launched the normal way
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t swz(uint32_t off) { return off ^ (((off >> 7) & 7u) << 4); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

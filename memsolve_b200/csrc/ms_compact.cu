@@ -281,6 +281,7 @@ compact_forward_kernel(const CompactFwdParams p) {
   uint64_t* bar = reinterpret_cast<uint64_t*>(dscale + R);      // 2 words
   float* stage = reinterpret_cast<float*>(bar + 2);             // chunks * pf when staged
 
+  grid_dependency_wait();
   const int tid = threadIdx.x;
   const int sys = blockIdx.x;
   const int b = sys / p.heads, h = sys - b * p.heads;
@@ -336,6 +337,7 @@ compact_forward_kernel(const CompactFwdParams p) {
   MS_TICK(1);
   cholesky_inverse_cta<R>(gs, ts, tT, rowbuf, colbuf, dscale, tid);
   __syncthreads();
+  grid_launch_dependents();
   MS_TICK(2);
   for (int i = tid; i < R * R; i += kCompactThreads) {
     const int row = i / R, col = i - row * R;
@@ -468,6 +470,7 @@ compact_backward_kernel(const CompactBwdParams p) {
   uint64_t* bar = reinterpret_cast<uint64_t*>(zs + R * kQP);
   float* stage = reinterpret_cast<float*>(bar + 2);
 
+  grid_dependency_wait();
   const int tid = threadIdx.x;
   const int sys = blockIdx.x;
   const int b = sys / p.heads, h = sys - b * p.heads;
@@ -609,6 +612,7 @@ compact_backward_kernel(const CompactBwdParams p) {
   }
 
   MS_TICK(16);
+  grid_launch_dependents();
   // H to shared memory and to global (for the per-head sum over the batch)
 #pragma unroll
   for (int e = 0; e < RT_PER; ++e) {
@@ -687,6 +691,8 @@ core_forward_kernel(const float* __restrict__ base_raw, const float* __restrict_
                     float* __restrict__ eta_out, float* __restrict__ slope_out, float* __restrict__ core_map,
                     int* __restrict__ core_info) {
   extern __shared__ __align__(16) double dsm[];
+  grid_launch_dependents();
+  grid_dependency_wait();
   core_forward_device<R, kCompactThreads>(base_raw, eta_raw, blockIdx.x, complement, eta_out, slope_out, core_map,
                                           core_info, reinterpret_cast<unsigned char*>(dsm), threadIdx.x);
 }
@@ -697,6 +703,8 @@ core_backward_kernel(const float* __restrict__ base_raw, const float* __restrict
                      const float* __restrict__ core_map, int r, int heads, int batch, int complement,
                      float grad_scale, float* __restrict__ d_base, float* __restrict__ d_eta_raw) {
   extern __shared__ double dsm[];
+  grid_launch_dependents();
+  grid_dependency_wait();
   core_backward_device(base_raw, hmat, de_sys, slope, core_map, r, blockIdx.x, heads, batch, complement,
                        grad_scale, d_base, d_eta_raw, reinterpret_cast<unsigned char*>(dsm), threadIdx.x,
                        kCompactThreads);
@@ -718,7 +726,7 @@ static int launch_core_fwd_r(const ms_shape& s, const float* base_raw, const flo
                              cudaStream_t st) {
   const size_t bytes = core_forward_smem_bytes(R);
   if (set_smem(core_forward_kernel<R>, bytes)) return MS_ERR_LAUNCH;
-  core_forward_kernel<R><<<s.heads, kCompactThreads, bytes, st>>>(base_raw, eta_raw, s.complement, t.eta,
+  launch_kernel(core_forward_kernel<R>, dim3(s.heads), dim3(kCompactThreads), bytes, st, base_raw, eta_raw, s.complement, t.eta,
                                                                  t.eta_slope, t.core_map, t.core_info);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
@@ -752,7 +760,7 @@ static int launch_compact_fwd_r(CompactFwdParams& p, int systems, cudaStream_t s
   p.staged = stage != 0;
   const size_t bytes = fixed * sizeof(float) + stage;
   if (set_smem(compact_forward_kernel<R>, bytes)) return MS_ERR_LAUNCH;
-  compact_forward_kernel<R><<<systems, kCompactThreads, bytes, st>>>(p);
+  launch_kernel(compact_forward_kernel<R>, dim3(systems), dim3(kCompactThreads), bytes, st, p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
 
@@ -784,7 +792,7 @@ static int launch_compact_bwd_r(CompactBwdParams& p, int systems, cudaStream_t s
   p.staged = stage != 0;
   const size_t bytes = fixed * sizeof(float) + stage;
   if (set_smem(compact_backward_kernel<R>, bytes)) return MS_ERR_LAUNCH;
-  compact_backward_kernel<R><<<systems, kCompactThreads, bytes, st>>>(p);
+  launch_kernel(compact_backward_kernel<R>, dim3(systems), dim3(kCompactThreads), bytes, st, p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
 
@@ -818,7 +826,7 @@ int launch_core_backward(const ms_shape& s, const float* base_raw, const float* 
                          cudaStream_t st) {
   const size_t bytes = core_backward_smem_bytes(s.rank);
   if (set_smem(core_backward_kernel, bytes)) return MS_ERR_LAUNCH;
-  core_backward_kernel<<<s.heads, kCompactThreads, bytes, st>>>(base_raw, hmat, de_sys, t.eta_slope,
+  launch_kernel(core_backward_kernel, dim3(s.heads), dim3(kCompactThreads), bytes, st, base_raw, hmat, de_sys, t.eta_slope,
                                                                t.core_map, s.rank, s.heads, s.batch,
                                                                s.complement, grad_scale, d_base, d_eta_raw);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;

@@ -57,6 +57,7 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  grid_launch_dependents();
   const int b = blockIdx.y;
   const int h0 = blockIdx.z * p.group_heads;
   const int gh = min(p.group_heads, p.heads - h0);
@@ -72,6 +73,7 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     mbar_fence_init();
   }
   __syncthreads();
+  grid_dependency_wait();
   if (tid == 0) {
     mbar_expect_tx(wbar, (uint32_t)(mats * 2 * Cfg::W_BYTES));
     for (int m = 0; m < mats; ++m) {
@@ -291,11 +293,11 @@ static int launch_readout_tma_cfg(const ms_shape& s, const Plan& plan, const voi
   if (rot) {
     auto kern = readout_tma_kernel<R, true, Cfg>;
     if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
-    kern<<<grid, WARPS * 32, smem_bytes, st>>>(map_a, map_c, map_w, map_y, p);
+    launch_kernel(kern, grid, dim3(WARPS * 32), smem_bytes, st, map_a, map_c, map_w, map_y, p);
   } else {
     auto kern = readout_tma_kernel<R, false, Cfg>;
     if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
-    kern<<<grid, WARPS * 32, smem_bytes, st>>>(map_a, map_c, map_w, map_y, p);
+    launch_kernel(kern, grid, dim3(WARPS * 32), smem_bytes, st, map_a, map_c, map_w, map_y, p);
   }
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }

@@ -81,6 +81,7 @@ stats_kernel(const StatsParams p) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int wm = warp % MS, wk = warp / MS;
   const int chunk = blockIdx.x, sys = blockIdx.y, dblk = blockIdx.z;
+  grid_dependency_wait();
   if (!GRAD && chunk == p.chunks) {
     // spare column of the grid: the per-head core runs beside the token reduction
     if (dblk == 0 && sys < p.heads)
@@ -255,6 +256,7 @@ stats_kernel(const StatsParams p) {
     }
   }
   cp_async_wait<0>();
+  grid_launch_dependents();   // the next kernel may become resident while the partial is reduced and written
   __syncthreads();
 
   // ---- combine the KS token-slices of the CTA, then write one partial -----------------
@@ -326,6 +328,8 @@ __global__ void pack_stats_kernel(const float* __restrict__ partials, const floa
                                   const float* __restrict__ counts, float* __restrict__ packed,
                                   int heads, int tokens, int chunks, int de_slots, int gram_floats,
                                   int partial_floats, int systems, int grad) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int sys = blockIdx.y;
   const int b = sys / heads;
   const float n = counts ? counts[b] : (float)tokens;
@@ -348,7 +352,7 @@ static int launch_one(const StatsParams& p, dim3 grid, cudaStream_t st) {
   using Sm = StatsSmem<R, GRAD, ROT>;
   auto kern = stats_kernel<R, GRAD, ROT, ALIGNED>;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Sm::TOTAL) != MS_OK) return MS_ERR_LAUNCH;
-  kern<<<grid, StatsCfg<R>::MS * StatsCfg<R>::KS * 32, Sm::TOTAL, st>>>(p);
+  launch_kernel(kern, grid, dim3(StatsCfg<R>::MS * StatsCfg<R>::KS * 32), Sm::TOTAL, st, p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
 

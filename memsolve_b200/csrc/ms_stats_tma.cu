@@ -76,6 +76,8 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int chunk = blockIdx.x, sys = blockIdx.y, dblk = blockIdx.z;
   if (!GRAD && chunk == p.chunks) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     // spare column of the grid: the per-head core runs beside the token reduction
     if (dblk == 0 && sys < p.heads)
       core_forward_device<R, NT>(p.base_raw, p.eta_raw, sys, p.complement, p.eta, p.eta_slope, p.core_map,
@@ -103,6 +105,7 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     mbar_fence_init();
   }
   __syncthreads();
+  grid_dependency_wait();
 
   // stage layout: [X: dY (adjoint) or C][C (adjoint only)][cos][sin][A]
   constexpr int OFF_C = Cfg::X_BYTES;
@@ -255,6 +258,7 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   }
   if (!ok && lane == 0) atomicExch(p.error, kErrBarrierTimeout);
+  grid_launch_dependents();
   __syncthreads();
 
   // ---- add the warp accumulators in warp order, write one partial ---------------------
@@ -326,7 +330,7 @@ static int launch_stats_tma_one(const ms_shape& s, const Plan& plan, const CUten
   auto kern = stats_tma_kernel<R, GRAD, ROT, CB, STAGES, WARPS>;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Cfg::TOTAL)) return MS_ERR_LAUNCH;
   dim3 grid(plan.chunks + (fuse_core ? 1 : 0), plan.systems, s.head_dim / CB);
-  kern<<<grid, WARPS * 32, Cfg::TOTAL, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+  launch_kernel(kern, grid, dim3(WARPS * 32), Cfg::TOTAL, st, maps[0], maps[1], maps[2], maps[3], maps[4], p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
 

@@ -91,6 +91,8 @@ readout_kernel(const TokenParams p) {
   const uint32_t smem = (smem_u32(smem_raw) + 127u) & ~127u;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int b = blockIdx.y;
   const int tk = blockIdx.x * kTileTokens;
   const int rows = min(kTileTokens, p.tokens - tk);
@@ -215,6 +217,8 @@ token_backward_kernel(const TokenParams p) {
   const uint32_t smem = (smem_u32(smem_raw) + 127u) & ~127u;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int b = blockIdx.y;
   if ((int)blockIdx.x >= p.tiles) {
     // spare CTAs: parameter gradients of one head each, beside the token pass
@@ -418,7 +422,7 @@ template <class K>
 static int launch_token(K kern, int smem_bytes, const TokenParams& p, cudaStream_t st) {
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes) != MS_OK) return MS_ERR_LAUNCH;
   dim3 grid(p.tiles + (p.d_eta_raw ? p.heads : 0), p.batch);
-  kern<<<grid, kTokenThreads, smem_bytes, st>>>(p);
+  launch_kernel(kern, grid, dim3(kTokenThreads), smem_bytes, st, p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
 

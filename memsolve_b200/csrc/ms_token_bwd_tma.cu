@@ -112,8 +112,10 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  grid_launch_dependents();
 
   if ((int)blockIdx.x >= p.work_ctas) {
+    grid_dependency_wait();
     if (blockIdx.y == 0 && blockIdx.z == 0)
       core_backward_device(p.base_raw, p.hmat, p.de_sys, p.eta_slope, p.core_map, R, blockIdx.x - p.work_ctas,
                            p.heads, p.batch, p.complement, p.grad_scale, p.d_base, p.d_eta_raw,
@@ -135,6 +137,7 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     mbar_fence_init();
   }
   __syncthreads();
+  grid_dependency_wait();
   if (tid == 0) {
     mbar_expect_tx(rbar, (uint32_t)(gh * Cfg::HEAD_BYTES));
     for (int hl = 0; hl < gh; ++hl) {
@@ -397,11 +400,13 @@ static int launch_token_bwd_tma_cfg(const ms_shape& s, const Plan& plan, const v
   if (s.rotary_rows > 0) {
     auto kern = token_backward_tma_kernel<R, true, Cfg>;
     if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
-    kern<<<grid, kTbWarps * 32, smem_bytes, st>>>(map_a, map_c, map_y, map_w, map_q, map_s, map_oa, map_oc, p);
+    launch_kernel(kern, grid, dim3(kTbWarps * 32), smem_bytes, st, map_a, map_c, map_y, map_w, map_q, map_s, map_oa,
+                  map_oc, p);
   } else {
     auto kern = token_backward_tma_kernel<R, false, Cfg>;
     if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
-    kern<<<grid, kTbWarps * 32, smem_bytes, st>>>(map_a, map_c, map_y, map_w, map_q, map_s, map_oa, map_oc, p);
+    launch_kernel(kern, grid, dim3(kTbWarps * 32), smem_bytes, st, map_a, map_c, map_y, map_w, map_q, map_s, map_oa,
+                  map_oc, p);
   }
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }

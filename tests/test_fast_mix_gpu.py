@@ -181,6 +181,41 @@ def test_bitwise_repeatability(cuda_mod):
         assert torch.equal(ga, gb)
 
 
+_PLAIN_LAUNCH_CHILD = """
+import sys, torch
+sys.path.insert(0, {root!r}); sys.path.insert(0, {tests!r})
+import test_fast_mix_gpu as T
+from memsolve_b200.ball import cuda
+cuda.load()
+out = {{}}
+for k, (rank, d, n, rot) in enumerate({cases!r}):
+    y, grads = T._run_fast(cuda, *T._random_case(11 + k, 2, n, 3, rank, d, rot=rot))
+    out[k] = [y.cpu()] + [g.cpu() for g in grads]
+torch.save(out, {path!r})
+"""
+
+
+def test_chained_launches_match_plain_launches(cuda_mod, tmp_path):
+    """`ms_mix_forward` / `ms_mix_backward` chain their second and third launch to the kernel before
+    (programmatic dependent launch); a child process with MEMSOLVE_NO_CHAIN=1 launches the same kernels
+    the plain way and must produce identical bits (TMA kernels, generic kernels, rank 64)."""
+    import os
+    import subprocess
+    import sys
+    cases = [(32, 64, 3000, True), (64, 64, 700, False), (16, 24, 130, True), (48, 40, 257, False)]
+    here = os.path.dirname(os.path.abspath(__file__))
+    path = str(tmp_path / "plain.pt")
+    code = _PLAIN_LAUNCH_CHILD.format(root=os.path.dirname(here), tests=here, cases=cases, path=path)
+    env = dict(os.environ, MEMSOLVE_NO_CHAIN="1")
+    subprocess.run([sys.executable, "-c", code], check=True, env=env, timeout=600)
+    plain = torch.load(path)
+    for k, (rank, d, n, rot) in enumerate(cases):
+        y, grads = _run_fast(cuda_mod, *_random_case(11 + k, 2, n, 3, rank, d, rot=rot))
+        mine = [y.cpu()] + [g.cpu() for g in grads]
+        for a, b in zip(mine, plain[k]):
+            assert torch.equal(a, b), (rank, d, n, rot)
+
+
 def test_inputs_are_not_mutated(cuda_mod):
     proj, base, eta_raw, counts, cos, sin, dy = _random_case(3, 1, 200, 2, 16, 32, rot=True)
     dev = [t.cuda() for t in (proj, base, eta_raw, cos, sin)]
