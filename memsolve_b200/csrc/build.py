@@ -74,7 +74,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     objs = [r[0] for r in results]
     logs = [r[1] for r in results if r[1]]
     out = library_path()
-    if logs or not os.path.exists(out):
+    stale = not os.path.exists(out) or any(os.path.getmtime(o) > os.path.getmtime(out) for o in objs)
+    if logs or stale:
         cmd = [_nvcc(), "-shared", "-o", out, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
                "-Xcompiler", "-fPIC", "-lcudart"]
         proc = subprocess.run(cmd, capture_output=True, text=True)

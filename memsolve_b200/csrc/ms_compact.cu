@@ -263,8 +263,9 @@ constexpr int compact_fwd_fixed_floats() {
   return R * R + 3 * R * CompactDims<R>::RP + 2 * R * kQP + 2 * (R + 4) + 2 * R + 2 * R + 4;
 }
 
-template <int R>
-__global__ void __launch_bounds__(kCompactThreads)
+// MINB > 1: register budget for that many resident CTAs per SM (many systems: throughput instead of latency)
+template <int R, int MINB = 1>
+__global__ void __launch_bounds__(kCompactThreads, MINB)
 compact_forward_kernel(const CompactFwdParams p) {
   using D = CompactDims<R>;
   constexpr int RP = D::RP;
@@ -453,8 +454,8 @@ constexpr int compact_bwd_fixed_floats() {
   return 5 * R * CompactDims<R>::RP + 3 * R * kQP + 4;
 }
 
-template <int R>
-__global__ void __launch_bounds__(kCompactThreads)
+template <int R, int MINB = 1>
+__global__ void __launch_bounds__(kCompactThreads, MINB)
 compact_backward_kernel(const CompactBwdParams p) {
   using D = CompactDims<R>;
   constexpr int RP = D::RP;
@@ -756,9 +757,20 @@ static size_t staging_bytes(const float* partials, int chunks, size_t floats, si
 template <int R>
 static int launch_compact_fwd_r(CompactFwdParams& p, int systems, cudaStream_t st) {
   const size_t fixed = compact_fwd_fixed_floats<R>();
-  const size_t stage = staging_bytes(p.partials, p.chunks == 0 ? 1 : p.chunks, (size_t)p.pf, fixed);
+  const int nch = p.chunks == 0 ? 1 : p.chunks;
+  // many systems: more CTAs per SM (a smaller register budget, a single partial read straight from global
+  // memory) matter more than the latency of one system
+  const bool many = R <= 32 && nch == 1 && systems >= 2 * sm_count();
+  const size_t stage = many ? 0 : staging_bytes(p.partials, nch, (size_t)p.pf, fixed);
   p.staged = stage != 0;
   const size_t bytes = fixed * sizeof(float) + stage;
+  if constexpr (R <= 32) {
+    if (many) {
+      if (set_smem(compact_forward_kernel<R, 4>, bytes)) return MS_ERR_LAUNCH;
+      launch_kernel(compact_forward_kernel<R, 4>, dim3(systems), dim3(kCompactThreads), bytes, st, p);
+      return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
+    }
+  }
   if (set_smem(compact_forward_kernel<R>, bytes)) return MS_ERR_LAUNCH;
   launch_kernel(compact_forward_kernel<R>, dim3(systems), dim3(kCompactThreads), bytes, st, p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
@@ -788,9 +800,18 @@ int launch_compact_forward(const ms_shape& s, const Plan& plan, const float* cou
 template <int R>
 static int launch_compact_bwd_r(CompactBwdParams& p, int systems, cudaStream_t st) {
   const size_t fixed = compact_bwd_fixed_floats<R>();
-  const size_t stage = staging_bytes(p.partials, p.chunks == 0 ? 1 : p.chunks, (size_t)p.pf, fixed);
+  const int nch = p.chunks == 0 ? 1 : p.chunks;
+  const bool many = R <= 32 && nch == 1 && systems >= 2 * sm_count();   // as in the forward launcher
+  const size_t stage = many ? 0 : staging_bytes(p.partials, nch, (size_t)p.pf, fixed);
   p.staged = stage != 0;
   const size_t bytes = fixed * sizeof(float) + stage;
+  if constexpr (R <= 32) {
+    if (many) {
+      if (set_smem(compact_backward_kernel<R, 4>, bytes)) return MS_ERR_LAUNCH;
+      launch_kernel(compact_backward_kernel<R, 4>, dim3(systems), dim3(kCompactThreads), bytes, st, p);
+      return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
+    }
+  }
   if (set_smem(compact_backward_kernel<R>, bytes)) return MS_ERR_LAUNCH;
   launch_kernel(compact_backward_kernel<R>, dim3(systems), dim3(kCompactThreads), bytes, st, p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;

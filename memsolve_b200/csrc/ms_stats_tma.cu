@@ -22,7 +22,7 @@ namespace ms {
 
 // CB: channels of one CTA (64, or 32 so that two CTAs with half the accumulators share an SM; the
 // Gram columns are then divided between the first two channel blocks of a head).
-template <int R, bool GRAD, bool ROT, int CB, int STAGES_, int WARPS_>
+template <int R, bool GRAD, bool ROT, int CB, int STAGES_, int WARPS_, bool SOLO = false>
 struct StatsTmaCfg {
   static constexpr int kStWarps = WARPS_;
   static constexpr int A_SLICE = 16 * R * 2;
@@ -37,7 +37,7 @@ struct StatsTmaCfg {
   static constexpr int GP = (CB == 32 && R >= 32) ? 2 : 1;            // channel blocks sharing the Gram columns
   static constexpr int GCOLS = GRAD ? 0 : R / GP;
   static constexpr int RCOLS = GCOLS + CB;
-  static constexpr int RED = kStWarps * R * RCOLS * 4;
+  static constexpr int RED = SOLO ? 0 : kStWarps * R * RCOLS * 4;
   static constexpr int CORE = GRAD ? 0 : (int)core_forward_smem_bytes(R);
   static constexpr int BODY = RING > RED ? (RING > CORE ? RING : CORE) : (RED > CORE ? RED : CORE);
   static constexpr int BARS = kStWarps * STAGES * 8;
@@ -49,6 +49,7 @@ struct StatsTmaParams {
   float* de_partials;
   int* error;
   int tokens, heads, head_dim, rotary_rows, chunks, chunk_tokens, de_slots, partial_floats;
+  int systems, work_ctas;   // warp-per-system variant: B*H and the CTAs that stream (the rest run the core)
   const float* base_raw;
   const float* eta_raw;
   float* eta;
@@ -58,12 +59,12 @@ struct StatsTmaParams {
   int complement;
 };
 
-template <int R, bool GRAD, bool ROT, int CB, int STAGES_, int WARPS_>
-__global__ void __launch_bounds__(WARPS_ * 32, CB == 32 ? 2 : 1)
+template <int R, bool GRAD, bool ROT, int CB, int STAGES_, int WARPS_, bool SOLO = false, int MINB = 1>
+__global__ void __launch_bounds__(WARPS_ * 32, MINB)
 stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_c,
                  const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_cos,
                  const __grid_constant__ CUtensorMap map_sin, const StatsTmaParams p) {
-  using Cfg = StatsTmaCfg<R, GRAD, ROT, CB, STAGES_, WARPS_>;
+  using Cfg = StatsTmaCfg<R, GRAD, ROT, CB, STAGES_, WARPS_, SOLO>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int kStWarps = WARPS_;
   constexpr int MT = R / 16, NG = Cfg::GCOLS / 8, NQ = CB / 8;
@@ -74,23 +75,32 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   unsigned char* smem_gen = smem_raw + (smem - smem_u32(smem_raw));
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int chunk = blockIdx.x, sys = blockIdx.y, dblk = blockIdx.z;
-  if (!GRAD && chunk == p.chunks) {
+  // SOLO: warp w of CTA x owns system x * WARPS + w and streams all its tokens (many short sequences);
+  // otherwise the CTA owns (system, token chunk) and its warps share the slices of the chunk
+  const int chunk = SOLO ? 0 : blockIdx.x, dblk = blockIdx.z;
+  const int sys_raw = SOLO ? (int)blockIdx.x * kStWarps + warp : (int)blockIdx.y;
+  const bool spare = SOLO ? (int)blockIdx.x >= p.work_ctas : (!GRAD && chunk == p.chunks);
+  if (spare) {
     grid_launch_dependents();
     grid_dependency_wait();
-    // spare column of the grid: the per-head core runs beside the token reduction
-    if (dblk == 0 && sys < p.heads)
-      core_forward_device<R, NT>(p.base_raw, p.eta_raw, sys, p.complement, p.eta, p.eta_slope, p.core_map,
+    // spare CTAs of the grid: the per-head core runs beside the token reduction
+    const int head = SOLO ? (int)blockIdx.x - p.work_ctas : sys_raw;
+    if (!GRAD && dblk == 0 && head < p.heads)
+      core_forward_device<R, NT>(p.base_raw, p.eta_raw, head, p.complement, p.eta, p.eta_slope, p.core_map,
                                  p.core_info, smem_gen, tid);
     return;
   }
+  const bool active = !SOLO || sys_raw < p.systems;
+  const int sys = active ? sys_raw : 0;
   const int b = sys / p.heads, h = sys - b * p.heads;
   const int d0 = dblk * CB;
   const int tok0 = chunk * p.chunk_tokens;
   const int tok1 = min(p.tokens, tok0 + p.chunk_tokens);
   const int slice0 = tok0 >> 4;
   const int nslices = (tok1 - tok0 + 15) >> 4;
-  const int n_items = nslices > warp ? (nslices - warp + kStWarps - 1) / kStWarps : 0;
+  const int first_slice = SOLO ? 0 : warp, slice_step = SOLO ? 1 : kStWarps;
+  const int n_items = SOLO ? (active ? nslices : 0)
+                           : (nslices > warp ? (nslices - warp + kStWarps - 1) / kStWarps : 0);
   const bool do_gram = !GRAD && dblk < Cfg::GP;
   const int gcol0 = dblk * Cfg::GCOLS;   // first Gram column of this CTA (when do_gram)
   const int tab_b = p.rotary_rows > 1 ? b : 0;
@@ -115,7 +125,7 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   // item k of this warp refills ring stage k % STAGES
   auto issue = [&](int k, int stage) {
-    const int row = (slice0 + warp + k * kStWarps) * 16;
+    const int row = (slice0 + first_slice + k * slice_step) * 16;
     const uint32_t st = ring + stage * Cfg::STAGE;
     const uint32_t bar = mybar + stage * 8;
     mbar_expect_tx(bar, TX);
@@ -259,6 +269,42 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
   if (!ok && lane == 0) atomicExch(p.error, kErrBarrierTimeout);
   grid_launch_dependents();
+  if (SOLO) {
+    // the warp holds the whole sum of its system: store the accumulator fragments as they are
+    if (!active) return;
+    const int g = lane >> 2, tq = lane & 3;
+    float* out = p.partials + (size_t)sys * p.partial_floats;
+    float* outq = out + (GRAD ? 0 : R * R) + d0;
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      const int r0 = m * 16 + g;
+      if (!GRAD && do_gram) {
+#pragma unroll
+        for (int n = 0; n < NG; ++n) {
+          const int col = gcol0 + n * 8 + 2 * tq;
+          *reinterpret_cast<float2*>(out + r0 * R + col) = make_float2(accG[m][n][0], accG[m][n][1]);
+          *reinterpret_cast<float2*>(out + (r0 + 8) * R + col) = make_float2(accG[m][n][2], accG[m][n][3]);
+        }
+      }
+#pragma unroll
+      for (int n = 0; n < NQ; ++n) {
+        const int col = n * 8 + 2 * tq;
+        *reinterpret_cast<float2*>(outq + r0 * p.head_dim + col) = make_float2(accQ[m][n][0], accQ[m][n][1]);
+        *reinterpret_cast<float2*>(outq + (r0 + 8) * p.head_dim + col) = make_float2(accQ[m][n][2], accQ[m][n][3]);
+      }
+    }
+    if (GRAD) {
+      float de_acc = (de_part[0] + de_part[1]) + (de_part[2] + de_part[3]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) de_acc += __shfl_xor_sync(0xffffffffu, de_acc, o);
+      if (lane == 0) {
+        float* de = p.de_partials + (size_t)sys * p.de_slots;
+        de[2 * dblk] = de_acc;
+        de[2 * dblk + 1] = 0.f;
+      }
+    }
+    return;
+  }
   __syncthreads();
 
   // ---- add the warp accumulators in warp order, write one partial ---------------------
@@ -302,7 +348,6 @@ stats_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
   if (GRAD) {
     __syncthreads();
-#pragma unroll
     float de_acc = (de_part[0] + de_part[1]) + (de_part[2] + de_part[3]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) de_acc += __shfl_xor_sync(0xffffffffu, de_acc, o);
@@ -332,6 +377,28 @@ static int launch_stats_tma_one(const ms_shape& s, const Plan& plan, const CUten
   dim3 grid(plan.chunks + (fuse_core ? 1 : 0), plan.systems, s.head_dim / CB);
   launch_kernel(kern, grid, dim3(WARPS * 32), Cfg::TOTAL, st, maps[0], maps[1], maps[2], maps[3], maps[4], p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
+}
+
+// Many short sequences (one chunk per system and at least one system per SM): four-warp CTAs, several per
+// SM, in which every warp reduces one whole system and writes its partial itself.
+constexpr int kSoloWarps = 4;
+
+template <int R, bool GRAD, bool ROT>
+static int launch_stats_tma_solo(const ms_shape& s, const Plan& plan, const CUtensorMap* maps, StatsTmaParams p,
+                                 bool fuse_core, cudaStream_t st) {
+  constexpr int MINB = GRAD ? 2 : 3;
+  using Cfg = StatsTmaCfg<R, GRAD, ROT, 64, 2, kSoloWarps, true>;
+  auto kern = stats_tma_kernel<R, GRAD, ROT, 64, 2, kSoloWarps, true, MINB>;
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Cfg::TOTAL)) return MS_ERR_LAUNCH;
+  p.systems = plan.systems;
+  p.work_ctas = (plan.systems + kSoloWarps - 1) / kSoloWarps;
+  dim3 grid(p.work_ctas + (fuse_core ? s.heads : 0), 1, s.head_dim / 64);
+  launch_kernel(kern, grid, dim3(kSoloWarps * 32), Cfg::TOTAL, st, maps[0], maps[1], maps[2], maps[3], maps[4], p);
+  return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
+}
+
+static bool solo_shape(const ms_shape& s, const Plan& plan) {
+  return plan.chunks == 1 && s.tokens <= 1024 && plan.systems >= sm_count();
 }
 
 template <int R, bool GRAD, int CB, int STAGES, int WARPS = 8>
@@ -369,6 +436,9 @@ static int launch_stats_tma_r(const ms_shape& s, const Plan& plan, const void* p
     if (encode_tensor_map(&maps[3], const_cast<float*>(cos), 4, 3, dims, str, box, Swizzle::None)) return MS_ERR_LAUNCH;
     if (encode_tensor_map(&maps[4], const_cast<float*>(sin), 4, 3, dims, str, box, Swizzle::None)) return MS_ERR_LAUNCH;
   }
+  if (CB == 64 && (GRAD || R <= 32) && solo_shape(s, plan))
+    return rot ? launch_stats_tma_solo<R, GRAD, true>(s, plan, maps, p, fuse_core, st)
+               : launch_stats_tma_solo<R, GRAD, false>(s, plan, maps, p, fuse_core, st);
   return rot ? launch_stats_tma_one<R, GRAD, true, CB, STAGES, WARPS>(s, plan, maps, p, fuse_core, st)
              : launch_stats_tma_one<R, GRAD, false, CB, STAGES, WARPS>(s, plan, maps, p, fuse_core, st);
 }
@@ -393,6 +463,7 @@ int launch_stats_tma(const ms_shape& s, const Plan& plan, bool grad, const void*
   p.core_map = fuse_core ? core_tape->core_map : nullptr;
   p.core_info = fuse_core ? core_tape->core_info : nullptr;
   p.complement = s.complement;
+  p.systems = plan.systems; p.work_ctas = 0;
   if (grad) {
     switch (s.rank) {
       case 16: return launch_stats_tma_r<16, true, 64, 2>(s, plan, projected, dy, cos, sin, p, false, st);

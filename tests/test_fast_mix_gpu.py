@@ -373,6 +373,20 @@ def test_tma_kernel_shapes(cuda_mod, batch, length, heads, rank, head_dim, rot):
     assert cuda_mod._LIB.ms_device_error() == 0
 
 
+@pytest.mark.parametrize("batch,length,heads,rank,head_dim,rot,masked", [
+    (40, 197, 4, 32, 64, True, False), (26, 128, 6, 32, 64, False, True), (80, 50, 2, 16, 128, True, True),
+    (50, 130, 3, 64, 64, False, False), (150, 7, 1, 32, 64, True, False)])
+def test_many_short_sequences(cuda_mod, batch, length, heads, rank, head_dim, rot, masked):
+    """At least one (sample, head) system per SM and one token chunk per system: the statistics kernels
+    switch to the variant in which every warp reduces one whole system (ragged and empty samples, two
+    channel blocks, rank 64 adjoint, fewer tokens than the rank)."""
+    case = _random_case(7000 + length, batch, length, heads, rank, head_dim, rot=rot, masked=masked,
+                        batched_table=rot and masked)
+    _assert_case(cuda_mod, *case, gproj=5e-3 if rot else 3e-2,
+                 tag=f"short B{batch} N{length} H{heads} r{rank} d{head_dim}")
+    assert cuda_mod._LIB.ms_device_error() == 0
+
+
 def test_rejects_bad_inputs(cuda_mod):
     proj, base, eta_raw, counts, cos, sin, dy = _random_case(1, 1, 40, 2, 16, 8)
     with pytest.raises(RuntimeError, match="mixed precision CUDA contract"):
