@@ -284,7 +284,10 @@ def time_kernels(layer, cfg, tokens, device, reps=10, warm=3, with_graph=True, b
             assert fn() == 0
         ts = []
         for _ in range(reps):
+            # flush L2: write 256 MB, then read it back so that no dirty lines are left to be written out
+            # while the timed kernel runs
             flush.zero_()
+            flush.view(torch.int64).sum()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             assert fn() == 0

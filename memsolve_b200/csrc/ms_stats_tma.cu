@@ -14,6 +14,8 @@
 // with TMA (one mbarrier per stage), the warp rotates the content in FP32, splits it into two
 // BF16 words and feeds mma.sync with the full r x (r + 64) accumulator held in registers.
 // At the end the warps' accumulators are added in warp order through shared memory.
+// SOLO variant (many short sequences, see solo_shape): four-warp CTAs, several per SM; warp w of CTA x
+// owns system 4 x + w, streams all its slices and stores its accumulator fragments as the partial.
 #include "ms_core.cuh"
 #include "ms_tma.cuh"
 
@@ -379,8 +381,8 @@ static int launch_stats_tma_one(const ms_shape& s, const Plan& plan, const CUten
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
 
-// Many short sequences (one chunk per system and at least one system per SM): four-warp CTAs, several per
-// SM, in which every warp reduces one whole system and writes its partial itself.
+// Many short sequences (one chunk per system, see solo_shape): four-warp CTAs, several per SM, in which
+// every warp reduces one whole system and writes its partial itself.
 constexpr int kSoloWarps = 4;
 
 template <int R, bool GRAD, bool ROT>
@@ -397,8 +399,11 @@ static int launch_stats_tma_solo(const ms_shape& s, const Plan& plan, const CUte
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
 
+// Worth it when the warps that stream (one per system) fill the machine: four systems per SM, or one
+// per SM when a system is so short that a twelve-warp CTA would mostly add up its warps' accumulators.
 static bool solo_shape(const ms_shape& s, const Plan& plan) {
-  return plan.chunks == 1 && s.tokens <= 1024 && plan.systems >= sm_count();
+  if (plan.chunks != 1 || s.tokens > 1024) return false;
+  return plan.systems >= 4 * sm_count() || (plan.systems >= sm_count() && s.tokens <= 256);
 }
 
 template <int R, bool GRAD, int CB, int STAGES, int WARPS = 8>
