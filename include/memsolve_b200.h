@@ -44,7 +44,7 @@ typedef enum ms_status {
   MS_OK = 0,
   MS_ERR_INVALID_ARGUMENT = 1, /* null pointer, non-positive size, bad rotary_rows ...          */
   MS_ERR_UNSUPPORTED_RANK = 2, /* rank not in {16, 32, 48, 64}                                  */
-  MS_ERR_WORKSPACE = 3,        /* workspace pointer null or smaller than ms_workspace_bytes()   */
+  MS_ERR_WORKSPACE = 3,        /* workspace null, not 16-byte aligned, or < ms_workspace_bytes() */
   MS_ERR_LAUNCH = 4,           /* a kernel launch reported a CUDA error                         */
   MS_ERR_DEVICE = 5,           /* current device is not sm_100-class                            */
   MS_ERR_ODD_HEAD_DIM = 6,     /* rotary tables given with an odd head dimension                */
@@ -110,7 +110,8 @@ int ms_padded_head_dim(int head_dim);
 int ms_device_error(void);
 
 /* Bytes of scratch the stats/compact calls need for this shape (partials of the token
- * reduction and backward intermediates).  Same workspace serves forward and backward. */
+ * reduction and backward intermediates).  Same workspace serves forward and backward; it must be
+ * 16-byte aligned. */
 size_t ms_workspace_bytes(const ms_shape* shape);
 
 /* Number of floats in the packed, reduced forward statistics (per rank):

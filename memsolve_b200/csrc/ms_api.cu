@@ -289,7 +289,7 @@ int ms_stats_forward(const ms_shape* shape, const void* projected, const float* 
   if (!projected) return MS_ERR_INVALID_ARGUMENT;
   if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
   Plan plan = make_plan(*shape);
-  if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+  if (!workspace || !is16(workspace) || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
   plan.aligned = plan.aligned && is16(projected) && (!shape->rotary_rows || (is16(cos) && is16(sin)));
   const Workspace w = carve(workspace, plan);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -348,7 +348,7 @@ int ms_compact_forward(const ms_shape* shape, const float* counts, const void* w
   const Plan plan = make_plan(*shape);
   const float* src = packed;
   if (!packed) {
-    if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+    if (!workspace || !is16(workspace) || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
     src = static_cast<const float*>(workspace);
   }
   return launch_compact_forward(*shape, plan, counts, src, packed != nullptr, *tape,
@@ -377,7 +377,7 @@ int ms_mix_forward(const ms_shape* shape, const void* projected, const float* ba
   if (!shape->complement && (!base_raw || !tape->core_map)) return MS_ERR_INVALID_ARGUMENT;
   if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
   Plan plan = make_plan(*shape);
-  if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+  if (!workspace || !is16(workspace) || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
   const bool tables16 = !shape->rotary_rows || (is16(cos) && is16(sin));
   const Workspace w = carve(workspace, plan);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -402,7 +402,7 @@ int ms_stats_backward(const ms_shape* shape, const void* projected, const void* 
   if (!projected || !dy) return MS_ERR_INVALID_ARGUMENT;
   if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
   Plan plan = make_plan(*shape);
-  if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+  if (!workspace || !is16(workspace) || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
   plan.aligned = plan.aligned && is16(projected) && is16(dy) && (!shape->rotary_rows || (is16(cos) && is16(sin)));
   const Workspace w = carve(workspace, plan);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -424,7 +424,7 @@ int ms_compact_backward(const ms_shape* shape, const float* counts, void* worksp
   const bool with_core = d_eta_raw != nullptr;
   if (with_core && !shape->complement && (!base_raw || !tape->core_map || !d_base_raw)) return MS_ERR_INVALID_ARGUMENT;
   const Plan plan = make_plan(*shape);
-  if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+  if (!workspace || !is16(workspace) || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
   const Workspace w = carve(workspace, plan);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   MS_TRY(launch_compact_backward(*shape, plan, counts, packed ? packed : w.partials, w.de_partials,
@@ -446,7 +446,7 @@ int ms_token_backward_core(const ms_shape* shape, const void* projected, const v
   if (!shape->complement && (!base_raw || !tape->core_map || !d_base_raw)) return MS_ERR_INVALID_ARGUMENT;
   if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
   Plan plan = make_plan(*shape);
-  if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+  if (!workspace || !is16(workspace) || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
   const Workspace w = carve(workspace, plan);
   plan.aligned = plan.aligned && is16(projected) && is16(dy) && is16(dprojected);
   CoreAdjoint core{base_raw, w.hmat, w.de_sys, d_base_raw, d_eta_raw, grad_scale};
@@ -465,7 +465,7 @@ int ms_stats_forward_core(const ms_shape* shape, const void* projected, const fl
   if (!shape->complement && (!base_raw || !tape->core_map)) return MS_ERR_INVALID_ARGUMENT;
   if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
   Plan plan = make_plan(*shape);
-  if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+  if (!workspace || !is16(workspace) || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
   plan.aligned = plan.aligned && is16(projected) && (!shape->rotary_rows || (is16(cos) && is16(sin)));
   const Workspace w = carve(workspace, plan);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -492,7 +492,7 @@ int ms_stats_exchange(const ms_shape* shape, int backward, const void* workspace
   MS_TRY(device_status());
   if (!packed || !areas) return MS_ERR_INVALID_ARGUMENT;
   const Plan plan = make_plan(*shape);
-  if (!workspace || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
+  if (!workspace || !is16(workspace) || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
   // the layout of an area follows from its size: the largest capacity (a multiple of four values)
   // whose area fits; every rank must pass the same size
   const size_t fixed = exchange_area_bytes(0);

@@ -275,13 +275,43 @@ __device__ __forceinline__ void core_backward_device(const float* __restrict__ b
   double* red = lc + r * p;                      // 64 doubles
 
   // dF = sum over the batch in fixed order; trace; <dY, C>
+  // (four consecutive entries per thread; eight samples in flight, their sums combined in a fixed tree, so
+  // that a large batch costs batch / 8 round trips to L2 instead of batch)
   double tr = 0.0;
+  for (int q = tid; q < (r * r) / 4; q += nthreads) {
+    const float4* src = reinterpret_cast<const float4*>(hmat + (size_t)h * r * r) + q;
+    const size_t step = (size_t)heads * r * r / 4;
+    float4 part[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) part[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    int b = 0;
+    for (; b + 8 <= batch; b += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = src[(size_t)(b + u) * step];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        part[u].x += v[u].x; part[u].y += v[u].y; part[u].z += v[u].z; part[u].w += v[u].w;
+      }
+    }
+    for (; b < batch; ++b) {
+      const float4 v = src[(size_t)b * step];
+      part[0].x += v.x; part[0].y += v.y; part[0].z += v.z; part[0].w += v.w;
+    }
+    float sum4[4];
+    sum4[0] = ((part[0].x + part[1].x) + (part[2].x + part[3].x)) + ((part[4].x + part[5].x) + (part[6].x + part[7].x));
+    sum4[1] = ((part[0].y + part[1].y) + (part[2].y + part[3].y)) + ((part[4].y + part[5].y) + (part[6].y + part[7].y));
+    sum4[2] = ((part[0].z + part[1].z) + (part[2].z + part[3].z)) + ((part[4].z + part[5].z) + (part[6].z + part[7].z));
+    sum4[3] = ((part[0].w + part[1].w) + (part[2].w + part[3].w)) + ((part[4].w + part[5].w) + (part[6].w + part[7].w));
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = 4 * q + e, row = i / r, col = i - row * r;
+      dfm[row * p + col] = (double)sum4[e];
+      if (row == col) tr += (double)sum4[e];
+    }
+  }
   for (int i = tid; i < r * r; i += nthreads) {
     const int row = i / r, col = i - row * r;
-    float acc = 0.f;
-    for (int b = 0; b < batch; ++b) acc += hmat[((size_t)b * heads + h) * r * r + i];
-    dfm[row * p + col] = (double)acc;
-    if (row == col) tr += (double)acc;
     if (!complement) {
       pm[row * p + col] = (double)core_map[(size_t)h * r * r + i] + (row == col ? 1.0 : 0.0);
       double v = 0.0;
