@@ -73,17 +73,6 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     mbar_fence_init();
   }
   __syncthreads();
-  grid_dependency_wait();
-  if (tid == 0) {
-    mbar_expect_tx(wbar, (uint32_t)(mats * 2 * Cfg::W_BYTES));
-    for (int m = 0; m < mats; ++m) {
-      const int hl = m / p.dblocks, jb = m - hl * p.dblocks;
-      const int row = ((b * p.heads + h0 + hl) * 2) * R;
-      tma_load_2d(w_base + (m * 2) * Cfg::W_BYTES, &map_w, jb * 64, row, wbar);
-      tma_load_2d(w_base + (m * 2 + 1) * Cfg::W_BYTES, &map_w, jb * 64, row + R, wbar);
-    }
-  }
-
   // contiguous item range of this warp; item = (slice, head-in-group, block)
   const int total = p.slices * mats;
   const int nwarps = gridDim.x * kRtWarps;
@@ -132,6 +121,19 @@ readout_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   for (int k = 0; k < PRE && k < n_items; ++k) {
     if (lane == 0) issue(ahead);
     advance(ahead);
+  }
+  // The token boxes above were requested before this point on purpose: `projected` and the counts were complete before the
+  // kernel ahead of the previous one started, so a chained launch may fetch them while the previous kernel
+  // (which produces the coefficient matrices) is still draining.
+  grid_dependency_wait();
+  if (tid == 0) {
+    mbar_expect_tx(wbar, (uint32_t)(mats * 2 * Cfg::W_BYTES));
+    for (int m = 0; m < mats; ++m) {
+      const int hl = m / p.dblocks, jb = m - hl * p.dblocks;
+      const int row = ((b * p.heads + h0 + hl) * 2) * R;
+      tma_load_2d(w_base + (m * 2) * Cfg::W_BYTES, &map_w, jb * 64, row, wbar);
+      tma_load_2d(w_base + (m * 2 + 1) * Cfg::W_BYTES, &map_w, jb * 64, row + R, wbar);
+    }
   }
   bool ok = mbar_wait(wbar, 0);
   ok = __all_sync(0xffffffffu, ok);

@@ -137,21 +137,6 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     mbar_fence_init();
   }
   __syncthreads();
-  grid_dependency_wait();
-  if (tid == 0) {
-    mbar_expect_tx(rbar, (uint32_t)(gh * Cfg::HEAD_BYTES));
-    for (int hl = 0; hl < gh; ++hl) {
-      const int sys = b * p.heads + h0 + hl;
-      const uint32_t hb = res_base + hl * Cfg::HEAD_BYTES;
-      tma_load_2d(hb, &map_w, 0, (sys * 2) * R, rbar);
-      tma_load_2d(hb + Cfg::W_BYTES, &map_w, 0, (sys * 2 + 1) * R, rbar);
-      tma_load_2d(hb + 2 * Cfg::W_BYTES, &map_q, 0, (sys * 2) * R, rbar);
-      tma_load_2d(hb + 3 * Cfg::W_BYTES, &map_q, 0, (sys * 2 + 1) * R, rbar);
-      tma_load_2d(hb + 4 * Cfg::W_BYTES, &map_s, 0, (sys * 2) * R, rbar);
-      tma_load_2d(hb + 4 * Cfg::W_BYTES + Cfg::S_BYTES, &map_s, 0, (sys * 2 + 1) * R, rbar);
-    }
-  }
-
   const int total = p.slices * gh;
   const int nwarps = p.work_ctas * WARPS;
   const int per = (total + nwarps - 1) / nwarps;
@@ -196,6 +181,23 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   for (int k = 0; k < PRE && k < n_items; ++k) {
     if (lane == 0) issue(ahead);
     advance(ahead);
+  }
+  // The token boxes above were requested before this point on purpose: `projected`, the gradient and the counts were
+  // complete before the kernel ahead of the previous one started, so a chained launch may fetch them while
+  // the previous kernel (which produces the resident matrices) is still draining.
+  grid_dependency_wait();
+  if (tid == 0) {
+    mbar_expect_tx(rbar, (uint32_t)(gh * Cfg::HEAD_BYTES));
+    for (int hl = 0; hl < gh; ++hl) {
+      const int sys = b * p.heads + h0 + hl;
+      const uint32_t hb = res_base + hl * Cfg::HEAD_BYTES;
+      tma_load_2d(hb, &map_w, 0, (sys * 2) * R, rbar);
+      tma_load_2d(hb + Cfg::W_BYTES, &map_w, 0, (sys * 2 + 1) * R, rbar);
+      tma_load_2d(hb + 2 * Cfg::W_BYTES, &map_q, 0, (sys * 2) * R, rbar);
+      tma_load_2d(hb + 3 * Cfg::W_BYTES, &map_q, 0, (sys * 2 + 1) * R, rbar);
+      tma_load_2d(hb + 4 * Cfg::W_BYTES, &map_s, 0, (sys * 2) * R, rbar);
+      tma_load_2d(hb + 4 * Cfg::W_BYTES + Cfg::S_BYTES, &map_s, 0, (sys * 2 + 1) * R, rbar);
+    }
   }
   bool ok = mbar_wait(rbar, 0);
   ok = __all_sync(0xffffffffu, ok);
