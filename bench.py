@@ -339,9 +339,8 @@ def run_ours(args, cfg):
         counts = sp.valid_counts(None, batch_size=1, device=device)
         sp.overlap_gradient_sum(layer)   # parameter-gradient SUMs overlap the rest of the backward pass
         # statistics and large gradients summed by kernels over NVLink peer memory (verified against the NCCL
-        # path on 2 and 4 GPUs; MEMSOLVE_BENCH_PEER_EXCHANGE=1 / 0 forces it on / off for any number of GPUs)
-        choice = os.environ.get("MEMSOLVE_BENCH_PEER_EXCHANGE", "")
-        if choice == "1" or (choice != "0" and world in (2, 4)):
+        # path on 2, 4 and 8 GPUs); MEMSOLVE_BENCH_PEER_EXCHANGE=0 selects NCCL for both instead
+        if os.environ.get("MEMSOLVE_BENCH_PEER_EXCHANGE", "") != "0":
             sp.use_peer_exchange()
 
     def step(xin, grad_out):

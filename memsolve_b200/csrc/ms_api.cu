@@ -167,8 +167,8 @@ Plan make_plan(const ms_shape& s) {
     const char* v = std::getenv("MEMSOLVE_NO_TMA");
     return v && v[0] == '1';
   }();
-  // the TMA statistics kernels (rank 16/32, head dimension a multiple of 64) run one 8-warp CTA
-  // per SM; the generic kernels two 4-warp CTAs
+  // the TMA statistics kernels (rank 16/32, head dimension a multiple of 64) run one CTA of eight
+  // to twelve warps per SM; the generic kernels two 4-warp CTAs
   const bool wide_ctas = !no_tma_env && (s.head_dim % 64) == 0 && (s.rank == 16 || s.rank == 32);
   p.de_slots = 2 * p.dblocks;
   const long want = (wide_ctas ? 1L : 2L) * sm_count();
