@@ -44,6 +44,7 @@ struct TokenBwdTmaParams {
   const float* eta;
   int* error;
   int tokens, heads, rotary_rows, group_heads, slices, work_ctas, batch;
+  int core_ctas;   // spare CTAs of the grid; spare CTA c takes the heads c, c + core_ctas, ...
   // per-head core adjoint (spare CTAs); d_eta_raw == nullptr disables it
   const float* base_raw;
   const float* hmat;
@@ -116,10 +117,14 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 
   if ((int)blockIdx.x >= p.work_ctas) {
     grid_dependency_wait();
-    if (blockIdx.y == 0 && blockIdx.z == 0)
-      core_backward_device(p.base_raw, p.hmat, p.de_sys, p.eta_slope, p.core_map, R, blockIdx.x - p.work_ctas,
-                           p.heads, p.batch, p.complement, p.grad_scale, p.d_base, p.d_eta_raw,
-                           smem_raw + (smem - smem_u32(smem_raw)), tid, WARPS * 32);
+    if (blockIdx.y == 0 && blockIdx.z == 0) {
+      for (int head = (int)blockIdx.x - p.work_ctas; head < p.heads; head += p.core_ctas) {
+        core_backward_device(p.base_raw, p.hmat, p.de_sys, p.eta_slope, p.core_map, R, head, p.heads, p.batch,
+                             p.complement, p.grad_scale, p.d_base, p.d_eta_raw,
+                             smem_raw + (smem - smem_u32(smem_raw)), tid, WARPS * 32);
+        __syncthreads();
+      }
+    }
     return;
   }
 
@@ -390,12 +395,16 @@ static int launch_token_bwd_tma_cfg(const ms_shape& s, const Plan& plan, const v
   const long total = (long)p.slices * group;
   // one CTA per SM: leave SMs for the per-head CTAs that ride along, so that the whole grid is
   // resident at once (a CTA that has to wait for a free SM would run after all the others)
-  long ctas = (sm_count() - (core ? heads : 0)) / ((long)s.batch * groups);
+  // With few samples the adjoint of one head takes a small part of the launch: one spare CTA then takes two
+  // heads, which frees SMs for the token pass (at 32768 tokens and 12 heads: 15 instead of 16 items per warp).
+  const int core_ctas = core ? (s.batch <= 4 ? (heads + 1) / 2 : heads) : 0;
+  long ctas = (sm_count() - core_ctas) / ((long)s.batch * groups);
   if (ctas < 1) ctas = 1;
   const long need = (total + kTbWarps * 6 - 1) / (kTbWarps * 6);
   if (ctas > need) ctas = need < 1 ? 1 : need;
   p.work_ctas = (int)ctas;
-  dim3 grid((unsigned)ctas + (core ? heads : 0), s.batch, groups);
+  p.core_ctas = core_ctas > 0 ? core_ctas : 1;
+  dim3 grid((unsigned)ctas + core_ctas, s.batch, groups);
   int smem_bytes = 1024 + group * Cfg::HEAD_BYTES + Cfg::RING + Cfg::BAR_BYTES;
   const int core_bytes = (int)core_backward_smem_bytes(R) + 1024;
   if (core && smem_bytes < core_bytes) smem_bytes = core_bytes;
