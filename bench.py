@@ -156,6 +156,11 @@ def run_reference(args, cfg):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # all the host threads this process may use (torchrun presets OMP_NUM_THREADS=1 for its workers)
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, RuntimeError):
+        pass
     full = cfg.get("local_tokens", cfg.get("global_tokens"))
     # bounded sample: pick the largest token count whose (steps+warmup) run stays near two minutes
     probe = time_cpu(cfg, 2048, 1, 1)
