@@ -577,8 +577,11 @@ def run_scaffold(args):
         targets = torch.where(chosen, ids, torch.full_like(ids, -100)).to(device)
         ids = torch.where(chosen, torch.full_like(ids, 103), ids).to(device)
 
+        positions = (targets.reshape(-1) != -100).nonzero().squeeze(1)
+        wanted = targets.reshape(-1)[positions]
+
         def loss_fn():
-            return model(ids, labels=targets)
+            return model.masked_lm_loss(ids, positions, wanted)
         units, unit = spec["batch"] * spec["tokens"], "tokens/s"
 
     def step():
@@ -632,6 +635,28 @@ def run_scaffold(args):
     for _ in range(3):
         graph.replay()
     layer_dt = timed(graph.replay, 50)
+
+    # the same step as one CUDA graph (static shapes; gradients are written into the same tensors each replay)
+    graph_dt = None
+    del loss   # no autograd graph of an eager step may be alive while the step is captured
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        step_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(step_graph):
+            step()
+        for _ in range(3):
+            step_graph.replay()
+        graph_dt = timed(step_graph.replay, args.steps)
+    except Exception as error:   # capture is an extra; the eager figure above stands on its own
+        print(f"graph capture of the scaffold step failed: {error}", file=sys.stderr)
+        torch.cuda.synchronize()
+
     width = spec["heads"] * spec["rank"] + spec["dim"]
     n_tok = spec["batch"] * spec["tokens"]
     hbm, _tc, which = _peaks()
@@ -643,6 +668,8 @@ def run_scaffold(args):
                                f"dim {spec['dim']}, {spec['heads']} heads, rank {spec['rank']}, batch {spec['batch']}"
                                f" x {spec['tokens']} tokens", "parallelism": "sp1"},
         "clocks": clocks, "gpu_launches": 6 * spec["depth"] * args.steps,
+        "graph_replay": None if graph_dt is None else {"ms_per_step": graph_dt * 1e3, "value": units / graph_dt,
+                                                         "unit": unit},
         "layer_alone": {"us": round(layer_dt * 1e6, 1), "tokens_per_s": n_tok / layer_dt,
                         "systems": spec["batch"] * spec["heads"],
                         "frac_of_layer_hbm_bound": 2 * (5 * width + 3 * spec["dim"] + 8 * spec["dim"] + 2 * width)

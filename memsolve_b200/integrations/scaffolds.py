@@ -167,7 +167,15 @@ class TextScaffold(nn.Module):
         if labels is None:
             hidden = self.head_norm(F.gelu(self.head_dense(x)))
             return F.linear(hidden, self.word.weight, self.decoder_bias)
-        chosen = labels.reshape(-1) != -100
-        hidden = self.head_norm(F.gelu(self.head_dense(x.reshape(-1, x.shape[-1])[chosen])))
+        positions = (labels.reshape(-1) != -100).nonzero().squeeze(1)
+        return self._loss_at(x, positions, labels.reshape(-1)[positions])
+
+    def _loss_at(self, x, positions, targets):
+        hidden = self.head_norm(F.gelu(self.head_dense(x.reshape(-1, x.shape[-1])[positions])))
         logits = F.linear(hidden, self.word.weight, self.decoder_bias)
-        return F.cross_entropy(logits.float(), labels.reshape(-1)[chosen])
+        return F.cross_entropy(logits.float(), targets)
+
+    def masked_lm_loss(self, input_ids, positions, targets, attention_mask=None, token_type_ids=None):
+        """The same loss with the target positions given as flat indices into `[batch * length]` (a tensor
+        of fixed size: no host synchronisation, so the step can be captured in a CUDA graph)."""
+        return self._loss_at(self.encode(input_ids, attention_mask, token_type_ids), positions, targets)
