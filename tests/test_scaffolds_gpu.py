@@ -103,5 +103,10 @@ def test_text_scaffold_padding_and_training_step(scaffolds):
     assert torch.isfinite(loss)
     missing = [n for n, p in model.named_parameters() if p.grad is None or not torch.isfinite(p.grad).all()]
     assert not missing
+    # the same loss with the target positions given as indices (the form a CUDA graph can capture)
+    positions = (labels.reshape(-1) != -100).nonzero().squeeze(1)
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        again = model.masked_lm_loss(ids, positions, labels.reshape(-1)[positions], attention)
+    assert torch.equal(again, loss.detach())
     with pytest.raises(ValueError, match="2D padding mask"):
         model.encode(ids, attention[:, None, :])
