@@ -181,6 +181,15 @@ Plan make_plan(const ms_shape& s) {
   const int tiles_per_chunk = (int)((tiles + chunks - 1) / chunks);
   p.chunk_tokens = tiles_per_chunk * kTileTokens;
   p.chunks = (s.tokens + p.chunk_tokens - 1) / p.chunk_tokens;
+  {
+    // adjoint reduction: every SM streams (no CTAs for the per-head core in that grid)
+    long cb = want / per;
+    if (cb < 1) cb = 1;
+    if (cb > tiles) cb = tiles;
+    const int per_chunk = (int)((tiles + cb - 1) / cb);
+    p.chunk_tokens_bwd = per_chunk * kTileTokens;
+    p.chunks_bwd = (s.tokens + p.chunk_tokens_bwd - 1) / p.chunk_tokens_bwd;
+  }
   p.aligned = (s.head_dim % 8) == 0;
   static const bool no_tma = [] {
     const char* v = std::getenv("MEMSOLVE_NO_TMA");
@@ -189,8 +198,11 @@ Plan make_plan(const ms_shape& s) {
   p.tma = !no_tma;
   p.fwd_partial_floats = (size_t)s.rank * s.rank + (size_t)s.rank * s.head_dim;
   p.bwd_partial_floats = (size_t)s.rank * s.head_dim;
-  p.ws_partials = round64((size_t)p.systems * p.chunks * p.fwd_partial_floats);
-  p.ws_de = round64((size_t)p.systems * p.chunks * p.de_slots);
+  {
+    const size_t fwd = (size_t)p.chunks * p.fwd_partial_floats, bwd = (size_t)p.chunks_bwd * p.bwd_partial_floats;
+    p.ws_partials = round64((size_t)p.systems * (fwd > bwd ? fwd : bwd));
+    p.ws_de = round64((size_t)p.systems * (p.chunks_bwd > p.chunks ? p.chunks_bwd : p.chunks) * p.de_slots);
+  }
   p.ws_hmat = round64((size_t)p.systems * s.rank * s.rank);
   p.ws_de_sys = round64((size_t)p.systems);
   p.ws_total_bytes = (p.ws_partials + p.ws_de + p.ws_hmat + p.ws_de_sys) * sizeof(float);
@@ -401,7 +413,7 @@ int ms_stats_backward(const ms_shape* shape, const void* projected, const void* 
   MS_TRY(device_status());
   if (!projected || !dy) return MS_ERR_INVALID_ARGUMENT;
   if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
-  Plan plan = make_plan(*shape);
+  Plan plan = backward_plan(make_plan(*shape));
   if (!workspace || !is16(workspace) || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
   plan.aligned = plan.aligned && is16(projected) && is16(dy) && (!shape->rotary_rows || (is16(cos) && is16(sin)));
   const Workspace w = carve(workspace, plan);
@@ -423,7 +435,7 @@ int ms_compact_backward(const ms_shape* shape, const float* counts, void* worksp
   if (!gram_grad || !cross_grad) return MS_ERR_INVALID_ARGUMENT;
   const bool with_core = d_eta_raw != nullptr;
   if (with_core && !shape->complement && (!base_raw || !tape->core_map || !d_base_raw)) return MS_ERR_INVALID_ARGUMENT;
-  const Plan plan = make_plan(*shape);
+  const Plan plan = backward_plan(make_plan(*shape));
   if (!workspace || !is16(workspace) || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
   const Workspace w = carve(workspace, plan);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -491,7 +503,7 @@ int ms_stats_exchange(const ms_shape* shape, int backward, const void* workspace
   MS_TRY(check_shape(shape));
   MS_TRY(device_status());
   if (!packed || !areas) return MS_ERR_INVALID_ARGUMENT;
-  const Plan plan = make_plan(*shape);
+  const Plan plan = backward != 0 ? backward_plan(make_plan(*shape)) : make_plan(*shape);
   if (!workspace || !is16(workspace) || workspace_bytes < plan.ws_total_bytes) return MS_ERR_WORKSPACE;
   // the layout of an area follows from its size: the largest capacity (a multiple of four values)
   // whose area fits; every rank must pass the same size
@@ -534,7 +546,7 @@ int ms_mix_backward(const ms_shape* shape, const void* projected, const void* dy
   if (!tape || !tape->eta || !tape->eta_slope || !tape->inverse || !tape->state) return MS_ERR_INVALID_ARGUMENT;
   if (!gram_grad || !cross_grad || !d_eta_raw) return MS_ERR_INVALID_ARGUMENT;
   if (!shape->complement && (!base_raw || !tape->core_map || !d_base_raw)) return MS_ERR_INVALID_ARGUMENT;
-  const Plan plan = make_plan(*shape);
+  const Plan plan = backward_plan(make_plan(*shape));
   const Workspace w = carve(workspace, plan);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ChainScope chain(chaining_allowed());

@@ -52,6 +52,8 @@ struct Plan {
   int dpad;          // d rounded up to a multiple of 8 (pitch of split coefficient tensors)
   int chunks;        // token chunks per system in the reductions
   int chunk_tokens;  // tokens per chunk (multiple of 64)
+  int chunks_bwd;        // the same for the adjoint reduction, whose grid has no per-head CTAs riding along
+  int chunk_tokens_bwd;  // (see backward_plan)
   bool aligned;      // 16-byte vector path usable for projected / dy / tables
   bool tma;          // TMA kernels allowed (off when the environment sets MEMSOLVE_NO_TMA=1)
   size_t fwd_partial_floats;  // per (system, chunk): r*r + r*d
@@ -114,6 +116,13 @@ inline void launch_kernel(void (*kernel)(Expected...), dim3 grid, dim3 block, si
 }
 
 Plan make_plan(const ms_shape& s);
+// the plan with the chunking of the adjoint reduction in `chunks` / `chunk_tokens`: what the adjoint
+// statistics, their pack / exchange and the compact backward take
+inline Plan backward_plan(Plan p) {
+  p.chunks = p.chunks_bwd;
+  p.chunk_tokens = p.chunk_tokens_bwd;
+  return p;
+}
 int check_shape(const ms_shape* s);
 int sm_count();
 int ensure_dynamic_smem(const void* kernel, int bytes);
