@@ -105,9 +105,18 @@ int ms_padded_head_dim(int head_dim);
 
 /* Diagnostic (synchronises the device): reads and clears the library's device-side error word of
  * the current device.  0 = no error; 0x100 = a kernel gave up waiting on a shared-memory barrier
- * (its bounded wait ran out) and returned early, so the last results are incomplete; -1 = the
- * word could not be read.  No counterpart in the reference, whose kernels have no such waits. */
+ * (its bounded wait ran out) and returned early, so the last results are incomplete; 0x200 = a
+ * peer-memory exchange (ms_stats_exchange, ms_peer_sum) gave up waiting for another rank and wrote
+ * NaN in place of the sums it could not form; -1 = the word could not be read.  No counterpart in
+ * the reference, whose kernels have no such waits. */
 int ms_device_error(void);
+
+/* Longest time a peer-memory exchange kernel waits for another rank before it gives up (error word
+ * 0x200, NaN results).  Default 20000 ms, or the value of the environment variable
+ * MEMSOLVE_PEER_WAIT_MS read at the first exchange; applies to launches made after the call.  The
+ * NCCL all-reduce this path replaces (integrations/distributed.py:47-50 of the reference) waits
+ * without a limit; a kernel that spins forever would hang the GPU for every other user of it. */
+int ms_set_peer_wait_ms(int milliseconds);
 
 /* Bytes of scratch the stats/compact calls need for this shape (partials of the token
  * reduction and backward intermediates).  Same workspace serves forward and backward; it must be
@@ -257,8 +266,9 @@ int ms_mix_backward(const ms_shape* shape, const void* projected, const void* dy
  * (peer-accessible memory of `area_bytes` bytes, e.g. one symmetric-memory allocation per rank;
  * same size on all ranks; >= ms_exchange_area_bytes(shape); 16-byte aligned).  The areas must be
  * zero before the first call and must only be touched by this function afterwards; every rank
- * has to make the same sequence of calls.  A peer that does not arrive within a few seconds sets
- * the device error word (ms_device_error) instead of hanging the GPU.  Only plain peer loads and
+ * has to make the same sequence of calls.  A peer that does not arrive within the limit of
+ * ms_set_peer_wait_ms sets the device error word (ms_device_error) and turns the affected sums into
+ * NaN instead of hanging the GPU.  Only plain peer loads and
  * stores are used.
  */
 size_t ms_exchange_area_bytes(const ms_shape* shape);

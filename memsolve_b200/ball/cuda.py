@@ -58,6 +58,7 @@ _SIGNATURES = {
     "ms_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "ms_padded_head_dim": (ctypes.c_int, [ctypes.c_int]),
     "ms_device_error": (ctypes.c_int, []),
+    "ms_set_peer_wait_ms": (ctypes.c_int, [ctypes.c_int]),
     "ms_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(_Shape)]),
     "ms_packed_stats_floats": (ctypes.c_size_t, [ctypes.POINTER(_Shape), ctypes.c_int]),
     "ms_core_forward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, ctypes.POINTER(_Tape), _P]),

@@ -115,6 +115,21 @@ int encode_tensor_map(CUtensorMap* out, void* base, int elem_bytes, int rank, co
   return r == CUDA_SUCCESS ? MS_OK : MS_ERR_LAUNCH;
 }
 
+// Longest time, in nanoseconds, a peer-memory exchange kernel waits for another rank.
+static std::atomic<long long> g_peer_wait_ms{-1};
+unsigned long long peer_wait_ns() {
+  long long ms = g_peer_wait_ms.load(std::memory_order_relaxed);
+  if (ms < 0) {
+    ms = 20000;
+    if (const char* v = std::getenv("MEMSOLVE_PEER_WAIT_MS")) {
+      const long long parsed = std::atoll(v);
+      if (parsed > 0) ms = parsed;
+    }
+    g_peer_wait_ms.store(ms, std::memory_order_relaxed);
+  }
+  return (unsigned long long)ms * 1000000ull;
+}
+
 __device__ int g_error_word = 0;
 
 int* device_error_word() {
@@ -271,6 +286,12 @@ int ms_device_error(void) {
   if (cudaMemcpy(&value, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
   if (value != 0) cudaMemset(word, 0, sizeof(int));
   return value;
+}
+
+int ms_set_peer_wait_ms(int milliseconds) {
+  if (milliseconds <= 0) return MS_ERR_INVALID_ARGUMENT;
+  g_peer_wait_ms.store(milliseconds, std::memory_order_relaxed);
+  return MS_OK;
 }
 
 size_t ms_workspace_bytes(const ms_shape* shape) {

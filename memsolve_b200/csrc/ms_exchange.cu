@@ -17,8 +17,10 @@
 // Thread block c owns slice c of the value vector on every rank, so blocks of one GPU never wait
 // for each other: block c publishes its slice, raises flags[me][c] on every peer (after a
 // system-wide fence), waits until its own flags[r][c] have reached this call's number for every
-// peer r (bounded polling; a timeout sets the library's error word and the block goes on) and
-// then reads slice c of every peer with loads that bypass the caches.  Double buffering makes one
+// peer r and then reads slice c of every peer with loads that bypass the caches.  The wait is bounded
+// by wall-clock time (peer_wait_ns(), 20 s unless ms_set_peer_wait_ms or MEMSOLVE_PEER_WAIT_MS says
+// otherwise): a block whose peer has not arrived by then sets the library's error word to 0x200 and
+// writes NaN instead of sums, so a late or dead rank can never turn into plausible-looking numbers.  Double buffering makes one
 // barrier per call sufficient: a rank can only publish call k+2 into the buffer of call k after
 // all peers have raised their flags of call k+1, i.e. after their kernels of call k have ended.
 // All loads of peer memory are plain loads; no multicast object, no TMA.
@@ -29,10 +31,16 @@ namespace ms {
 constexpr int kExCtas = 32;          // thread blocks = slices of the value vector
 constexpr int kExThreads = 256;
 constexpr int kExMaxRanks = 8;
-constexpr int kExWaitLimit = 1 << 22;
 constexpr int kErrPeerTimeout = 0x200;
 
 int* device_error_word();
+unsigned long long peer_wait_ns();   // ms_api.cu: the limit set by ms_set_peer_wait_ms / MEMSOLVE_PEER_WAIT_MS
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 struct ExchangeParams {
   const float* partials;
@@ -41,6 +49,7 @@ struct ExchangeParams {
   float* out;
   float* areas[kExMaxRanks];
   int* error;
+  unsigned long long wait_ns;
   int world, rank, capacity;
   int heads, tokens, chunks, de_slots, gram_floats, pf, systems, grad, total;
 };
@@ -52,6 +61,18 @@ __device__ __forceinline__ unsigned ld_flag(const unsigned* p) {
 }
 __device__ __forceinline__ void st_flag(unsigned* p, unsigned v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Polls `flag` until it has reached `call`; false when `wait_ns` nanoseconds went by first.  The clock is
+// read once per 64 polls.
+__device__ __forceinline__ bool wait_flag(const unsigned* flag, unsigned call, unsigned long long wait_ns) {
+  if ((int)(ld_flag(flag) - call) >= 0) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if ((int)(ld_flag(flag) - call) >= 0) return true;
+    if (global_ns() - t0 > wait_ns) return false;
+  }
 }
 __device__ __forceinline__ float4 ld_peer4(const float* p) {
   float4 v;
@@ -131,17 +152,12 @@ __global__ void __launch_bounds__(kExThreads) exchange_kernel(const ExchangePara
   if (tid < p.world && tid != p.rank) {
     unsigned* theirs = reinterpret_cast<unsigned*>(p.areas[tid] + 2 * (size_t)p.capacity);
     st_flag(theirs + p.rank * kExCtas + c, call);
-    const unsigned* flag = my_flags + tid * kExCtas + c;
-    int polls = 0;
-    while ((int)(ld_flag(flag) - call) < 0) {
-      if (++polls > kExWaitLimit) {
-        s_ok = 0;
-        break;
-      }
-    }
+    if (!wait_flag(my_flags + tid * kExCtas + c, call, p.wait_ns)) s_ok = 0;
   }
   __syncthreads();
-  if (!s_ok && tid == 0) atomicExch(p.error, kErrPeerTimeout);
+  const bool arrived = s_ok != 0;
+  if (!arrived && tid == 0) atomicExch(p.error, kErrPeerTimeout);
+  const float poison = __int_as_float(0x7fc00000);
 
   // 3. add the slices of all ranks in rank order; all peer loads of a pass are in flight together
   for (int base = lo + tid; base < hi; base += kExThreads * kExVecs) {
@@ -169,6 +185,7 @@ __global__ void __launch_bounds__(kExThreads) exchange_kernel(const ExchangePara
             acc.x += vals[v][r].x; acc.y += vals[v][r].y; acc.z += vals[v][r].z; acc.w += vals[v][r].w;
           }
         }
+        if (!arrived) acc = make_float4(poison, poison, poison, poison);   // a peer never published this slice
         float* dst = p.out + 4 * (size_t)i4;
         if (4 * i4 + 3 < p.total) {
           *reinterpret_cast<float4*>(dst) = acc;
@@ -211,6 +228,7 @@ struct PeerSumParams {
   float* values;
   float* areas[kExMaxRanks];
   int* error;
+  unsigned long long wait_ns;
   int world, rank, capacity, total4;   // total4: vector length in units of four values
 };
 
@@ -222,14 +240,9 @@ __device__ __forceinline__ bool flag_round(const PeerSumParams& p, unsigned* my_
     unsigned* theirs = reinterpret_cast<unsigned*>(p.areas[tid] + 4 * (size_t)p.capacity) +
                        round * kExMaxRanks * kSumCtas;
     st_flag(theirs + p.rank * kSumCtas + c, call);
-    const unsigned* flag = my_flags + round * kExMaxRanks * kSumCtas + tid * kSumCtas + c;
-    int polls = 0;
-    while ((int)(ld_flag(flag) - call) < 0) {
-      if (++polls > kExWaitLimit) {
-        *s_ok = 0;
-        break;
-      }
-    }
+    // after a first timeout the later rounds do not wait again
+    if (*s_ok && !wait_flag(my_flags + round * kExMaxRanks * kSumCtas + tid * kSumCtas + c, call, p.wait_ns))
+      *s_ok = 0;
   }
   __syncthreads();
   return *s_ok != 0;
@@ -313,6 +326,17 @@ __global__ void __launch_bounds__(kExThreads) peer_sum_kernel(const PeerSumParam
     }
   }
 
+  if (!s_ok) {
+    // a peer did not arrive in time: this block's part of every slice becomes NaN instead of a partial sum
+    const float poison = __int_as_float(0x7fc00000);
+    for (int s = 0; s < p.world; ++s)
+      for (int j = plo + tid; j < phi; j += kExThreads) {
+        const int i4 = s * slice4 + j;
+        if (i4 < p.total4)
+          *reinterpret_cast<float4*>(p.values + 4 * (size_t)i4) = make_float4(poison, poison, poison, poison);
+      }
+  }
+
   __syncthreads();
   if (tid == 0) {
     __threadfence();
@@ -344,6 +368,7 @@ int launch_peer_sum(float* values, size_t count, void* const* areas, size_t area
   p.error = device_error_word();
   if (!p.error) return MS_ERR_LAUNCH;
   p.world = world; p.rank = rank; p.capacity = (int)capacity; p.total4 = (int)(count >> 2);
+  p.wait_ns = peer_wait_ns();
   if (count == 0) return MS_OK;
   peer_sum_kernel<<<kSumCtas, kExThreads, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
@@ -365,6 +390,7 @@ int launch_exchange(const ms_shape& s, const Plan& plan, bool grad, const float*
   p.error = device_error_word();
   if (!p.error) return MS_ERR_LAUNCH;
   p.world = world; p.rank = rank;
+  p.wait_ns = peer_wait_ns();
   p.heads = s.heads; p.tokens = s.tokens; p.chunks = plan.chunks; p.de_slots = plan.de_slots;
   p.gram_floats = grad ? 0 : s.rank * s.rank;
   p.pf = (int)(grad ? plan.bwd_partial_floats : plan.fwd_partial_floats);

@@ -20,6 +20,7 @@ NVLink on GPUs, gloo in CPU tests).
 from __future__ import annotations
 
 import itertools
+import os
 from typing import Iterable, Sequence
 
 import torch
@@ -99,16 +100,39 @@ class _PeerExchange:
         make it on every rank, outside CUDA-graph capture."""
         entry = self._areas.get(device.index)
         if entry is None or entry[3] < nbytes:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(
+                    "the peer-memory exchange areas must be allocated before CUDA-graph capture: run one eager "
+                    "step (or call SequenceParallel.prepare_peer_exchange) on every rank first")
+            if entry is not None:
+                torch.cuda.current_stream(device).synchronize()   # no kernel may still use the old area
             entry = self._areas[device.index] = self._allocate(max(nbytes, self.MINIMUM_BYTES), device)
         return entry[2], entry[3]
+
+    def prepare(self, statistics_bytes: int, largest_gradient_numel: int, device: torch.device) -> None:
+        """Allocate both kinds of areas once, outside capture (collective: call on every rank)."""
+        from ..ball import cuda as backend
+        self.areas(statistics_bytes, device)
+        if largest_gradient_numel >= self.SUM_MINIMUM_NUMEL and device.index not in self._sum_areas:
+            need = int(backend._LIB.ms_peer_sum_area_bytes(largest_gradient_numel))
+            self._sum_areas[device.index] = self._allocate(max(need, 16 << 20), device)
+            self._streams[device.index] = torch.cuda.Stream(device)
 
     # ---- in-place SUM of a gradient over the ranks, on a stream of its own
     SUM_MINIMUM_NUMEL = 1 << 18   # smaller gradients are latency-bound either way: leave them to NCCL
 
     def can_sum(self, tensor: torch.Tensor) -> bool:
-        return (tensor.is_cuda and tensor.dtype == torch.float32 and tensor.is_contiguous()
+        if not (tensor.is_cuda and tensor.dtype == torch.float32 and tensor.is_contiguous()
                 and tensor.numel() >= self.SUM_MINIMUM_NUMEL and tensor.numel() % 4 == 0
-                and tensor.data_ptr() % 16 == 0)
+                and tensor.data_ptr() % 16 == 0):
+            return False
+        entry = self._sum_areas.get(tensor.device.index)
+        if entry is None:
+            # the first SUM allocates (a collective host operation): not while a graph is being captured
+            return not torch.cuda.is_current_stream_capturing()
+        # an area is never replaced while work may be queued on it: what does not fit goes to NCCL
+        from ..ball import cuda as backend
+        return int(backend._LIB.ms_peer_sum_area_bytes(tensor.numel())) <= entry[3]
 
     def sum_async(self, tensor: torch.Tensor) -> "_StreamWork":
         """Launch the peer-memory SUM of `tensor` on the exchange's side stream, ordered after the
@@ -120,9 +144,11 @@ class _PeerExchange:
         lib = backend._LIB
         entry = self._sum_areas.get(device.index)
         need = int(lib.ms_peer_sum_area_bytes(tensor.numel()))
-        if entry is None or entry[3] < need:
+        if entry is None:
             entry = self._sum_areas[device.index] = self._allocate(max(need, 16 << 20), device)
             self._streams[device.index] = torch.cuda.Stream(device)
+        elif entry[3] < need:
+            raise RuntimeError("gradient larger than the peer-memory SUM area; can_sum() routes such tensors to NCCL")
         side = self._streams[device.index]
         side.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.stream(side):
@@ -147,7 +173,7 @@ class _StreamWork:
 class SequenceParallel:
     """Layout of one sharded sequence: the process group, every rank's shard length, this rank."""
 
-    __slots__ = ("group", "shard_lengths", "rank", "_starts", "_overlaps", "peer_exchange")
+    __slots__ = ("group", "shard_lengths", "rank", "_starts", "_overlaps", "peer_exchange", "check_device_errors")
 
     def __init__(self, group, shard_lengths: Iterable[int], rank: int):
         self.group = group
@@ -156,6 +182,9 @@ class SequenceParallel:
         self._starts = (0, *itertools.accumulate(self.shard_lengths))
         self._overlaps: dict[int, _GradientOverlap] = {}
         self.peer_exchange: _PeerExchange | None = None
+        # read the kernels' error word at the end of reduce_gradients_ (one device synchronisation per step):
+        # off unless asked for, because a peer that never arrives already turns the sums into NaN
+        self.check_device_errors = os.environ.get("MEMSOLVE_CHECK_DEVICE_ERRORS", "") == "1"
 
     def __repr__(self) -> str:
         return f"SequenceParallel(shard_lengths={self.shard_lengths}, rank={self.rank})"
@@ -254,6 +283,31 @@ class SequenceParallel:
             raise ValueError("the peer-memory exchange supports at most 8 ranks")
         self.peer_exchange = _PeerExchange(self) if enabled and self.world_size > 1 else None
 
+    def prepare_peer_exchange(self, module: torch.nn.Module, local_batch: int = 1) -> None:
+        """Allocate the exchange areas for `module` (a MemSolve layer or a model containing such layers) once,
+        before any CUDA-graph capture: the statistics areas from the largest layer shape, the gradient-SUM
+        areas from the largest trainable parameter.  Collective host operation: call on every rank."""
+        if self.peer_exchange is None:
+            return
+        import ctypes
+        from ..ball import cuda as backend
+        backend.require_available()
+        params = [p for p in module.parameters() if p.requires_grad and p.is_cuda]
+        if not params:
+            return
+        device = params[0].device
+        need = 0
+        for sub in module.modules():
+            cfg = getattr(sub, "config", None)
+            if cfg is None or not hasattr(cfg, "rank") or not hasattr(cfg, "num_heads"):
+                continue
+            shape = backend._Shape(local_batch, self.local_length, cfg.num_heads, cfg.rank,
+                                   cfg.dim // cfg.num_heads, 0, 0, 0)
+            need = max(need, int(backend._LIB.ms_exchange_area_bytes(ctypes.byref(shape))))
+        largest = max(p.numel() for p in params)
+        with torch.cuda.device(device):
+            self.peer_exchange.prepare(max(need, _PeerExchange.MINIMUM_BYTES), largest, device)
+
     # ---------------------------------------------------------------- parameter gradients
     def overlap_gradient_sum(self, module: torch.nn.Module) -> _GradientOverlap:
         """Start the SUM of each parameter gradient of `module` as soon as autograd has written it.
@@ -287,8 +341,25 @@ class SequenceParallel:
         overlap = self._overlaps.get(id(module))
         if overlap is not None and overlap._handles:
             overlap.finish(trainable)
+        else:
+            self._sum_in_place([p.grad for p in trainable])
+        if self.check_device_errors and self.peer_exchange is not None and trainable[0].is_cuda:
+            self.raise_on_device_error(trainable[0].device)
+
+    def raise_on_device_error(self, device) -> None:
+        """Synchronise `device` and raise if one of the library's kernels recorded an error since the last
+        check: 0x200 means a rank waited for a peer longer than the limit (`ms_set_peer_wait_ms`) and its
+        statistics or gradients of this step are NaN; 0x100 a shared-memory barrier timeout inside a kernel."""
+        from ..ball import cuda as backend
+        if torch.cuda.is_current_stream_capturing():
             return
-        self._sum_in_place([p.grad for p in trainable])
+        with torch.cuda.device(device):
+            word = int(backend._LIB.ms_device_error())
+        if word != 0:
+            raise RuntimeError(
+                f"MemSolve CUDA kernels reported device error {word:#x} on rank {self.rank}"
+                + (": a peer did not publish its statistics or gradients within the wait limit; this step's "
+                   "results are NaN" if word == 0x200 else ""))
 
     def _sum_in_place(self, tensors: Sequence[torch.Tensor]) -> None:
         """One coalesced collective over all tensors (no packing copies) where the backend offers

@@ -85,6 +85,44 @@ def test_layer_matches_reference_module(mods, name, recompute):
     assert rel_l2(y, g["y_f32"]) <= 2e-2
 
 
+def test_layer_config1_shape_matches_reference_module(mods):
+    """dim 384, 6 heads, rank 32, x [4, 196, 384] ~ N(0,1) from seed 0, default initialisation: the
+    reference module's own outputs on this input (FP32 path and FP64 evaluation, every fourth token kept in
+    the fixture) against the CUDA layer on the BF16-rounded input; <= 2e-2 (stated BF16 bound)."""
+    MemSolve, MemSolveConfig, _, _ = mods
+    g = load_golden("layer_config1.npz")
+    torch.manual_seed(0)
+    layer = MemSolve(MemSolveConfig(dim=384, num_heads=6, rank=32))
+    x = torch.randn(4, 196, 384)
+    same = (abs(float(x.double().sum()) - float(g["x_sum"])) < 1e-9
+            and abs(float(layer.w_bc.weight.double().abs().sum()) - float(g["w_bc_abs"])) < 1e-9
+            and abs(float(layer.w_o.weight.double().abs().sum()) - float(g["w_o_abs"])) < 1e-9)
+    if not same:
+        pytest.skip("seeded inputs differ from the ones the fixture was made with (different torch RNG)")
+    layer = layer.cuda()
+    xg = x.bfloat16().cuda().requires_grad_()
+    y = layer(xg, implementation="cuda")
+    dout = torch.randn(4, 196, 384, generator=torch.Generator().manual_seed(1)).bfloat16()
+    y.backward(dout.cuda())
+    torch.cuda.synchronize()
+    errs = {"vs_f64": rel_l2(y[:, ::4], g["y_f64_sub"]), "vs_f32": rel_l2(y[:, ::4], g["y_f32_sub"])}
+    # gradients: the FP64 oracle (pinned to the same fixture in the CPU tests) on the same rounded input
+    p = O.LayerParams(layer.w_bc.weight.detach().cpu(), layer.w_o.weight.detach().cpu(),
+                      layer.core_base_raw.detach().cpu(), layer.eta_raw.detach().cpu(), heads=6,
+                      rank=32).to(torch.float64)
+    for t in p.tensors():
+        t.requires_grad_()
+    xr = x.bfloat16().double().requires_grad_()
+    yr = O.layer_forward(p, xr)
+    yr.backward(dout.double())
+    errs.update({"y": rel_l2(y, yr), "dx": rel_l2(xg.grad, xr.grad),
+                 "dw_bc": rel_l2(layer.w_bc.weight.grad, p.w_bc.grad), "dw_o": rel_l2(layer.w_o.weight.grad, p.w_o.grad),
+                 "deta": rel_l2(layer.eta_raw.grad, p.eta_raw.grad)})
+    print("config-1 shape", {k: f"{v:.2e}" for k, v in errs.items()})
+    assert errs["vs_f64"] <= 2e-2 and errs["vs_f32"] <= 2e-2 and errs["y"] <= 2e-2, errs
+    assert all(errs[k] <= 3e-2 for k in ("dx", "dw_bc", "dw_o", "deta")), errs
+
+
 def test_recompute_policies_give_identical_results(mods):
     """Dropping and rebuilding the mixed readout leaves outputs and gradients bit-identical
     (tests/cuda/test_fast_path.py:2130-2202)."""

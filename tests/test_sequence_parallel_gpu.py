@@ -108,3 +108,89 @@ def test_sharded_layer_matches_unsharded(tmp_path):
     results = manager.dict()
     mp.spawn(_worker, args=(str(tmp_path / "nccl"), results), nprocs=2, join=True)
     assert dict(results) == {0: 1, 1: 1}
+
+
+def _peer_worker(rank, world, path, results):
+    """Peer-memory kernels against NCCL on `world` GPUs: the statistics exchange (through the layer, both
+    directions) and the in-place gradient SUM (`ms_peer_sum`: reduce-scatter + all-gather, two flag rounds)."""
+    sys.path.insert(0, ROOT)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from memsolve_b200 import MemSolve, MemSolveConfig
+    from memsolve_b200.ball import cuda
+    from memsolve_b200.integrations.distributed import SequenceParallel
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"file://{path}", rank=rank, world_size=world,
+                            timeout=timedelta(seconds=180), device_id=torch.device("cuda", rank))
+    try:
+        cuda.load()
+        lib = cuda._LIB
+        # --- gradient SUM: several calls in a row (both buffer parities), a length that is not a multiple of
+        # world * 16, values that differ per rank and call
+        sp = SequenceParallel.create(64)
+        sp.use_peer_exchange()
+        exchange = sp.peer_exchange
+        for call, numel in enumerate((1 << 18, (1 << 18) + 4 * 37, 768 * 1152, 1 << 18)):
+            torch.manual_seed(1000 * call + rank)
+            values = torch.randn(numel, device="cuda")
+            want = values.clone()
+            dist.all_reduce(want)
+            assert exchange.can_sum(values)
+            exchange.sum_async(values).wait()
+            torch.cuda.synchronize()
+            # the kernel adds in rank order on every rank; NCCL's order differs: compare to rounding
+            assert _rel(values, want) < 1e-6, (call, _rel(values, want))
+            gathered = [torch.empty_like(values) for _ in range(world)]
+            dist.all_gather(gathered, values)
+            assert all(torch.equal(gathered[0], g) for g in gathered)      # identical bits on all ranks
+        assert not exchange.can_sum(torch.randn(1 << 10, device="cuda"))   # small gradients stay on NCCL
+        assert lib.ms_device_error() == 0
+
+        # --- a layer whose weight gradients are large enough for the peer-memory SUM (dim 512): sharded step
+        # with the peer exchange against the same step with NCCL for statistics and gradients
+        local = 256 + 16 * rank
+        torch.manual_seed(77)
+        layer = MemSolve(MemSolveConfig(512, 8, rank=32, rotary=True)).cuda()
+        with torch.no_grad():
+            layer.core_base_raw.normal_(std=0.1)
+        twin = copy.deepcopy(layer)
+        total = sum(256 + 16 * r for r in range(world))
+        full = torch.randn(1, total, 512).bfloat16().cuda()
+        upstream = (torch.randn(1, total, 512) * 0.01).bfloat16().cuda()
+        outs = []
+        for module, peer in ((layer, True), (twin, False)):
+            sp = SequenceParallel.create(local)
+            sp.check_device_errors = True
+            sp.overlap_gradient_sum(module)
+            if peer:
+                sp.use_peer_exchange()
+                sp.prepare_peer_exchange(module)
+            sel = slice(sp.offset, sp.offset + local)
+            x = full[:, sel].clone().requires_grad_()
+            counts = sp.valid_counts(None, batch_size=1, device=x.device)
+            for _ in range(3):   # several steps: both parities of the double-buffered areas
+                module.zero_grad(set_to_none=True)
+                x.grad = None
+                y = module(x, implementation="cuda", sequence_parallel=sp, valid_counts=counts)
+                y.backward(upstream[:, sel])
+                sp.reduce_gradients_(module)
+            torch.cuda.synchronize()
+            outs.append((y.detach(), x.grad.clone(), [p.grad.clone() for p in module.parameters()]))
+        (y1, dx1, g1), (y2, dx2, g2) = outs
+        assert _rel(y1, y2) < 1e-3 and _rel(dx1, dx2) < 1e-3
+        for a, b in zip(g1, g2):
+            assert _rel(a, b) < 1e-3, (tuple(a.shape), _rel(a, b))
+        assert lib.ms_device_error() == 0
+        results[rank] = 1
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_peer_memory_kernels_match_nccl(tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"requires {world} CUDA devices")
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_peer_worker, args=(world, str(tmp_path / f"nccl{world}"), results), nprocs=world, join=True)
+    assert dict(results) == {r: 1 for r in range(world)}

@@ -19,6 +19,9 @@ import ctypes
 import pytest
 import torch
 
+from conftest import rel_l2
+from oracle import memsolve_oracle as O
+
 pytestmark = pytest.mark.gpu
 
 MS_ERR_STATIC_SCRATCH = 7
@@ -57,6 +60,19 @@ def test_static_scratch_entry_matches_workspace_entry():
         # L2) is met with room to spare, in fact bit for bit
         err = float((got.double() - want.double()).norm() / want.double().norm())
         assert err <= 1e-5
+        assert torch.equal(got, want)
+        # and against the FP64 oracle, at the limit of the statistics tests
+        g64, q64 = O.stage_stats(proj.cpu(), heads, rank, None, cos.cpu(), sin.cpu())
+        pk = got.view(batch * heads, rank * rank + rank * head_dim).cpu()
+        assert rel_l2(pk[:, : rank * rank].reshape(batch, heads, rank, rank), g64) <= 1e-5
+        assert rel_l2(pk[:, rank * rank:].reshape(batch, heads, rank, head_dim), q64) <= 1e-5
+        # "allocates nothing": the device's free memory is the same before and after another call
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        assert lib.ms_stats_forward_static(ctypes.byref(shape), proj.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                           None, got.data_ptr(), stream) == 0
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before
         assert torch.equal(got, want)
 
 
