@@ -48,7 +48,8 @@ typedef enum ms_status {
   MS_ERR_LAUNCH = 4,           /* a kernel launch reported a CUDA error                         */
   MS_ERR_DEVICE = 5,           /* current device is not sm_100-class                            */
   MS_ERR_ODD_HEAD_DIM = 6,     /* rotary tables given with an odd head dimension                */
-  MS_ERR_STATIC_SCRATCH = 7    /* shape too large for the built-in scratch of ms_stats_forward_static */
+  MS_ERR_STATIC_SCRATCH = 7,   /* shape too large for the built-in scratch of ms_stats_forward_static */
+  MS_ERR_DEBUG_SHAPE = 8       /* an FP32 debug entry point was called with a shape its kernel does not take */
 } ms_status;
 
 /* Capacity, in floats, of the scratch buffer compiled into the library for
@@ -205,7 +206,7 @@ int ms_stats_backward(const ms_shape* shape, const void* projected, const void* 
 /*
  * Compact adjoint per (b,h) and per head.  Inputs: E/de (workspace partials or `packed`),
  * the forward tape, base_raw, eta_raw.  Outputs (device, caller-allocated):
- *   gram_grad  bf16 [B,H,2,r,r]   dG + dG^T, split high/residual
+ *   gram_grad  bf16 [B,H,2,r,r]   (dG + dG^T) / sqrt(n), split high/residual (n = counts[b], or N)
  *   cross_grad bf16 [B,H,2,r,dp]  dQ, split high/residual
  *   d_base_raw f32  [H,r,r]       (not written in complement mode)
  *   d_eta_raw  f32  [H]
@@ -224,6 +225,18 @@ int ms_token_backward(const ms_shape* shape, const void* projected, const void* 
                       const float* cos, const float* sin, const float* counts,
                       const ms_tape* tape, const void* gram_grad, const void* cross_grad,
                       void* dprojected, void* stream);
+
+/*
+ * ms_token_backward that also writes its results before the BF16 rounding: dprojected_f32 is FP32
+ * [B, N, H*r + H*d] in the layout of dprojected.  Test instrument for the FP32 accuracy of the token
+ * pass on identical BF16 inputs (the reference checks its FP32 path the same way, stage by stage,
+ * tests/cuda/test_fast_path.py:2122-2123); it always runs the tcgen05 kernel and returns
+ * MS_ERR_DEBUG_SHAPE for shapes that kernel does not take (head_dim != 64, rank 48, unaligned).
+ */
+int ms_token_backward_debug(const ms_shape* shape, const void* projected, const void* dy,
+                            const float* cos, const float* sin, const float* counts,
+                            const ms_tape* tape, const void* gram_grad, const void* cross_grad,
+                            void* dprojected, float* dprojected_f32, void* stream);
 
 /*
  * Sequence-parallel building blocks that keep the per-head core off the critical path (same work

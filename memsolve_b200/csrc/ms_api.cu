@@ -35,6 +35,10 @@ int launch_readout(const ms_shape&, const Plan&, const void* projected, const fl
 int launch_token_backward(const ms_shape&, const Plan&, const void* projected, const void* dy, const float* cos,
                           const float* sin, const float* counts, const ms_tape&, const void* gram_grad,
                           const void* cross_grad, void* dprojected, const CoreAdjoint* core, cudaStream_t);
+int launch_token_backward_tc(const ms_shape&, const Plan&, const void* projected, const void* dy, const float* cos,
+                             const float* sin, const float* counts, const ms_tape&, const void* gram_grad,
+                             const void* cross_grad, void* dprojected, const CoreAdjoint* core, float* debug,
+                             cudaStream_t);
 
 static std::atomic<int> g_sm_count[64];
 
@@ -211,6 +215,11 @@ Plan make_plan(const ms_shape& s) {
     return v && v[0] == '1';
   }();
   p.tma = !no_tma;
+  static const bool no_tc = [] {
+    const char* v = std::getenv("MEMSOLVE_NO_TCGEN05");
+    return v && v[0] == '1';
+  }();
+  p.tc = p.tma && !no_tc;
   p.fwd_partial_floats = (size_t)s.rank * s.rank + (size_t)s.rank * s.head_dim;
   p.bwd_partial_floats = (size_t)s.rank * s.head_dim;
   {
@@ -270,6 +279,9 @@ const char* ms_status_string(int status) {
     case MS_ERR_LAUNCH: return "a CUDA kernel launch failed";
     case MS_ERR_DEVICE: return "the current CUDA device is not an sm_100-class GPU";
     case MS_ERR_ODD_HEAD_DIM: return "rotary content requires an even head dimension";
+    case MS_ERR_DEBUG_SHAPE:
+      return "the FP32 debug entry points cover the tensor-core (tcgen05) kernels only: head dimension 64, rank 16, "
+             "32 or 64, 16-byte aligned pointers";
     case MS_ERR_STATIC_SCRATCH:
       return "this shape needs more scratch than the built-in static buffer of ms_stats_forward_static holds "
              "(MS_STATIC_SCRATCH_FLOATS); use ms_stats_forward with a caller-provided workspace";
@@ -556,6 +568,23 @@ int ms_token_backward(const ms_shape* shape, const void* projected, const void* 
   plan.aligned = plan.aligned && is16(projected) && is16(dy) && is16(dprojected);
   return launch_token_backward(*shape, plan, projected, dy, cos, sin, counts, *tape, gram_grad, cross_grad,
                                dprojected, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int ms_token_backward_debug(const ms_shape* shape, const void* projected, const void* dy, const float* cos,
+                            const float* sin, const float* counts, const ms_tape* tape, const void* gram_grad,
+                            const void* cross_grad, void* dprojected, float* dprojected_f32, void* stream) {
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  if (!projected || !dy || !dprojected || !dprojected_f32 || !gram_grad || !cross_grad || !tape || !tape->eta ||
+      !tape->coeff)
+    return MS_ERR_INVALID_ARGUMENT;
+  if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
+  Plan plan = make_plan(*shape);
+  plan.aligned = plan.aligned && is16(projected) && is16(dy) && is16(dprojected) &&
+                 (!shape->rotary_rows || (is16(cos) && is16(sin)));
+  const int r = launch_token_backward_tc(*shape, plan, projected, dy, cos, sin, counts, *tape, gram_grad, cross_grad,
+                                         dprojected, nullptr, dprojected_f32, static_cast<cudaStream_t>(stream));
+  return r == -1 ? MS_ERR_DEBUG_SHAPE : r;
 }
 
 int ms_mix_backward(const ms_shape* shape, const void* projected, const void* dy, const float* base_raw,

@@ -663,7 +663,9 @@ compact_backward_kernel(const CompactBwdParams p) {
   }
   __syncthreads();
   MS_TICK(18);
-  // dG = T^T Y ;  stored as dG + dG^T (dG is symmetric) in two BF16 words
+  // dG = T^T Y ;  stored as s (dG + dG^T) (dG is symmetric, s = 1/sqrt(n): the factor the token pass would
+  // otherwise apply to the product A (dG + dG^T) before adding the other two products) in two BF16 words
+  const float s_tok = inv_sqrt_rn(n);
   __nv_bfloat16* ghi = p.gram_grad + (size_t)sys * 2 * R * R;
   __nv_bfloat16* glo = ghi + R * R;
   for (int tile = tid; tile < RTILES; tile += kCompactThreads) {
@@ -674,8 +676,8 @@ compact_backward_kernel(const CompactBwdParams p) {
     mm_tn_s(acc, ys, RP, ts, RP, i0, j0, j1, j0, R);
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      store_split(ghi, glo, (size_t)(i0 + r) * R + j0, acc[r][0]);
-      store_split(ghi, glo, (size_t)(i0 + r) * R + j1, acc[r][1]);
+      store_split(ghi, glo, (size_t)(i0 + r) * R + j0, acc[r][0] * s_tok);
+      store_split(ghi, glo, (size_t)(i0 + r) * R + j1, acc[r][1] * s_tok);
     }
   }
   MS_TICK(19);

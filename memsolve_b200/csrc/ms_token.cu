@@ -1,7 +1,7 @@
 // Token-parallel passes of the MemSolve mixer.
 //
 //   readout         Y  = eta*C + rot^-1(A_raw W) / sqrt(n)
-//   token backward  dA = s*( s*A_raw (dG+dG^T) + rot(dY) W^T + rot(C) dQ^T ),   s = 1/sqrt(n)
+//   token backward  dA = s*( A_raw S' + rot(dY) W^T + rot(C) dQ^T ),   S' = s (dG+dG^T),   s = 1/sqrt(n)
 //                   dC = eta*dY + s * rot^-1(A_raw dQ)
 //
 // Replaces the reference's `_readout` and `_token_backward` (memsolve/ball/cuda.py:1670-1922).
@@ -309,7 +309,7 @@ token_backward_kernel(const TokenParams p) {
       ldsm_x4(af[ks], a_tile + swz((warp * 16 + mr + 8 * (mi & 1)) * (R * 2) + (ks * 16 + 8 * (mi >> 1)) * 2));
 
     if (jb == 0) {
-      // s * A (dG + dG^T): the symmetric matrix is stored [n][k], residual word first
+      // A S' with S' = s (dG + dG^T): the symmetric matrix is stored [n][k], residual word first
 #pragma unroll
       for (int j = 0; j < NR; ++j)
 #pragma unroll
@@ -328,10 +328,6 @@ token_backward_kernel(const TokenParams p) {
           }
         }
       }
-#pragma unroll
-      for (int j = 0; j < NR; ++j)
-#pragma unroll
-        for (int k = 0; k < 4; ++k) acc_a[j][k] *= inv_s;
     }
 
     // rot(dY) W^T and rot(C) dQ^T
@@ -452,6 +448,11 @@ int launch_token_backward_tma(const ms_shape& s, const Plan& plan, const void* p
                               const void* gram_grad, const void* cross_grad, void* dprojected,
                               const CoreAdjoint* core, cudaStream_t st);
 
+int launch_token_backward_tc(const ms_shape& s, const Plan& plan, const void* projected, const void* dy,
+                             const float* cos, const float* sin, const float* counts, const ms_tape& t,
+                             const void* gram_grad, const void* cross_grad, void* dprojected,
+                             const CoreAdjoint* core, float* debug, cudaStream_t st);
+
 static TokenParams token_params(const ms_shape& s, const Plan& plan, const void* projected, const void* dy,
                                 const float* cos, const float* sin, const float* counts, const ms_tape& t,
                                 const void* gram_grad, const void* cross_grad, void* out) {
@@ -493,6 +494,11 @@ int launch_token_backward(const ms_shape& s, const Plan& plan, const void* proje
                           const float* cos, const float* sin, const float* counts, const ms_tape& t,
                           const void* gram_grad, const void* cross_grad, void* dprojected,
                           const CoreAdjoint* core, cudaStream_t st) {
+  if (plan.tc) {
+    const int r = launch_token_backward_tc(s, plan, projected, dy, cos, sin, counts, t, gram_grad, cross_grad,
+                                           dprojected, core, nullptr, st);
+    if (r != -1) return r;
+  }
   if (plan.tma) {
     const int r = launch_token_backward_tma(s, plan, projected, dy, cos, sin, counts, t, gram_grad, cross_grad,
                                             dprojected, core, st);

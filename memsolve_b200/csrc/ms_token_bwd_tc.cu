@@ -1,0 +1,521 @@
+// Token backward on the fifth-generation tensor cores (tcgen05), for long sequences: head dimension 64,
+// rank 16/32/64, aligned pointers, at least kTcMinTokens tokens per sample (other shapes take the
+// mma.sync kernels in ms_token_bwd_tma.cu / ms_token.cu).
+//
+//   dA = s*( A_raw S' + rot(dY) W^T + rot(C) dQ^T ),   S' = s (dG + dG^T),   dC = eta*dY + s*rot^-1(A_raw dQ)
+//
+// Same arithmetic as the reference's `_token_backward` (memsolve/ball/cuda.py:1767-1922): FP32 rotation,
+// rotated operands and the compact matrices W, dQ, S' carried as two BF16 words each, products of the
+// words accumulated in FP32 (high*high + low*high + high*low).
+//
+// Work item = (128-token tile, head).  A CTA serves one sample and one group of heads whose compact
+// matrices stay in shared memory, and walks over its items with a ring of shared-memory stages:
+//
+//   warp 8 (one thread)   TMA: loads the relation, content and upstream-gradient boxes of an item into a
+//                         stage; stores dA and dC, which the compute warps wrote over the relation and
+//                         gradient boxes, back to `dprojected`.
+//   warp 9 (one thread)   issues the tcgen05 MMAs; the accumulators of an item (dC: 128 x 64, dA: 128 x r,
+//                         FP32) live in tensor memory, two items in flight (slots).
+//   warps 0-3 / 4-7       one group per slot, one token row per thread: rotate dY and C in FP32, split them
+//                         into two BF16 words and write those straight into tensor memory, from where the
+//                         MMAs take them as the row operand (no rotated copy in shared memory); later read
+//                         the accumulators, apply the inverse rotation / eta / scale and write BF16 rows.
+//
+// Every wait is bounded (mbar_wait); after a timeout the error word is set and the CTA drains.  Spare
+// CTAs (blockIdx.x >= work CTAs) compute the per-head parameter gradients as in the mma.sync kernel.
+#include "ms_core.cuh"
+#include "ms_tc.cuh"
+
+namespace ms {
+
+constexpr int kTcThreads = 320;
+constexpr int kTcTile = 128;       // tokens per item
+constexpr int kTcMinTokens = 512;  // shorter samples leave most of a tile empty: mma.sync kernels
+
+template <int R>
+struct TokenBwdTcCfg {
+  static constexpr int A_ROW = R * 2;                   // bytes of one relation row
+  static constexpr int A_TILE = kTcTile * A_ROW;
+  static constexpr int STAGE = 32768 + A_TILE;          // content, gradient, relation boxes
+  static constexpr int STAGES = R == 64 ? 3 : 4;
+  static constexpr int W_BYTES = R * 128;
+  static constexpr int S_BYTES = R * R * 2;
+  static constexpr int HEAD_BYTES = 4 * W_BYTES + 2 * S_BYTES;   // W hi/lo, dQ hi/lo, S' hi/lo
+  static constexpr int BAR_BYTES = (2 * STAGES + 9) * 8 + 16;
+  static constexpr int MAX_SMEM = 227 * 1024;
+  static constexpr int RESIDENT_BUDGET = MAX_SMEM - 1024 - STAGES * STAGE - BAR_BYTES;
+  // tensor-memory columns of one slot
+  static constexpr int COL_DC = 0, COL_DA = 64, COL_YH = 128, COL_YL = 160, COL_CH = 192, COL_CL = 224, SLOT_COLS = 256;
+  static_assert(64 + R <= 128, "accumulators of a slot");
+};
+
+struct TokenBwdTcParams {
+  const float* cos;
+  const float* sin;
+  const float* counts;
+  const float* eta;
+  float* debug;      // optional FP32 copy of dprojected before the BF16 rounding ([B, N, H*(r+64)]), or null
+  int* error;
+  int tokens, heads, rotary_rows, group_heads, tiles, work_ctas, batch;
+  int core_ctas;
+  const float* base_raw;
+  const float* hmat;
+  const float* de_sys;
+  const float* eta_slope;
+  const float* core_map;
+  float* d_base;
+  float* d_eta_raw;
+  float grad_scale;
+  int complement;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+
+// one warp-uniform bounded wait
+__device__ __forceinline__ bool wait_uniform(uint32_t bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity));
+}
+
+// Rotate one 128-byte row (64 channels) of a 128-byte-swizzled tile and write its two BF16 words to the
+// tensor-memory columns [t_hi, t_hi + 32) and [t_lo, t_lo + 32) of this thread's lane.
+__device__ __forceinline__ void rotate_row_to_tmem(uint32_t tile, int row, const float (&cs)[32], const float (&sn)[32],
+                                                   uint32_t t_hi, uint32_t t_lo) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint32_t hi[16], lo[16];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int chunk = half * 4 + c;
+      const uint4 v = ld_shared_v4(tile + row * 128 + ((chunk ^ (row & 7)) << 4));
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int j = half * 16 + c * 4 + k;
+        const float2 f = bf2_to_f2(w[k]);
+        const float2 r = rot_pair(f.x, f.y, cs[j], sn[j]);
+        split2(r.x, r.y, hi[c * 4 + k], lo[c * 4 + k]);
+      }
+    }
+    tc::tmem_st16(t_hi + half * 16, hi);
+    tc::tmem_st16(t_lo + half * 16, lo);
+  }
+}
+
+template <int R, bool ROT>
+__global__ void __launch_bounds__(kTcThreads, 1)
+token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_c,
+                         const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_w,
+                         const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_s,
+                         const __grid_constant__ CUtensorMap map_oa, const __grid_constant__ CUtensorMap map_oc,
+                         const TokenBwdTcParams p) {
+  using Cfg = TokenBwdTcCfg<R>;
+  constexpr int S = Cfg::STAGES;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  grid_launch_dependents();
+
+  if ((int)blockIdx.x >= p.work_ctas) {
+    grid_dependency_wait();
+    if (blockIdx.y == 0 && blockIdx.z == 0) {
+      for (int head = (int)blockIdx.x - p.work_ctas; head < p.heads; head += p.core_ctas) {
+        core_backward_device(p.base_raw, p.hmat, p.de_sys, p.eta_slope, p.core_map, R, head, p.heads, p.batch,
+                             p.complement, p.grad_scale, p.d_base, p.d_eta_raw,
+                             smem_raw + (smem - smem_u32(smem_raw)), tid, kTcThreads);
+        __syncthreads();
+      }
+    }
+    return;
+  }
+
+  const int b = blockIdx.y;
+  const int h0 = blockIdx.z * p.group_heads;
+  const int gh = min(p.group_heads, p.heads - h0);
+  const uint32_t res_base = smem;
+  const uint32_t ring = smem + p.group_heads * Cfg::HEAD_BYTES;
+  const uint32_t bar_full = ring + S * Cfg::STAGE;
+  const uint32_t bar_out = bar_full + 8 * S;
+  const uint32_t bar_xf = bar_out + 8 * S;
+  const uint32_t bar_m1 = bar_xf + 16, bar_m2 = bar_m1 + 16, bar_free = bar_m2 + 16, bar_res = bar_free + 16;
+  const uint32_t tslot = bar_res + 8;
+
+  if (tid == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(bar_full + 8 * i, 1);
+      mbar_init(bar_out + 8 * i, 128);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_xf + 8 * i, 128);
+      mbar_init(bar_m1 + 8 * i, 1);
+      mbar_init(bar_m2 + 8 * i, 1);
+      mbar_init(bar_free + 8 * i, 128);
+    }
+    mbar_init(bar_res, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (warp == 9) tc::tmem_alloc(tslot, 512);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = ld_shared_u32(tslot);
+
+  const int total = p.tiles * gh;
+  const int per = (total + p.work_ctas - 1) / p.work_ctas;
+  const int it0 = min(total, (int)blockIdx.x * per);
+  const int n_items = min(total, it0 + per) - it0;
+  bool ok = true;
+
+  if (warp == 8) {
+    // ---------------------------------------------------------------- TMA producer / store issuer
+    if (lane == 0) {
+      auto issue_load = [&](int i) {
+        const int idx = it0 + i, tile = idx / gh, h = h0 + (idx - tile * gh);
+        const uint32_t st = ring + (i % S) * Cfg::STAGE, bar = bar_full + 8 * (i % S);
+        mbar_expect_tx(bar, Cfg::STAGE);
+        tma_load_3d(st, &map_c, p.heads * R + h * 64, tile * kTcTile, b, bar);
+        tma_load_3d(st + 16384, &map_y, h * 64, tile * kTcTile, b, bar);
+        tma_load_3d(st + 32768, &map_a, h * R, tile * kTcTile, b, bar);
+      };
+      // `projected` and the upstream gradient were complete before the kernel ahead of this one started, so
+      // a chained launch may fetch them while that kernel (which produces dQ and S') is still draining
+      for (int k = 0; k < S && k < n_items; ++k) issue_load(k);
+      grid_dependency_wait();
+      mbar_expect_tx(bar_res, (uint32_t)(gh * Cfg::HEAD_BYTES));
+      for (int hl = 0; hl < gh; ++hl) {
+        const int sys = b * p.heads + h0 + hl;
+        const uint32_t hb = res_base + hl * Cfg::HEAD_BYTES;
+        tma_load_2d(hb, &map_w, 0, (sys * 2) * R, bar_res);
+        tma_load_2d(hb + Cfg::W_BYTES, &map_w, 0, (sys * 2 + 1) * R, bar_res);
+        tma_load_2d(hb + 2 * Cfg::W_BYTES, &map_q, 0, (sys * 2) * R, bar_res);
+        tma_load_2d(hb + 3 * Cfg::W_BYTES, &map_q, 0, (sys * 2 + 1) * R, bar_res);
+        tma_load_2d(hb + 4 * Cfg::W_BYTES, &map_s, 0, (sys * 2) * R, bar_res);
+        tma_load_2d(hb + 4 * Cfg::W_BYTES + Cfg::S_BYTES, &map_s, 0, (sys * 2 + 1) * R, bar_res);
+      }
+      for (int i = 0; i < n_items; ++i) {
+        ok = mbar_wait(bar_out + 8 * (i % S), (i / S) & 1);
+        if (!ok) break;
+        const int idx = it0 + i, tile = idx / gh, h = h0 + (idx - tile * gh);
+        const uint32_t st = ring + (i % S) * Cfg::STAGE;
+        tma_store_3d(&map_oc, p.heads * R + h * 64, tile * kTcTile, b, st + 16384);
+        tma_store_3d(&map_oa, h * R, tile * kTcTile, b, st + 32768);
+        tma_store_commit();
+        if (i + S < n_items) {
+          tma_store_wait_read<0>();   // the stage is read by the stores just issued
+          issue_load(i + S);
+        }
+      }
+      tma_store_wait_all<0>();
+      if (!ok) atomicExch(p.error, kErrBarrierTimeout);
+    }
+  } else if (warp == 9) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_c = tc::idesc_bf16(128, 64, true);    // dC: B = dQ stored [r][64]
+      constexpr uint32_t idesc_a = tc::idesc_bf16(128, R, false);    // dA: B stored [r output columns][k]
+      grid_dependency_wait();
+      ok = mbar_wait(bar_res, 0);
+      auto head_tiles = [&](int i, uint32_t& st, uint32_t& hb) {
+        const int idx = it0 + i, tile = idx / gh;
+        st = ring + (i % S) * Cfg::STAGE;
+        hb = res_base + (idx - tile * gh) * Cfg::HEAD_BYTES;
+      };
+      // products that need only the raw relation rows: dC = A dQ, dA = A S'
+      auto phase_a = [&](int i) {
+        const int slot = i & 1;
+        if (!mbar_wait(bar_full + 8 * (i % S), (i / S) & 1)) return false;
+        if (i >= 2 && !mbar_wait(bar_free + 8 * slot, ((i >> 1) - 1) & 1)) return false;
+        tc::fence_after_sync();
+        uint32_t st, hb;
+        head_tiles(i, st, hb);
+        const uint32_t a_tile = st + 32768, tb = tmem + slot * Cfg::SLOT_COLS;
+        const uint32_t qh = hb + 2 * Cfg::W_BYTES, ql = qh + Cfg::W_BYTES;
+        const uint32_t sh = hb + 4 * Cfg::W_BYTES, sl = sh + Cfg::S_BYTES;
+#pragma unroll
+        for (int word = 0; word < 2; ++word) {
+#pragma unroll
+          for (int ks = 0; ks < R / 16; ++ks)
+            tc::mma_ss(tb + Cfg::COL_DC, tc::smem_desc_k_major<Cfg::A_ROW>(a_tile + ks * 32),
+                       tc::smem_desc_n_major_128((word == 0 ? ql : qh) + ks * 2048), idesc_c, (word | ks) != 0);
+        }
+#pragma unroll
+        for (int word = 0; word < 2; ++word) {
+#pragma unroll
+          for (int ks = 0; ks < R / 16; ++ks)
+            tc::mma_ss(tb + Cfg::COL_DA, tc::smem_desc_k_major<Cfg::A_ROW>(a_tile + ks * 32),
+                       tc::smem_desc_k_major<Cfg::A_ROW>((word == 0 ? sl : sh) + ks * 32), idesc_a, (word | ks) != 0);
+        }
+        tc::mma_commit(bar_m1 + 8 * slot);
+        return true;
+      };
+      // products with the (rotated) content and gradient rows: dA += rot(dY) W^T + rot(C) dQ^T
+      auto phase_b = [&](int i) {
+        const int slot = i & 1;
+        if (ROT) {
+          if (!mbar_wait(bar_xf + 8 * slot, (i >> 1) & 1)) return false;
+          tc::fence_after_sync();
+        }
+        uint32_t st, hb;
+        head_tiles(i, st, hb);
+        const uint32_t tb = tmem + slot * Cfg::SLOT_COLS;
+        const uint32_t wh = hb, wl = hb + Cfg::W_BYTES, qh = hb + 2 * Cfg::W_BYTES, ql = qh + Cfg::W_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t d_wh = tc::smem_desc_k_major<128>(wh + ks * 32), d_wl = tc::smem_desc_k_major<128>(wl + ks * 32);
+          const uint64_t d_qh = tc::smem_desc_k_major<128>(qh + ks * 32), d_ql = tc::smem_desc_k_major<128>(ql + ks * 32);
+          if (ROT) {
+            tc::mma_ts(tb + Cfg::COL_DA, tb + Cfg::COL_YL + ks * 8, d_wh, idesc_a, 1);
+            tc::mma_ts(tb + Cfg::COL_DA, tb + Cfg::COL_YH + ks * 8, d_wl, idesc_a, 1);
+            tc::mma_ts(tb + Cfg::COL_DA, tb + Cfg::COL_YH + ks * 8, d_wh, idesc_a, 1);
+            tc::mma_ts(tb + Cfg::COL_DA, tb + Cfg::COL_CL + ks * 8, d_qh, idesc_a, 1);
+            tc::mma_ts(tb + Cfg::COL_DA, tb + Cfg::COL_CH + ks * 8, d_ql, idesc_a, 1);
+            tc::mma_ts(tb + Cfg::COL_DA, tb + Cfg::COL_CH + ks * 8, d_qh, idesc_a, 1);
+          } else {
+            const uint64_t d_y = tc::smem_desc_k_major<128>(st + 16384 + ks * 32);
+            const uint64_t d_c = tc::smem_desc_k_major<128>(st + ks * 32);
+            tc::mma_ss(tb + Cfg::COL_DA, d_y, d_wl, idesc_a, 1);
+            tc::mma_ss(tb + Cfg::COL_DA, d_y, d_wh, idesc_a, 1);
+            tc::mma_ss(tb + Cfg::COL_DA, d_c, d_ql, idesc_a, 1);
+            tc::mma_ss(tb + Cfg::COL_DA, d_c, d_qh, idesc_a, 1);
+          }
+        }
+        tc::mma_commit(bar_m2 + 8 * slot);
+        return true;
+      };
+      if (ok && n_items > 0) ok = phase_a(0);
+      for (int i = 0; i < n_items && ok; ++i) {
+        if (i + 1 < n_items) ok = phase_a(i + 1);
+        if (ok) ok = phase_b(i);
+      }
+      if (!ok) atomicExch(p.error, kErrBarrierTimeout);
+    }
+  } else {
+    // ---------------------------------------------------------------- compute warps: one token row per thread
+    const int g = warp >> 2, q = warp & 3, row = q * 32 + lane;
+    const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16) + g * Cfg::SLOT_COLS;
+    grid_dependency_wait();
+    const float n = p.counts ? p.counts[b] : (float)p.tokens;
+    const float inv_s = inv_sqrt_rn(n);
+    const long tab_row_b = p.rotary_rows > 1 ? (long)b * p.tokens : 0;
+    const int width = p.heads * (R + 64);
+    float cs[32], sn[32];
+    int tab_tile = -1;
+
+    for (int i = g; i < n_items && ok; i += 2) {
+      const int stage = i % S;
+      const int idx = it0 + i, tile = idx / gh, h = h0 + (idx - tile * gh);
+      const uint32_t st = ring + stage * Cfg::STAGE;
+      const uint32_t c_tile = st, y_tile = st + 16384, a_tile = st + 32768;
+      const int tok = tile * kTcTile + row;
+      const bool valid = tok < p.tokens;
+      if (ROT && tile != tab_tile) {
+        const float4* c4 = reinterpret_cast<const float4*>(p.cos + (tab_row_b + tok) * 32);
+        const float4* s4 = reinterpret_cast<const float4*>(p.sin + (tab_row_b + tok) * 32);
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          float4 cv = make_float4(1.f, 1.f, 1.f, 1.f), sv = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (valid) {
+            cv = __ldg(c4 + v);
+            sv = __ldg(s4 + v);
+          }
+          cs[4 * v] = cv.x; cs[4 * v + 1] = cv.y; cs[4 * v + 2] = cv.z; cs[4 * v + 3] = cv.w;
+          sn[4 * v] = sv.x; sn[4 * v + 1] = sv.y; sn[4 * v + 2] = sv.z; sn[4 * v + 3] = sv.w;
+        }
+        tab_tile = tile;
+      }
+      const float eta = __ldg(p.eta + h);
+      const uint32_t par = (i >> 1) & 1;
+
+      ok = wait_uniform(bar_full + 8 * stage, (i / S) & 1);
+      if (!ok) break;
+      if (ROT) {
+        rotate_row_to_tmem(y_tile, row, cs, sn, lane_base + Cfg::COL_YH, lane_base + Cfg::COL_YL);
+        rotate_row_to_tmem(c_tile, row, cs, sn, lane_base + Cfg::COL_CH, lane_base + Cfg::COL_CL);
+        tc::wait_st();
+        tc::fence_before_sync();
+        mbar_arrive(bar_xf + 8 * g);
+      }
+
+      // dC = eta*dY + s * rot^-1(A dQ), written over the upstream-gradient row.  Without rotation the MMAs
+      // read that row from shared memory, so all of them must have completed first.
+      ok = wait_uniform((ROT ? bar_m1 : bar_m2) + 8 * g, par);
+      if (!ok) break;
+      tc::fence_after_sync();
+      float* dbg = (p.debug && valid) ? p.debug + ((size_t)b * p.tokens + tok) * width : nullptr;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t acc[32];
+        tc::tmem_ld16(lane_base + Cfg::COL_DC + half * 32, *reinterpret_cast<uint32_t(*)[16]>(&acc[0]));
+        tc::tmem_ld16(lane_base + Cfg::COL_DC + half * 32 + 16, *reinterpret_cast<uint32_t(*)[16]>(&acc[16]));
+        tc::wait_ld();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int chunk = half * 4 + c;
+          const uint32_t addr = y_tile + row * 128 + ((chunk ^ (row & 7)) << 4);
+          const uint4 yv = ld_shared_v4(addr);
+          const uint32_t yw[4] = {yv.x, yv.y, yv.z, yv.w};
+          uint32_t ow[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int j = half * 16 + c * 4 + k;
+            float2 corr = make_float2(__uint_as_float(acc[2 * (c * 4 + k)]), __uint_as_float(acc[2 * (c * 4 + k) + 1]));
+            if (ROT) corr = rot_pair(corr.x, corr.y, cs[j], -sn[j]);
+            const float2 yy = bf2_to_f2(yw[k]);
+            const float o0 = fmaf(corr.x, inv_s, eta * yy.x), o1 = fmaf(corr.y, inv_s, eta * yy.y);
+            ow[k] = f2_to_bf2(o0, o1);
+            if (dbg) {
+              dbg[p.heads * R + h * 64 + 2 * j] = o0;
+              dbg[p.heads * R + h * 64 + 2 * j + 1] = o1;
+            }
+          }
+          st_shared_v4(addr, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+        }
+      }
+
+      // dA = s * (A S' + rot(dY) W^T + rot(C) dQ^T), written over the relation row
+      if (ROT) {
+        ok = wait_uniform(bar_m2 + 8 * g, par);
+        if (!ok) break;
+        tc::fence_after_sync();
+      }
+      {
+        uint32_t acc[R];
+#pragma unroll
+        for (int c0 = 0; c0 < R; c0 += 16)
+          tc::tmem_ld16(lane_base + Cfg::COL_DA + c0, *reinterpret_cast<uint32_t(*)[16]>(&acc[c0]));
+        tc::wait_ld();
+#pragma unroll
+        for (int c = 0; c < R / 8; ++c) {
+          uint32_t ow[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float o0 = __uint_as_float(acc[8 * c + 2 * k]) * inv_s, o1 = __uint_as_float(acc[8 * c + 2 * k + 1]) * inv_s;
+            ow[k] = f2_to_bf2(o0, o1);
+            if (dbg) {
+              dbg[h * R + 8 * c + 2 * k] = o0;
+              dbg[h * R + 8 * c + 2 * k + 1] = o1;
+            }
+          }
+          st_shared_v4(a_tile + swz_rows<Cfg::A_ROW>(row * Cfg::A_ROW + c * 16), make_uint4(ow[0], ow[1], ow[2], ow[3]));
+        }
+      }
+      tc::fence_before_sync();
+      mbar_arrive(bar_free + 8 * g);
+      fence_async_shared();
+      mbar_arrive(bar_out + 8 * stage);
+    }
+    if (!ok && lane == 0) atomicExch(p.error, kErrBarrierTimeout);
+  }
+
+  // all roles meet here; the tensor memory goes back before the CTA exits
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 9) tc::tmem_free(tmem, 512);
+}
+
+template <int R>
+static int launch_token_bwd_tc_r(const ms_shape& s, const Plan& plan, const void* projected, const void* dy,
+                                 const float* cos, const float* sin, const float* counts, const ms_tape& t,
+                                 const void* gram_grad, const void* cross_grad, void* dprojected,
+                                 const CoreAdjoint* core, float* debug, cudaStream_t st) {
+  using Cfg = TokenBwdTcCfg<R>;
+  const int heads = s.heads, width = heads * (R + 64), dmodel = heads * 64;
+  int group = Cfg::RESIDENT_BUDGET / Cfg::HEAD_BYTES;
+  if (group < 1) return -1;
+  if (group > heads) group = heads;
+  const int groups = (heads + group - 1) / group;
+  group = (heads + groups - 1) / groups;   // even out the groups
+
+  CUtensorMap map_a, map_c, map_y, map_w, map_q, map_s, map_oa, map_oc;
+  {
+    const uint64_t dims[3] = {(uint64_t)width, (uint64_t)s.tokens, (uint64_t)s.batch};
+    const uint64_t str[2] = {(uint64_t)width * 2, (uint64_t)s.tokens * width * 2};
+    const uint32_t box_a[3] = {(uint32_t)R, kTcTile, 1};
+    const uint32_t box_c[3] = {64, kTcTile, 1};
+    const Swizzle sa = swizzle_for_rows<R * 2>();
+    if (encode_tensor_map(&map_a, const_cast<void*>(projected), 2, 3, dims, str, box_a, sa)) return MS_ERR_LAUNCH;
+    if (encode_tensor_map(&map_c, const_cast<void*>(projected), 2, 3, dims, str, box_c, Swizzle::B128)) return MS_ERR_LAUNCH;
+    if (encode_tensor_map(&map_oa, dprojected, 2, 3, dims, str, box_a, sa)) return MS_ERR_LAUNCH;
+    if (encode_tensor_map(&map_oc, dprojected, 2, 3, dims, str, box_c, Swizzle::B128)) return MS_ERR_LAUNCH;
+  }
+  {
+    const uint64_t dims[3] = {(uint64_t)dmodel, (uint64_t)s.tokens, (uint64_t)s.batch};
+    const uint64_t str[2] = {(uint64_t)dmodel * 2, (uint64_t)s.tokens * dmodel * 2};
+    const uint32_t box[3] = {64, kTcTile, 1};
+    if (encode_tensor_map(&map_y, const_cast<void*>(dy), 2, 3, dims, str, box, Swizzle::B128)) return MS_ERR_LAUNCH;
+  }
+  {
+    const uint64_t dims[2] = {64, (uint64_t)plan.systems * 2 * R};
+    const uint64_t str[1] = {128};
+    const uint32_t box[2] = {64, (uint32_t)R};
+    if (encode_tensor_map(&map_w, t.coeff, 2, 2, dims, str, box, Swizzle::B128)) return MS_ERR_LAUNCH;
+    if (encode_tensor_map(&map_q, const_cast<void*>(cross_grad), 2, 2, dims, str, box, Swizzle::B128)) return MS_ERR_LAUNCH;
+    const uint64_t sdims[2] = {(uint64_t)R, (uint64_t)plan.systems * 2 * R};
+    const uint64_t sstr[1] = {(uint64_t)R * 2};
+    const uint32_t sbox[2] = {(uint32_t)R, (uint32_t)R};
+    if (encode_tensor_map(&map_s, const_cast<void*>(gram_grad), 2, 2, sdims, sstr, sbox, swizzle_for_rows<R * 2>()))
+      return MS_ERR_LAUNCH;
+  }
+
+  TokenBwdTcParams p;
+  p.cos = cos; p.sin = sin; p.counts = counts; p.eta = t.eta; p.debug = debug;
+  p.error = device_error_word();
+  if (!p.error) return MS_ERR_LAUNCH;
+  p.tokens = s.tokens; p.heads = heads; p.rotary_rows = s.rotary_rows; p.group_heads = group;
+  p.tiles = (s.tokens + kTcTile - 1) / kTcTile; p.batch = s.batch;
+  p.base_raw = nullptr; p.hmat = nullptr; p.de_sys = nullptr; p.eta_slope = t.eta_slope; p.core_map = t.core_map;
+  p.d_base = nullptr; p.d_eta_raw = nullptr; p.grad_scale = 1.f; p.complement = s.complement;
+  if (core) {
+    p.base_raw = core->base_raw; p.hmat = core->hmat; p.de_sys = core->de_sys;
+    p.d_base = core->d_base; p.d_eta_raw = core->d_eta_raw; p.grad_scale = core->grad_scale;
+  }
+  const long total = (long)p.tiles * group;
+  // one CTA per SM; SMs are left for the per-head CTAs that ride along so that the whole grid is resident
+  const int core_ctas = core ? (s.batch <= 4 ? (heads + 1) / 2 : heads) : 0;
+  long ctas = (sm_count() - core_ctas) / ((long)s.batch * groups);
+  if (ctas < 1) ctas = 1;
+  const long need = (total + 3) / 4;   // at least four items per CTA pay for its resident matrices
+  if (ctas > need) ctas = need < 1 ? 1 : need;
+  p.work_ctas = (int)ctas;
+  p.core_ctas = core_ctas > 0 ? core_ctas : 1;
+  dim3 grid((unsigned)ctas + core_ctas, s.batch, groups);
+  int smem_bytes = 1024 + group * Cfg::HEAD_BYTES + Cfg::STAGES * Cfg::STAGE + Cfg::BAR_BYTES;
+  const int core_bytes = (int)core_backward_smem_bytes(R) + 1024;
+  if (core && smem_bytes < core_bytes) smem_bytes = core_bytes;
+  if (s.rotary_rows > 0) {
+    auto kern = token_backward_tc_kernel<R, true>;
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
+    launch_kernel(kern, grid, dim3(kTcThreads), smem_bytes, st, map_a, map_c, map_y, map_w, map_q, map_s, map_oa, map_oc, p);
+  } else {
+    auto kern = token_backward_tc_kernel<R, false>;
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
+    launch_kernel(kern, grid, dim3(kTcThreads), smem_bytes, st, map_a, map_c, map_y, map_w, map_q, map_s, map_oa, map_oc, p);
+  }
+  return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
+}
+
+// MS_OK / error, or -1 when the shape is outside this kernel's envelope.  `debug` (FP32 [B, N, H*(r+64)], or
+// null) receives the values before the BF16 rounding; with `debug` set shapes below kTcMinTokens are taken too.
+int launch_token_backward_tc(const ms_shape& s, const Plan& plan, const void* projected, const void* dy,
+                             const float* cos, const float* sin, const float* counts, const ms_tape& t,
+                             const void* gram_grad, const void* cross_grad, void* dprojected,
+                             const CoreAdjoint* core, float* debug, cudaStream_t st) {
+  if (!plan.aligned || s.head_dim != 64) return -1;
+  if (s.tokens < kTcMinTokens && !debug) return -1;
+  if (s.batch > 65535) return -1;
+  if (((reinterpret_cast<uintptr_t>(t.coeff) | reinterpret_cast<uintptr_t>(gram_grad) |
+        reinterpret_cast<uintptr_t>(cross_grad)) & 15u) != 0)
+    return -1;
+#define MS_TC_ARGS s, plan, projected, dy, cos, sin, counts, t, gram_grad, cross_grad, dprojected, core, debug, st
+  switch (s.rank) {
+    case 16: return launch_token_bwd_tc_r<16>(MS_TC_ARGS);
+    case 32: return launch_token_bwd_tc_r<32>(MS_TC_ARGS);
+    case 64: return launch_token_bwd_tc_r<64>(MS_TC_ARGS);
+  }
+#undef MS_TC_ARGS
+  return -1;
+}
+
+}  // namespace ms

@@ -1,7 +1,7 @@
 // Token backward -- TMA / persistent-warp version (head dimension 64, rank 16/32/64, aligned
 // pointers; other shapes take token_backward_kernel in ms_token.cu).
 //
-//   dA = s*( s*A_raw (dG+dG^T) + rot(dY) W^T + rot(C) dQ^T ),   dC = eta*dY + s*rot^-1(A_raw dQ)
+//   dA = s*( A_raw S' + rot(dY) W^T + rot(C) dQ^T ),  S' = s (dG+dG^T),   dC = eta*dY + s*rot^-1(A_raw dQ)
 //
 // Same arithmetic as the generic kernel (the reference's `_token_backward`,
 // memsolve/ball/cuda.py:1767-1922).  A CTA serves one sample and one group of heads whose
@@ -282,7 +282,7 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       }
     }
 
-    // dA = s*( s*A (dG + dG^T) + rot(dY) W^T + rot(C) dQ^T ): the symmetric matrix is stored [n][k],
+    // dA = s*( A S' + rot(dY) W^T + rot(C) dQ^T ): the symmetric matrix S' = s (dG + dG^T) is stored [n][k],
     // residual word first
     float acc_a[NR][4];
 #pragma unroll
@@ -303,10 +303,6 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         }
       }
     }
-#pragma unroll
-    for (int j = 0; j < NR; ++j)
-#pragma unroll
-      for (int q = 0; q < 4; ++q) acc_a[j][q] *= inv_s;
     mma_rotated_rows<R, ROT>(acc_a, xraw, tab, wh_tile, wl_tile, lane);
     load_row_frags(xraw, c_tile, 0, lane);
     mma_rotated_rows<R, ROT>(acc_a, xraw, tab, qh_tile, ql_tile, lane);

@@ -1,0 +1,108 @@
+"""The tcgen05 (fifth-generation tensor core) token kernels: parity against the FP64 oracle on the shapes
+that take them (head dimension 64, rank 16/32/64, long samples), and their FP32 results before the BF16
+store against the same oracle at the FP32 criterion (<= 1e-4 relative L2 on identical BF16 inputs)."""
+from __future__ import annotations
+
+import ctypes
+
+import pytest
+import torch
+
+from conftest import rel_l2
+from oracle import memsolve_oracle as O
+from test_fast_mix_gpu import _assert_case, _dev, _random_case, cuda_mod  # noqa: F401  (fixture)
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("batch,length,heads,rank,rot,comp,masked", [
+    (1, 515, 2, 32, True, False, False),      # ragged last 128-token tile
+    (2, 3000, 12, 32, True, False, False),    # four head groups per sample
+    (1, 4096, 12, 64, True, False, False),    # one head per CTA group
+    (2, 2500, 5, 16, True, True, False),      # rank 16, complement mode
+    (2, 1500, 3, 32, False, False, True),     # no rotation: operands straight from shared memory; gaps, empty sample
+    (1, 2048, 4, 64, False, True, False),
+    (3, 700, 6, 16, False, False, False),
+    (2, 1100, 4, 32, True, False, True),      # per-sample tables with gaps
+])
+def test_tcgen05_token_backward_matches_oracle(cuda_mod, batch, length, heads, rank, rot, comp, masked):
+    case = _random_case(9100 + length + rank, batch, length, heads, rank, 64, comp=comp, rot=rot, masked=masked,
+                        batched_table=rot and masked)
+    _assert_case(cuda_mod, *case, gproj=5e-3 if rot else 3e-2, gpar=5e-4 if rot else 3e-2,
+                 tag=f"tcgen05 B{batch} N{length} H{heads} r{rank} rot={rot} comp={comp} masked={masked}")
+    assert cuda_mod._LIB.ms_device_error() == 0
+
+
+def _backward_stages(cuda_mod, proj, base, eta_raw, counts, cos, sin, dy):
+    """Forward tape, adjoint statistics and compact adjoint through the C ABI; returns what the token pass needs."""
+    lib = cuda_mod._LIB
+    dp, db, de, ddy = proj.cuda(), base.cuda(), eta_raw.cuda(), dy.cuda().contiguous()
+    dcos, dsin, dcounts = _dev(cos), _dev(sin), _dev(counts)
+    _, tape, dims = cuda_mod._mix_forward(dp, db, de, dcounts, None, dcos, dsin)
+    shape = cuda_mod._Shape(*dims, 0)
+    batch, length, heads, rank, head_dim = dims[:5]
+    ws = cuda_mod._workspace(shape, dp.device)
+    tape_c = tape.as_struct()
+    stream = torch.cuda.current_stream().cuda_stream
+    ptr = cuda_mod._ptr
+    gram = torch.empty(batch, heads, 2, rank, rank, device="cuda", dtype=torch.bfloat16)
+    cross = torch.empty(batch, heads, 2, rank, lib.ms_padded_head_dim(head_dim), device="cuda", dtype=torch.bfloat16)
+    d_base, d_raw = torch.empty_like(db), torch.empty_like(de)
+    assert lib.ms_stats_backward(ctypes.byref(shape), dp.data_ptr(), ddy.data_ptr(), ptr(dcos), ptr(dsin),
+                                 ptr(dcounts), ws.data_ptr(), ws.numel(), None, stream) == 0
+    assert lib.ms_compact_backward(ctypes.byref(shape), ptr(dcounts), ws.data_ptr(), ws.numel(), None,
+                                   ctypes.byref(tape_c), db.data_ptr() if db.numel() else None, de.data_ptr(), 1.0,
+                                   gram.data_ptr(), cross.data_ptr(), d_base.data_ptr() if db.numel() else None,
+                                   d_raw.data_ptr(), stream) == 0
+    return shape, tape, tape_c, (dp, ddy, dcos, dsin, dcounts), gram, cross
+
+
+@pytest.mark.parametrize("rank,rot,length", [(32, True, 2300), (64, True, 1024), (16, False, 1500), (32, False, 300)])
+def test_token_backward_fp32_before_rounding(cuda_mod, rank, rot, length):
+    """The token pass itself at the FP32 criterion: its FP32 results (two-word operands, FP32 accumulation,
+    FP32 rotation) against the FP64 oracle on identical BF16 `projected` and upstream gradient, <= 1e-4; the
+    BF16 tensor written beside them is exactly the rounding of those FP32 values."""
+    lib = cuda_mod._LIB
+    heads, batch = 3, 2
+    proj, base, eta_raw, counts, cos, sin, dy = _random_case(640 + rank, batch, length, heads, rank, 64, rot=rot)
+    shape, tape, tape_c, (dp, ddy, dcos, dsin, dcounts), gram, cross = _backward_stages(
+        cuda_mod, proj, base, eta_raw, counts, cos, sin, dy)
+    ptr = cuda_mod._ptr
+    out16 = torch.empty_like(dp)
+    out32 = torch.full(dp.shape, float("nan"), device="cuda", dtype=torch.float32)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.ms_token_backward_debug(ctypes.byref(shape), dp.data_ptr(), ddy.data_ptr(), ptr(dcos), ptr(dsin),
+                                       ptr(dcounts), ctypes.byref(tape_c), gram.data_ptr(), cross.data_ptr(),
+                                       out16.data_ptr(), out32.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert lib.ms_device_error() == 0
+    want = O.stage_backward(proj, dy, base, eta_raw, counts, cos, sin)["dprojected"]
+    err32, err16 = rel_l2(out32, want), rel_l2(out16, want)
+    print(f"token backward r{rank} rot={rot} N{length}: FP32 {err32:.2e}, BF16 {err16:.2e}")
+    assert torch.isfinite(out32).all()
+    assert err32 <= 1e-4
+    assert err16 <= 5e-3
+    assert torch.equal(out32.bfloat16(), out16)
+    # the production entry point gives the same BF16 tensor
+    again = torch.empty_like(dp)
+    assert lib.ms_token_backward(ctypes.byref(shape), dp.data_ptr(), ddy.data_ptr(), ptr(dcos), ptr(dsin),
+                                 ptr(dcounts), ctypes.byref(tape_c), gram.data_ptr(), cross.data_ptr(),
+                                 again.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    if length >= 512:
+        assert torch.equal(again, out16)
+    else:
+        assert rel_l2(again, out16) <= 4e-3   # short samples take the mma.sync kernel: same values to BF16 rounding
+
+
+def test_debug_entry_rejects_other_shapes(cuda_mod):
+    lib = cuda_mod._LIB
+    proj, base, eta_raw, counts, cos, sin, dy = _random_case(5, 1, 600, 2, 48, 64)
+    shape, tape, tape_c, (dp, ddy, dcos, dsin, dcounts), gram, cross = _backward_stages(
+        cuda_mod, proj, base, eta_raw, counts, cos, sin, dy)
+    out16 = torch.empty_like(dp)
+    out32 = torch.empty(dp.shape, device="cuda")
+    status = lib.ms_token_backward_debug(ctypes.byref(shape), dp.data_ptr(), ddy.data_ptr(), None, None, None,
+                                         ctypes.byref(tape_c), gram.data_ptr(), cross.data_ptr(), out16.data_ptr(),
+                                         out32.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert status == 8 and b"tcgen05" in lib.ms_status_string(status)
