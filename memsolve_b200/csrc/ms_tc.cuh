@@ -63,30 +63,93 @@ __host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, bool b_n_major) 
 }
 
 // ---------------------------------------------------------------------------------------
-// MMA issue (one thread) and completion
+// MMA issue and completion
 // ---------------------------------------------------------------------------------------
-// D[128 x N] (+)= A[128 x 16] B[N x 16]^T; `accumulate` == 0 overwrites D.
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// The three functions below are called by a whole, converged warp with warp-uniform arguments; one elected
+// lane (always the same one) executes the instruction.  Keeping the surrounding code warp-uniform lets the
+// compiler hold descriptors in uniform registers, which is where the MMA instruction wants them: issued
+// from a divergent `if (lane == 0)` region the same loop took about 80 cycles per MMA.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t chosen;
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
+      "elect.sync _|p, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(chosen));
+  return chosen != 0;
+}
+// D[128 x N] (+)= A[128 x 16] B[N x 16]^T; `accumulate` == 0 overwrites D.
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  if (elect_one()) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
 }
 // the same with the row operand A in tensor memory: lane = row, 8 columns per 16 BF16 values
 __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  if (elect_one()) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// the mbarrier at `bar` receives one arrival when every MMA issued so far by the elected lane has completed
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  if (elect_one())
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------
+// the same instructions for a batch issued from inside ONE elected region: no election per MMA, the
+// constant upper descriptor word and the instruction descriptor are immediates, the lower word (start
+// address / 16 and leading offset) is the only run-time part.  With the election, the 64-bit descriptor
+// arithmetic and the conversions to uniform registers done per MMA, the issuing warp (which shares its
+// scheduler with compute warps) needed ~200 cycles per MMA against the 22-50 the tensor core takes.
+// ---------------------------------------------------------------------------------------
+constexpr uint32_t desc_hi_k_major(int row_bytes) {
+  return (uint32_t)((8 * row_bytes) >> 4) | (1u << 14) | ((row_bytes == 128 ? 2u : (row_bytes == 64 ? 4u : 6u)) << 29);
+}
+constexpr uint32_t desc_hi_n_major_128() { return (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29); }
+__device__ __forceinline__ uint32_t desc_lo_k_major(uint32_t addr) { return ((addr & 0x3ffffu) >> 4) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_lo_n_major_128(uint32_t addr) { return ((addr & 0x3ffffu) >> 4) | ((1024u >> 4) << 16); }
+
+template <uint32_t HI_A, uint32_t HI_B, uint32_t IDESC>
+__device__ __forceinline__ void mma_ss_raw(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t accumulate) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      ".reg .b64 da, db;\n"
+      "mov.b64 da, {%1, %4};\n"
+      "mov.b64 db, {%2, %5};\n"
+      "setp.ne.b32 p, %3, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %6, p;\n"
+      "}\n" ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(accumulate), "n"(HI_A), "n"(HI_B), "n"(IDESC)
       : "memory");
 }
-// the mbarrier at `bar` receives one arrival when every MMA issued so far by this thread has completed
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
+template <uint32_t HI_B, uint32_t IDESC>
+__device__ __forceinline__ void mma_ts_raw(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 db;\n"
+      "mov.b64 db, {%2, %4};\n"
+      "setp.ne.b32 p, %3, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %5, p;\n"
+      "}\n" ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(accumulate), "n"(HI_B), "n"(IDESC)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_raw(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
 
@@ -101,6 +164,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&r)[16]) {
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(addr)
       : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(addr)
+               : "memory");
 }
 __device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&r)[16]) {
   asm volatile(

@@ -11,15 +11,21 @@
 // Work item = (128-token tile, head).  A CTA serves one sample and one group of heads whose compact
 // matrices stay in shared memory, and walks over its items with a ring of shared-memory stages:
 //
-//   warp 8 (one thread)   TMA: loads the relation, content and upstream-gradient boxes of an item into a
+//   warp 16 (one thread)  TMA: loads the relation, content and upstream-gradient boxes of an item into a
 //                         stage; stores dA and dC, which the compute warps wrote over the relation and
 //                         gradient boxes, back to `dprojected`.
-//   warp 9 (one thread)   issues the tcgen05 MMAs; the accumulators of an item (dC: 128 x 64, dA: 128 x r,
-//                         FP32) live in tensor memory, two items in flight (slots).
-//   warps 0-3 / 4-7       one group per slot, one token row per thread: rotate dY and C in FP32, split them
+//   warp 17               issues the tcgen05 MMAs (warp-uniform control flow, one elected lane issues each
+//                         batch); the accumulators of an item (dC: 128 x 64, dA: 128 x r, FP32) live in
+//                         tensor memory, two items in flight (slots).
+//   warps 0-7 / 8-15      one group per slot, half a token row per thread: rotate dY and C in FP32, split them
 //                         into two BF16 words and write those straight into tensor memory, from where the
 //                         MMAs take them as the row operand (no rotated copy in shared memory); later read
 //                         the accumulators, apply the inverse rotation / eta / scale and write BF16 rows.
+//
+//   warp 18 (one thread)  TMA: brings the cos / sin rows of the next token tile (128 x 32 FP32 each) into a
+//                         shared-memory buffer; every compute thread copies its 16 + 16 entries to registers
+//                         once per tile.  (Read straight from global memory, one row per thread, the tables
+//                         cost 16 us of a 60 us launch: 32 cache lines per load instruction.)
 //
 // Every wait is bounded (mbar_wait); after a timeout the error word is set and the CTA drains.  Spare
 // CTAs (blockIdx.x >= work CTAs) compute the per-head parameter gradients as in the mma.sync kernel.
@@ -28,7 +34,9 @@
 
 namespace ms {
 
-constexpr int kTcThreads = 320;
+constexpr int kTcComputeWarps = 16;                  // two groups of eight
+constexpr int kTcThreads = (kTcComputeWarps + 3) * 32;
+constexpr int kTcGroupThreads = 256;
 constexpr int kTcTile = 128;       // tokens per item
 constexpr int kTcMinTokens = 512;  // shorter samples leave most of a tile empty: mma.sync kernels
 
@@ -37,13 +45,14 @@ struct TokenBwdTcCfg {
   static constexpr int A_ROW = R * 2;                   // bytes of one relation row
   static constexpr int A_TILE = kTcTile * A_ROW;
   static constexpr int STAGE = 32768 + A_TILE;          // content, gradient, relation boxes
-  static constexpr int STAGES = R == 64 ? 3 : 4;
+  static constexpr int STAGES = R == 16 ? 4 : 3;
+  static constexpr int TABLE_BYTES = 32768;             // cos and sin rows of one token tile
   static constexpr int W_BYTES = R * 128;
   static constexpr int S_BYTES = R * R * 2;
   static constexpr int HEAD_BYTES = 4 * W_BYTES + 2 * S_BYTES;   // W hi/lo, dQ hi/lo, S' hi/lo
-  static constexpr int BAR_BYTES = (2 * STAGES + 9) * 8 + 16;
+  static constexpr int BAR_BYTES = (2 * STAGES + 11) * 8 + 16;
   static constexpr int MAX_SMEM = 227 * 1024;
-  static constexpr int RESIDENT_BUDGET = MAX_SMEM - 1024 - STAGES * STAGE - BAR_BYTES;
+  static constexpr int RESIDENT_BUDGET = MAX_SMEM - 1024 - STAGES * STAGE - TABLE_BYTES - BAR_BYTES;
   // tensor-memory columns of one slot
   static constexpr int COL_DC = 0, COL_DA = 64, COL_YH = 128, COL_YL = 160, COL_CH = 192, COL_CL = 224, SLOT_COLS = 256;
   static_assert(64 + R <= 128, "accumulators of a slot");
@@ -78,29 +87,25 @@ __device__ __forceinline__ bool wait_uniform(uint32_t bar, uint32_t parity) {
   return __all_sync(0xffffffffu, mbar_wait(bar, parity));
 }
 
-// Rotate one 128-byte row (64 channels) of a 128-byte-swizzled tile and write its two BF16 words to the
-// tensor-memory columns [t_hi, t_hi + 32) and [t_lo, t_lo + 32) of this thread's lane.
-__device__ __forceinline__ void rotate_row_to_tmem(uint32_t tile, int row, const float (&cs)[32], const float (&sn)[32],
-                                                   uint32_t t_hi, uint32_t t_lo) {
+// Rotate 32 channels (64 bytes: 16-byte chunks 4*half .. 4*half + 3) of one row of a 128-byte-swizzled tile and
+// write their two BF16 words to 16 tensor-memory columns each, starting at t_hi / t_lo, of this thread's lane.
+__device__ __forceinline__ void rotate_half_row_to_tmem(uint32_t tile, int row, int half, const float (&cs)[16],
+                                                        const float (&sn)[16], uint32_t t_hi, uint32_t t_lo) {
+  uint32_t hi[16], lo[16];
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    uint32_t hi[16], lo[16];
+  for (int c = 0; c < 4; ++c) {
+    const int chunk = half * 4 + c;
+    const uint4 v = ld_shared_v4(tile + row * 128 + ((chunk ^ (row & 7)) << 4));
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const int chunk = half * 4 + c;
-      const uint4 v = ld_shared_v4(tile + row * 128 + ((chunk ^ (row & 7)) << 4));
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int j = half * 16 + c * 4 + k;
-        const float2 f = bf2_to_f2(w[k]);
-        const float2 r = rot_pair(f.x, f.y, cs[j], sn[j]);
-        split2(r.x, r.y, hi[c * 4 + k], lo[c * 4 + k]);
-      }
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = bf2_to_f2(w[k]);
+      const float2 r = rot_pair(f.x, f.y, cs[c * 4 + k], sn[c * 4 + k]);
+      split2(r.x, r.y, hi[c * 4 + k], lo[c * 4 + k]);
     }
-    tc::tmem_st16(t_hi + half * 16, hi);
-    tc::tmem_st16(t_lo + half * 16, lo);
   }
+  tc::tmem_st16(t_hi, hi);
+  tc::tmem_st16(t_lo, lo);
 }
 
 template <int R, bool ROT>
@@ -109,9 +114,11 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                          const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_w,
                          const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_s,
                          const __grid_constant__ CUtensorMap map_oa, const __grid_constant__ CUtensorMap map_oc,
+                         const __grid_constant__ CUtensorMap map_cos, const __grid_constant__ CUtensorMap map_sin,
                          const TokenBwdTcParams p) {
   using Cfg = TokenBwdTcCfg<R>;
   constexpr int S = Cfg::STAGES;
+  constexpr int kProducerWarp = kTcComputeWarps, kMmaWarp = kTcComputeWarps + 1, kTableWarp = kTcComputeWarps + 2;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -135,28 +142,32 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int gh = min(p.group_heads, p.heads - h0);
   const uint32_t res_base = smem;
   const uint32_t ring = smem + p.group_heads * Cfg::HEAD_BYTES;
-  const uint32_t bar_full = ring + S * Cfg::STAGE;
+  const uint32_t tab_buf = ring + S * Cfg::STAGE;
+  const uint32_t bar_full = tab_buf + Cfg::TABLE_BYTES;
   const uint32_t bar_out = bar_full + 8 * S;
   const uint32_t bar_xf = bar_out + 8 * S;
   const uint32_t bar_m1 = bar_xf + 16, bar_m2 = bar_m1 + 16, bar_free = bar_m2 + 16, bar_res = bar_free + 16;
-  const uint32_t tslot = bar_res + 8;
+  const uint32_t bar_tab_full = bar_res + 8, bar_tab_free = bar_tab_full + 8;
+  const uint32_t tslot = bar_tab_free + 8;
 
   if (tid == 0) {
     for (int i = 0; i < S; ++i) {
       mbar_init(bar_full + 8 * i, 1);
-      mbar_init(bar_out + 8 * i, 128);
+      mbar_init(bar_out + 8 * i, kTcGroupThreads);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bar_xf + 8 * i, 128);
+      mbar_init(bar_xf + 8 * i, kTcGroupThreads);
       mbar_init(bar_m1 + 8 * i, 1);
       mbar_init(bar_m2 + 8 * i, 1);
-      mbar_init(bar_free + 8 * i, 128);
+      mbar_init(bar_free + 8 * i, kTcGroupThreads);
     }
     mbar_init(bar_res, 1);
+    mbar_init(bar_tab_full, 1);
+    mbar_init(bar_tab_free, 2 * kTcGroupThreads);
     mbar_fence_init();
   }
   __syncthreads();
-  if (warp == 9) tc::tmem_alloc(tslot, 512);
+  if (warp == kMmaWarp) tc::tmem_alloc(tslot, 512);
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
@@ -166,18 +177,21 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int per = (total + p.work_ctas - 1) / p.work_ctas;
   const int it0 = min(total, (int)blockIdx.x * per);
   const int n_items = min(total, it0 + per) - it0;
+  // token tiles this CTA touches: ordinal k = tile - tile0
+  const int tile0 = it0 / gh;
+  const int n_tiles = n_items > 0 ? (it0 + n_items - 1) / gh - tile0 + 1 : 0;
   bool ok = true;
 
-  if (warp == 8) {
+  if (warp == kProducerWarp) {
     // ---------------------------------------------------------------- TMA producer / store issuer
     if (lane == 0) {
       auto issue_load = [&](int i) {
         const int idx = it0 + i, tile = idx / gh, h = h0 + (idx - tile * gh);
         const uint32_t st = ring + (i % S) * Cfg::STAGE, bar = bar_full + 8 * (i % S);
         mbar_expect_tx(bar, Cfg::STAGE);
-        tma_load_3d(st, &map_c, p.heads * R + h * 64, tile * kTcTile, b, bar);
-        tma_load_3d(st + 16384, &map_y, h * 64, tile * kTcTile, b, bar);
         tma_load_3d(st + 32768, &map_a, h * R, tile * kTcTile, b, bar);
+        tma_load_3d(st + 16384, &map_y, h * 64, tile * kTcTile, b, bar);
+        tma_load_3d(st, &map_c, p.heads * R + h * 64, tile * kTcTile, b, bar);
       };
       // `projected` and the upstream gradient were complete before the kernel ahead of this one started, so
       // a chained launch may fetch them while that kernel (which produces dQ and S') is still draining
@@ -210,98 +224,151 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tma_store_wait_all<0>();
       if (!ok) atomicExch(p.error, kErrBarrierTimeout);
     }
-  } else if (warp == 9) {
-    // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_c = tc::idesc_bf16(128, 64, true);    // dC: B = dQ stored [r][64]
-      constexpr uint32_t idesc_a = tc::idesc_bf16(128, R, false);    // dA: B stored [r output columns][k]
-      grid_dependency_wait();
-      ok = mbar_wait(bar_res, 0);
-      auto head_tiles = [&](int i, uint32_t& st, uint32_t& hb) {
-        const int idx = it0 + i, tile = idx / gh;
-        st = ring + (i % S) * Cfg::STAGE;
-        hb = res_base + (idx - tile * gh) * Cfg::HEAD_BYTES;
-      };
-      // products that need only the raw relation rows: dC = A dQ, dA = A S'
-      auto phase_a = [&](int i) {
-        const int slot = i & 1;
-        if (!mbar_wait(bar_full + 8 * (i % S), (i / S) & 1)) return false;
-        if (i >= 2 && !mbar_wait(bar_free + 8 * slot, ((i >> 1) - 1) & 1)) return false;
-        tc::fence_after_sync();
-        uint32_t st, hb;
-        head_tiles(i, st, hb);
-        const uint32_t a_tile = st + 32768, tb = tmem + slot * Cfg::SLOT_COLS;
-        const uint32_t qh = hb + 2 * Cfg::W_BYTES, ql = qh + Cfg::W_BYTES;
-        const uint32_t sh = hb + 4 * Cfg::W_BYTES, sl = sh + Cfg::S_BYTES;
-#pragma unroll
-        for (int word = 0; word < 2; ++word) {
-#pragma unroll
-          for (int ks = 0; ks < R / 16; ++ks)
-            tc::mma_ss(tb + Cfg::COL_DC, tc::smem_desc_k_major<Cfg::A_ROW>(a_tile + ks * 32),
-                       tc::smem_desc_n_major_128((word == 0 ? ql : qh) + ks * 2048), idesc_c, (word | ks) != 0);
+  } else if (warp == kTableWarp) {
+    // ---------------------------------------------------------------- table producer
+    if (ROT && lane == 0) {
+      const int tab_b = p.rotary_rows > 1 ? b : 0;
+      for (int k = 0; k < n_tiles; ++k) {
+        if (k > 0) {
+          ok = mbar_wait(bar_tab_free, (k - 1) & 1);   // every compute thread has copied the rows of tile k - 1
+          if (!ok) break;
         }
-#pragma unroll
-        for (int word = 0; word < 2; ++word) {
-#pragma unroll
-          for (int ks = 0; ks < R / 16; ++ks)
-            tc::mma_ss(tb + Cfg::COL_DA, tc::smem_desc_k_major<Cfg::A_ROW>(a_tile + ks * 32),
-                       tc::smem_desc_k_major<Cfg::A_ROW>((word == 0 ? sl : sh) + ks * 32), idesc_a, (word | ks) != 0);
-        }
-        tc::mma_commit(bar_m1 + 8 * slot);
-        return true;
-      };
-      // products with the (rotated) content and gradient rows: dA += rot(dY) W^T + rot(C) dQ^T
-      auto phase_b = [&](int i) {
-        const int slot = i & 1;
-        if (ROT) {
-          if (!mbar_wait(bar_xf + 8 * slot, (i >> 1) & 1)) return false;
-          tc::fence_after_sync();
-        }
-        uint32_t st, hb;
-        head_tiles(i, st, hb);
-        const uint32_t tb = tmem + slot * Cfg::SLOT_COLS;
-        const uint32_t wh = hb, wl = hb + Cfg::W_BYTES, qh = hb + 2 * Cfg::W_BYTES, ql = qh + Cfg::W_BYTES;
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t d_wh = tc::smem_desc_k_major<128>(wh + ks * 32), d_wl = tc::smem_desc_k_major<128>(wl + ks * 32);
-          const uint64_t d_qh = tc::smem_desc_k_major<128>(qh + ks * 32), d_ql = tc::smem_desc_k_major<128>(ql + ks * 32);
-          if (ROT) {
-            tc::mma_ts(tb + Cfg::COL_DA, tb + Cfg::COL_YL + ks * 8, d_wh, idesc_a, 1);
-            tc::mma_ts(tb + Cfg::COL_DA, tb + Cfg::COL_YH + ks * 8, d_wl, idesc_a, 1);
-            tc::mma_ts(tb + Cfg::COL_DA, tb + Cfg::COL_YH + ks * 8, d_wh, idesc_a, 1);
-            tc::mma_ts(tb + Cfg::COL_DA, tb + Cfg::COL_CL + ks * 8, d_qh, idesc_a, 1);
-            tc::mma_ts(tb + Cfg::COL_DA, tb + Cfg::COL_CH + ks * 8, d_ql, idesc_a, 1);
-            tc::mma_ts(tb + Cfg::COL_DA, tb + Cfg::COL_CH + ks * 8, d_qh, idesc_a, 1);
-          } else {
-            const uint64_t d_y = tc::smem_desc_k_major<128>(st + 16384 + ks * 32);
-            const uint64_t d_c = tc::smem_desc_k_major<128>(st + ks * 32);
-            tc::mma_ss(tb + Cfg::COL_DA, d_y, d_wl, idesc_a, 1);
-            tc::mma_ss(tb + Cfg::COL_DA, d_y, d_wh, idesc_a, 1);
-            tc::mma_ss(tb + Cfg::COL_DA, d_c, d_ql, idesc_a, 1);
-            tc::mma_ss(tb + Cfg::COL_DA, d_c, d_qh, idesc_a, 1);
-          }
-        }
-        tc::mma_commit(bar_m2 + 8 * slot);
-        return true;
-      };
-      if (ok && n_items > 0) ok = phase_a(0);
-      for (int i = 0; i < n_items && ok; ++i) {
-        if (i + 1 < n_items) ok = phase_a(i + 1);
-        if (ok) ok = phase_b(i);
+        mbar_expect_tx(bar_tab_full, Cfg::TABLE_BYTES);
+        tma_load_3d(tab_buf, &map_cos, 0, (tile0 + k) * kTcTile, tab_b, bar_tab_full);
+        tma_load_3d(tab_buf + 16384, &map_sin, 0, (tile0 + k) * kTcTile, tab_b, bar_tab_full);
       }
       if (!ok) atomicExch(p.error, kErrBarrierTimeout);
     }
+  } else if (warp == kMmaWarp) {
+    // ---------------------------------------------------------------- MMA issuer: the whole warp runs the control
+    // flow (uniform), one elected lane issues each batch of MMAs and its commit
+    constexpr uint32_t IDESC_C = tc::idesc_bf16(128, 64, true);    // dC: B = dQ stored [r][64]
+    constexpr uint32_t IDESC_A = tc::idesc_bf16(128, R, false);    // dA: B stored [r output columns][k]
+    constexpr uint32_t HI_A = tc::desc_hi_k_major(Cfg::A_ROW), HI_K = tc::desc_hi_k_major(128), HI_N = tc::desc_hi_n_major_128();
+    grid_dependency_wait();
+    ok = wait_uniform(bar_res, 0);
+    const uint32_t res_lo = tc::desc_lo_k_major(res_base);   // leading-offset field of the contraction-major form
+    const uint32_t ring_lo = tc::desc_lo_k_major(ring);
+    constexpr uint32_t N_MAJOR_LBO = ((1024u >> 4) - 1u) << 16;   // added to a contraction-major low word
+    auto item_words = [&](int i, uint32_t& st_lo, uint32_t& hb_lo) {
+      const int idx = it0 + i, tile = idx / gh;
+      st_lo = ring_lo + (uint32_t)((i % S) * (Cfg::STAGE >> 4));
+      hb_lo = res_lo + (uint32_t)((idx - tile * gh) * (Cfg::HEAD_BYTES >> 4));
+    };
+    // products that need only the raw relation rows: dC = A dQ, dA = A S'
+    auto ready_a = [&](int i) {
+      return mbar_test(bar_full + 8 * (i % S), (i / S) & 1) &&
+             (i < 2 || mbar_test(bar_free + 8 * (i & 1), ((i >> 1) - 1) & 1));
+    };
+    auto phase_a = [&](int i) {
+      const int slot = i & 1;
+      tc::fence_after_sync();
+      uint32_t st_lo, hb_lo;
+      item_words(i, st_lo, hb_lo);
+      const uint32_t a_lo = st_lo + (32768 >> 4), tb = tmem + slot * Cfg::SLOT_COLS;
+      const uint32_t qh = hb_lo + ((2 * Cfg::W_BYTES) >> 4) + N_MAJOR_LBO, ql = qh + (Cfg::W_BYTES >> 4);
+      const uint32_t sh = hb_lo + ((4 * Cfg::W_BYTES) >> 4), sl = sh + (Cfg::S_BYTES >> 4);
+      if (tc::elect_one()) {
+#pragma unroll
+        for (int word = 0; word < 2; ++word) {
+#pragma unroll
+          for (int ks = 0; ks < R / 16; ++ks)
+            tc::mma_ss_raw<HI_A, HI_N, IDESC_C>(tb + Cfg::COL_DC, a_lo + ks * 2, (word == 0 ? ql : qh) + ks * 128,
+                                                (word | ks) != 0);
+        }
+#pragma unroll
+        for (int word = 0; word < 2; ++word) {
+#pragma unroll
+          for (int ks = 0; ks < R / 16; ++ks)
+            tc::mma_ss_raw<HI_A, HI_A, IDESC_A>(tb + Cfg::COL_DA, a_lo + ks * 2, (word == 0 ? sl : sh) + ks * 2,
+                                                (word | ks) != 0);
+        }
+        tc::mma_commit_raw(bar_m1 + 8 * slot);
+      }
+      __syncwarp();
+    };
+    // products with the (rotated) content and gradient rows: dA += rot(dY) W^T + rot(C) dQ^T
+    auto ready_b = [&](int i) { return !ROT || mbar_test(bar_xf + 8 * (i & 1), (i >> 1) & 1); };
+    auto phase_b = [&](int i) {
+      const int slot = i & 1;
+      tc::fence_after_sync();
+      uint32_t st_lo, hb_lo;
+      item_words(i, st_lo, hb_lo);
+      const uint32_t tb = tmem + slot * Cfg::SLOT_COLS;
+      const uint32_t wh = hb_lo, wl = wh + (Cfg::W_BYTES >> 4), qh = wl + (Cfg::W_BYTES >> 4), ql = qh + (Cfg::W_BYTES >> 4);
+      if (tc::elect_one()) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          if (ROT) {
+            tc::mma_ts_raw<HI_K, IDESC_A>(tb + Cfg::COL_DA, tb + Cfg::COL_YL + ks * 8, wh + ks * 2, 1);
+            tc::mma_ts_raw<HI_K, IDESC_A>(tb + Cfg::COL_DA, tb + Cfg::COL_YH + ks * 8, wl + ks * 2, 1);
+            tc::mma_ts_raw<HI_K, IDESC_A>(tb + Cfg::COL_DA, tb + Cfg::COL_YH + ks * 8, wh + ks * 2, 1);
+            tc::mma_ts_raw<HI_K, IDESC_A>(tb + Cfg::COL_DA, tb + Cfg::COL_CL + ks * 8, qh + ks * 2, 1);
+            tc::mma_ts_raw<HI_K, IDESC_A>(tb + Cfg::COL_DA, tb + Cfg::COL_CH + ks * 8, ql + ks * 2, 1);
+            tc::mma_ts_raw<HI_K, IDESC_A>(tb + Cfg::COL_DA, tb + Cfg::COL_CH + ks * 8, qh + ks * 2, 1);
+          } else {
+            const uint32_t y_lo = st_lo + (16384 >> 4) + ks * 2, c_lo = st_lo + ks * 2;
+            tc::mma_ss_raw<HI_K, HI_K, IDESC_A>(tb + Cfg::COL_DA, y_lo, wl + ks * 2, 1);
+            tc::mma_ss_raw<HI_K, HI_K, IDESC_A>(tb + Cfg::COL_DA, y_lo, wh + ks * 2, 1);
+            tc::mma_ss_raw<HI_K, HI_K, IDESC_A>(tb + Cfg::COL_DA, c_lo, ql + ks * 2, 1);
+            tc::mma_ss_raw<HI_K, HI_K, IDESC_A>(tb + Cfg::COL_DA, c_lo, qh + ks * 2, 1);
+          }
+        }
+        tc::mma_commit_raw(bar_m2 + 8 * slot);
+      }
+      __syncwarp();
+    };
+    // Event loop: the first phase of the next item and the second phase of the oldest open item are issued
+    // in whichever order their inputs become ready (an item's second phase follows its first; both advance
+    // in item order).  Waiting for them in a fixed order made the two compute groups take turns.  The loop is
+    // bounded like every other wait: after kWaitLimit rounds without progress it gives up.
+    int next_a = 0, next_b = 0, idle = 0;
+    while (ok && next_b < n_items) {
+      bool progressed = false;
+      if (next_a < n_items && next_a < next_b + 2 && __all_sync(0xffffffffu, ready_a(next_a))) {
+        phase_a(next_a++);
+        progressed = true;
+      }
+      if (next_b < next_a && __all_sync(0xffffffffu, ready_b(next_b))) {
+        phase_b(next_b++);
+        progressed = true;
+      }
+      idle = progressed ? 0 : idle + 1;
+      if (idle > kWaitLimit) ok = false;
+    }
+    if (!ok && lane == 0) atomicExch(p.error, kErrBarrierTimeout);
   } else {
-    // ---------------------------------------------------------------- compute warps: one token row per thread
-    const int g = warp >> 2, q = warp & 3, row = q * 32 + lane;
+    // ---------------------------------------------------------------- compute warps: eight per slot; a thread owns
+    // one token row (the lanes its warp may touch in tensor memory: 32 * (warp % 4) ...) and half of its channels
+    const int g = warp >> 3, q = warp & 3, half = (warp >> 2) & 1, row = q * 32 + lane;
     const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16) + g * Cfg::SLOT_COLS;
     grid_dependency_wait();
     const float n = p.counts ? p.counts[b] : (float)p.tokens;
     const float inv_s = inv_sqrt_rn(n);
     const long tab_row_b = p.rotary_rows > 1 ? (long)b * p.tokens : 0;
     const int width = p.heads * (R + 64);
-    float cs[32], sn[32];
-    int tab_tile = -1;
+    float cs[16], sn[16];
+    int tab_next = 0;   // ordinal of the next tile whose table rows this thread has not yet passed
+    // Copy this thread's 16 cos / sin entries of tile ordinal k from the shared-memory buffer; tiles in between
+    // (this group had no item in them) are passed without copying, so that the buffer can be refilled.
+    auto take_tables = [&](int k) {
+      bool good = true;
+      while (tab_next <= k && good) {
+        good = wait_uniform(bar_tab_full, tab_next & 1);
+        if (good && tab_next == k) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint32_t off = row * 128 + (((half * 4 + v) ^ (row & 7)) << 4);
+            const float4 cv = ld_shared_f4(tab_buf + off), sv = ld_shared_f4(tab_buf + 16384 + off);
+            cs[4 * v] = cv.x; cs[4 * v + 1] = cv.y; cs[4 * v + 2] = cv.z; cs[4 * v + 3] = cv.w;
+            sn[4 * v] = sv.x; sn[4 * v + 1] = sv.y; sn[4 * v + 2] = sv.z; sn[4 * v + 3] = sv.w;
+          }
+        }
+        if (good) mbar_arrive(bar_tab_free);
+        ++tab_next;
+      }
+      return good;
+    };
 
     for (int i = g; i < n_items && ok; i += 2) {
       const int stage = i % S;
@@ -310,29 +377,22 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const uint32_t c_tile = st, y_tile = st + 16384, a_tile = st + 32768;
       const int tok = tile * kTcTile + row;
       const bool valid = tok < p.tokens;
-      if (ROT && tile != tab_tile) {
-        const float4* c4 = reinterpret_cast<const float4*>(p.cos + (tab_row_b + tok) * 32);
-        const float4* s4 = reinterpret_cast<const float4*>(p.sin + (tab_row_b + tok) * 32);
-#pragma unroll
-        for (int v = 0; v < 8; ++v) {
-          float4 cv = make_float4(1.f, 1.f, 1.f, 1.f), sv = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (valid) {
-            cv = __ldg(c4 + v);
-            sv = __ldg(s4 + v);
-          }
-          cs[4 * v] = cv.x; cs[4 * v + 1] = cv.y; cs[4 * v + 2] = cv.z; cs[4 * v + 3] = cv.w;
-          sn[4 * v] = sv.x; sn[4 * v + 1] = sv.y; sn[4 * v + 2] = sv.z; sn[4 * v + 3] = sv.w;
-        }
-        tab_tile = tile;
-      }
       const float eta = __ldg(p.eta + h);
       const uint32_t par = (i >> 1) & 1;
 
+      if (ROT && tile - tile0 >= tab_next) {
+        // rows past the end of the sample come back as zeros from the TMA load: rotation by cos = sin = 0 of
+        // zero content, harmless
+        ok = take_tables(tile - tile0);
+        if (!ok) break;
+      }
       ok = wait_uniform(bar_full + 8 * stage, (i / S) & 1);
       if (!ok) break;
       if (ROT) {
-        rotate_row_to_tmem(y_tile, row, cs, sn, lane_base + Cfg::COL_YH, lane_base + Cfg::COL_YL);
-        rotate_row_to_tmem(c_tile, row, cs, sn, lane_base + Cfg::COL_CH, lane_base + Cfg::COL_CL);
+        rotate_half_row_to_tmem(y_tile, row, half, cs, sn, lane_base + Cfg::COL_YH + half * 16,
+                                lane_base + Cfg::COL_YL + half * 16);
+        rotate_half_row_to_tmem(c_tile, row, half, cs, sn, lane_base + Cfg::COL_CH + half * 16,
+                                lane_base + Cfg::COL_CL + half * 16);
         tc::wait_st();
         tc::fence_before_sync();
         mbar_arrive(bar_xf + 8 * g);
@@ -344,8 +404,7 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       if (!ok) break;
       tc::fence_after_sync();
       float* dbg = (p.debug && valid) ? p.debug + ((size_t)b * p.tokens + tok) * width : nullptr;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         uint32_t acc[32];
         tc::tmem_ld16(lane_base + Cfg::COL_DC + half * 32, *reinterpret_cast<uint32_t(*)[16]>(&acc[0]));
         tc::tmem_ld16(lane_base + Cfg::COL_DC + half * 32 + 16, *reinterpret_cast<uint32_t(*)[16]>(&acc[16]));
@@ -359,46 +418,53 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           uint32_t ow[4];
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const int j = half * 16 + c * 4 + k;
-            float2 corr = make_float2(__uint_as_float(acc[2 * (c * 4 + k)]), __uint_as_float(acc[2 * (c * 4 + k) + 1]));
+            const int j = c * 4 + k;
+            float2 corr = make_float2(__uint_as_float(acc[2 * j]), __uint_as_float(acc[2 * j + 1]));
             if (ROT) corr = rot_pair(corr.x, corr.y, cs[j], -sn[j]);
             const float2 yy = bf2_to_f2(yw[k]);
             const float o0 = fmaf(corr.x, inv_s, eta * yy.x), o1 = fmaf(corr.y, inv_s, eta * yy.y);
             ow[k] = f2_to_bf2(o0, o1);
             if (dbg) {
-              dbg[p.heads * R + h * 64 + 2 * j] = o0;
-              dbg[p.heads * R + h * 64 + 2 * j + 1] = o1;
+              dbg[p.heads * R + h * 64 + half * 32 + 2 * j] = o0;
+              dbg[p.heads * R + h * 64 + half * 32 + 2 * j + 1] = o1;
             }
           }
           st_shared_v4(addr, make_uint4(ow[0], ow[1], ow[2], ow[3]));
         }
       }
 
-      // dA = s * (A S' + rot(dY) W^T + rot(C) dQ^T), written over the relation row
+      // dA = s * (A S' + rot(dY) W^T + rot(C) dQ^T), written over the relation row: this thread's R/2 columns
       if (ROT) {
         ok = wait_uniform(bar_m2 + 8 * g, par);
         if (!ok) break;
         tc::fence_after_sync();
       }
       {
-        uint32_t acc[R];
+        constexpr int COLS = R / 2;   // 8, 16 or 32
+        uint32_t acc[COLS];
+        if constexpr (COLS >= 16) {
 #pragma unroll
-        for (int c0 = 0; c0 < R; c0 += 16)
-          tc::tmem_ld16(lane_base + Cfg::COL_DA + c0, *reinterpret_cast<uint32_t(*)[16]>(&acc[c0]));
+          for (int c0 = 0; c0 < COLS; c0 += 16)
+            tc::tmem_ld16(lane_base + Cfg::COL_DA + half * COLS + c0, *reinterpret_cast<uint32_t(*)[16]>(&acc[c0]));
+        } else {
+          tc::tmem_ld8(lane_base + Cfg::COL_DA + half * COLS, *reinterpret_cast<uint32_t(*)[8]>(&acc[0]));
+        }
         tc::wait_ld();
 #pragma unroll
-        for (int c = 0; c < R / 8; ++c) {
+        for (int c = 0; c < COLS / 8; ++c) {
+          const int src = 8 * c;
           uint32_t ow[4];
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const float o0 = __uint_as_float(acc[8 * c + 2 * k]) * inv_s, o1 = __uint_as_float(acc[8 * c + 2 * k + 1]) * inv_s;
+            const float o0 = __uint_as_float(acc[src + 2 * k]) * inv_s, o1 = __uint_as_float(acc[src + 2 * k + 1]) * inv_s;
             ow[k] = f2_to_bf2(o0, o1);
             if (dbg) {
-              dbg[h * R + 8 * c + 2 * k] = o0;
-              dbg[h * R + 8 * c + 2 * k + 1] = o1;
+              dbg[h * R + half * COLS + 8 * c + 2 * k] = o0;
+              dbg[h * R + half * COLS + 8 * c + 2 * k + 1] = o1;
             }
           }
-          st_shared_v4(a_tile + swz_rows<Cfg::A_ROW>(row * Cfg::A_ROW + c * 16), make_uint4(ow[0], ow[1], ow[2], ow[3]));
+          st_shared_v4(a_tile + swz_rows<Cfg::A_ROW>(row * Cfg::A_ROW + (half * (COLS / 8) + c) * 16),
+                       make_uint4(ow[0], ow[1], ow[2], ow[3]));
         }
       }
       tc::fence_before_sync();
@@ -406,13 +472,19 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       fence_async_shared();
       mbar_arrive(bar_out + 8 * stage);
     }
+    // tiles after this group's last item: pass them, the other group may still need the buffer refilled
+    while (ROT && ok && tab_next < n_tiles) {
+      ok = wait_uniform(bar_tab_full, tab_next & 1);
+      if (ok) mbar_arrive(bar_tab_free);
+      ++tab_next;
+    }
     if (!ok && lane == 0) atomicExch(p.error, kErrBarrierTimeout);
   }
 
   // all roles meet here; the tensor memory goes back before the CTA exits
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 9) tc::tmem_free(tmem, 512);
+  if (warp == kMmaWarp) tc::tmem_free(tmem, 512);
 }
 
 template <int R>
@@ -459,6 +531,15 @@ static int launch_token_bwd_tc_r(const ms_shape& s, const Plan& plan, const void
       return MS_ERR_LAUNCH;
   }
 
+  CUtensorMap map_cos = map_a, map_sin = map_a;   // placeholders when there is no rotation
+  if (s.rotary_rows > 0) {
+    const uint64_t dims[3] = {32, (uint64_t)s.tokens, (uint64_t)s.rotary_rows};
+    const uint64_t str[2] = {128, (uint64_t)s.tokens * 128};
+    const uint32_t box[3] = {32, kTcTile, 1};
+    if (encode_tensor_map(&map_cos, const_cast<float*>(cos), 4, 3, dims, str, box, Swizzle::B128)) return MS_ERR_LAUNCH;
+    if (encode_tensor_map(&map_sin, const_cast<float*>(sin), 4, 3, dims, str, box, Swizzle::B128)) return MS_ERR_LAUNCH;
+  }
+
   TokenBwdTcParams p;
   p.cos = cos; p.sin = sin; p.counts = counts; p.eta = t.eta; p.debug = debug;
   p.error = device_error_word();
@@ -481,17 +562,17 @@ static int launch_token_bwd_tc_r(const ms_shape& s, const Plan& plan, const void
   p.work_ctas = (int)ctas;
   p.core_ctas = core_ctas > 0 ? core_ctas : 1;
   dim3 grid((unsigned)ctas + core_ctas, s.batch, groups);
-  int smem_bytes = 1024 + group * Cfg::HEAD_BYTES + Cfg::STAGES * Cfg::STAGE + Cfg::BAR_BYTES;
+  int smem_bytes = 1024 + group * Cfg::HEAD_BYTES + Cfg::STAGES * Cfg::STAGE + Cfg::TABLE_BYTES + Cfg::BAR_BYTES;
   const int core_bytes = (int)core_backward_smem_bytes(R) + 1024;
   if (core && smem_bytes < core_bytes) smem_bytes = core_bytes;
   if (s.rotary_rows > 0) {
     auto kern = token_backward_tc_kernel<R, true>;
     if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
-    launch_kernel(kern, grid, dim3(kTcThreads), smem_bytes, st, map_a, map_c, map_y, map_w, map_q, map_s, map_oa, map_oc, p);
+    launch_kernel(kern, grid, dim3(kTcThreads), smem_bytes, st, map_a, map_c, map_y, map_w, map_q, map_s, map_oa, map_oc, map_cos, map_sin, p);
   } else {
     auto kern = token_backward_tc_kernel<R, false>;
     if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
-    launch_kernel(kern, grid, dim3(kTcThreads), smem_bytes, st, map_a, map_c, map_y, map_w, map_q, map_s, map_oa, map_oc, p);
+    launch_kernel(kern, grid, dim3(kTcThreads), smem_bytes, st, map_a, map_c, map_y, map_w, map_q, map_s, map_oa, map_oc, map_cos, map_sin, p);
   }
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
