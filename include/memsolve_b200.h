@@ -189,6 +189,11 @@ int ms_compact_forward(const ms_shape* shape, const float* counts, const void* w
 int ms_readout(const ms_shape* shape, const void* projected, const float* cos, const float* sin,
                const float* counts, const ms_tape* tape, void* mixed, void* stream);
 
+/* ms_readout that also writes its results before the BF16 rounding (mixed_f32: FP32 [B, N, H*d]); test
+ * instrument like ms_token_backward_debug below, same shape envelope and status codes. */
+int ms_readout_debug(const ms_shape* shape, const void* projected, const float* cos, const float* sin,
+                     const float* counts, const ms_tape* tape, void* mixed, float* mixed_f32, void* stream);
+
 /* Whole forward on one rank: core + stats + compact + readout (no collective). */
 int ms_mix_forward(const ms_shape* shape, const void* projected, const float* base_raw,
                    const float* eta_raw, const float* cos, const float* sin, const float* counts,

@@ -74,6 +74,7 @@ _SIGNATURES = {
                                            ctypes.POINTER(_Tape), _P, _P, ctypes.c_float, _P, _P, _P, _P, _P]),
     "ms_token_backward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, ctypes.POINTER(_Tape),
                                          _P, _P, _P, _P]),
+    "ms_readout_debug": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, ctypes.POINTER(_Tape), _P, _P, _P]),
     "ms_token_backward_debug": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, ctypes.POINTER(_Tape),
                                                _P, _P, _P, _P, _P]),
     "ms_stats_forward_core": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t,

@@ -35,6 +35,8 @@ int launch_readout(const ms_shape&, const Plan&, const void* projected, const fl
 int launch_token_backward(const ms_shape&, const Plan&, const void* projected, const void* dy, const float* cos,
                           const float* sin, const float* counts, const ms_tape&, const void* gram_grad,
                           const void* cross_grad, void* dprojected, const CoreAdjoint* core, cudaStream_t);
+int launch_readout_tc(const ms_shape&, const Plan&, const void* projected, const float* cos, const float* sin,
+                      const float* counts, const ms_tape&, void* mixed, float* debug, cudaStream_t);
 int launch_token_backward_tc(const ms_shape&, const Plan&, const void* projected, const void* dy, const float* cos,
                              const float* sin, const float* counts, const ms_tape&, const void* gram_grad,
                              const void* cross_grad, void* dprojected, const CoreAdjoint* core, float* debug,
@@ -409,6 +411,19 @@ int ms_readout(const ms_shape* shape, const void* projected, const float* cos, c
   Plan plan = make_plan(*shape);
   plan.aligned = plan.aligned && is16(projected) && is16(mixed);
   return launch_readout(*shape, plan, projected, cos, sin, counts, *tape, mixed, static_cast<cudaStream_t>(stream));
+}
+
+int ms_readout_debug(const ms_shape* shape, const void* projected, const float* cos, const float* sin,
+                     const float* counts, const ms_tape* tape, void* mixed, float* mixed_f32, void* stream) {
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  if (!projected || !mixed || !mixed_f32 || !tape || !tape->eta || !tape->coeff) return MS_ERR_INVALID_ARGUMENT;
+  if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
+  Plan plan = make_plan(*shape);
+  plan.aligned = plan.aligned && is16(projected) && is16(mixed) && (!shape->rotary_rows || (is16(cos) && is16(sin)));
+  const int r = launch_readout_tc(*shape, plan, projected, cos, sin, counts, *tape, mixed, mixed_f32,
+                                  static_cast<cudaStream_t>(stream));
+  return r == -1 ? MS_ERR_DEBUG_SHAPE : r;
 }
 
 int ms_mix_forward(const ms_shape* shape, const void* projected, const float* base_raw, const float* eta_raw,

@@ -453,6 +453,9 @@ int launch_token_backward_tc(const ms_shape& s, const Plan& plan, const void* pr
                              const void* gram_grad, const void* cross_grad, void* dprojected,
                              const CoreAdjoint* core, float* debug, cudaStream_t st);
 
+int launch_readout_tc(const ms_shape& s, const Plan& plan, const void* projected, const float* cos, const float* sin,
+                      const float* counts, const ms_tape& t, void* mixed, float* debug, cudaStream_t st);
+
 static TokenParams token_params(const ms_shape& s, const Plan& plan, const void* projected, const void* dy,
                                 const float* cos, const float* sin, const float* counts, const ms_tape& t,
                                 const void* gram_grad, const void* cross_grad, void* out) {
@@ -475,6 +478,10 @@ static TokenParams token_params(const ms_shape& s, const Plan& plan, const void*
 
 int launch_readout(const ms_shape& s, const Plan& plan, const void* projected, const float* cos,
                    const float* sin, const float* counts, const ms_tape& t, void* mixed, cudaStream_t st) {
+  if (plan.tc) {
+    const int r = launch_readout_tc(s, plan, projected, cos, sin, counts, t, mixed, nullptr, st);
+    if (r != -1) return r;
+  }
   if (plan.tma) {
     const int r = launch_readout_tma(s, plan, projected, cos, sin, counts, t, mixed, st);
     if (r != -1) return r;

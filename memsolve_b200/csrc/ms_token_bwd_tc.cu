@@ -11,9 +11,11 @@
 // Work item = (128-token tile, head).  A CTA serves one sample and one group of heads whose compact
 // matrices stay in shared memory, and walks over its items with a ring of shared-memory stages:
 //
-//   warp 16 (one thread)  TMA: loads the relation, content and upstream-gradient boxes of an item into a
-//                         stage; stores dA and dC, which the compute warps wrote over the relation and
-//                         gradient boxes, back to `dprojected`.
+//   warp 16 (one thread)  TMA: loads the relation and upstream-gradient boxes of an item into a stage;
+//                         stores dA and dC, which the compute warps wrote over those boxes, back to
+//                         `dprojected`.
+//   warp 19 (one thread)  TMA: content boxes, in a ring of their own (a box is free again as soon as its rows
+//                         have been rotated into tensor memory, long before the item's outputs are stored).
 //   warp 17               issues the tcgen05 MMAs (warp-uniform control flow, one elected lane issues each
 //                         batch); the accumulators of an item (dC: 128 x 64, dA: 128 x r, FP32) live in
 //                         tensor memory, two items in flight (slots).
@@ -35,7 +37,7 @@
 namespace ms {
 
 constexpr int kTcComputeWarps = 16;                  // two groups of eight
-constexpr int kTcThreads = (kTcComputeWarps + 3) * 32;
+constexpr int kTcThreads = (kTcComputeWarps + 4) * 32;
 constexpr int kTcGroupThreads = 256;
 constexpr int kTcTile = 128;       // tokens per item
 constexpr int kTcMinTokens = 512;  // shorter samples leave most of a tile empty: mma.sync kernels
@@ -44,15 +46,18 @@ template <int R>
 struct TokenBwdTcCfg {
   static constexpr int A_ROW = R * 2;                   // bytes of one relation row
   static constexpr int A_TILE = kTcTile * A_ROW;
-  static constexpr int STAGE = 32768 + A_TILE;          // content, gradient, relation boxes
-  static constexpr int STAGES = R == 16 ? 4 : 3;
+  static constexpr int STAGE = 16384 + A_TILE;          // gradient and relation boxes (outputs are written over them)
+  static constexpr int STAGES = R == 64 ? 3 : 4;
+  static constexpr int C_STAGES = 3;                    // content boxes have a ring of their own: they are free
+  static constexpr int C_STAGE = 16384;                 // again as soon as the rows have been rotated
   static constexpr int TABLE_BYTES = 32768;             // cos and sin rows of one token tile
   static constexpr int W_BYTES = R * 128;
   static constexpr int S_BYTES = R * R * 2;
   static constexpr int HEAD_BYTES = 4 * W_BYTES + 2 * S_BYTES;   // W hi/lo, dQ hi/lo, S' hi/lo
-  static constexpr int BAR_BYTES = (2 * STAGES + 11) * 8 + 16;
+  static constexpr int BAR_BYTES = (2 * STAGES + 2 * C_STAGES + 11) * 8 + 16;
+  static constexpr int RING_BYTES = STAGES * STAGE + C_STAGES * C_STAGE;
   static constexpr int MAX_SMEM = 227 * 1024;
-  static constexpr int RESIDENT_BUDGET = MAX_SMEM - 1024 - STAGES * STAGE - TABLE_BYTES - BAR_BYTES;
+  static constexpr int RESIDENT_BUDGET = MAX_SMEM - 1024 - RING_BYTES - TABLE_BYTES - BAR_BYTES;
   // tensor-memory columns of one slot
   static constexpr int COL_DC = 0, COL_DA = 64, COL_YH = 128, COL_YL = 160, COL_CH = 192, COL_CL = 224, SLOT_COLS = 256;
   static_assert(64 + R <= 128, "accumulators of a slot");
@@ -108,7 +113,7 @@ __device__ __forceinline__ void rotate_half_row_to_tmem(uint32_t tile, int row, 
   tc::tmem_st16(t_lo, lo);
 }
 
-template <int R, bool ROT>
+template <int R, bool ROT, bool DEBUG>
 __global__ void __launch_bounds__(kTcThreads, 1)
 token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_c,
                          const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_w,
@@ -118,7 +123,9 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                          const TokenBwdTcParams p) {
   using Cfg = TokenBwdTcCfg<R>;
   constexpr int S = Cfg::STAGES;
-  constexpr int kProducerWarp = kTcComputeWarps, kMmaWarp = kTcComputeWarps + 1, kTableWarp = kTcComputeWarps + 2;
+  constexpr int SC = Cfg::C_STAGES;
+  constexpr int kProducerWarp = kTcComputeWarps, kMmaWarp = kTcComputeWarps + 1, kTableWarp = kTcComputeWarps + 2,
+                kContentWarp = kTcComputeWarps + 3;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -142,10 +149,13 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int gh = min(p.group_heads, p.heads - h0);
   const uint32_t res_base = smem;
   const uint32_t ring = smem + p.group_heads * Cfg::HEAD_BYTES;
-  const uint32_t tab_buf = ring + S * Cfg::STAGE;
+  const uint32_t c_ring = ring + S * Cfg::STAGE;
+  const uint32_t tab_buf = c_ring + SC * Cfg::C_STAGE;
   const uint32_t bar_full = tab_buf + Cfg::TABLE_BYTES;
   const uint32_t bar_out = bar_full + 8 * S;
-  const uint32_t bar_xf = bar_out + 8 * S;
+  const uint32_t bar_cfull = bar_out + 8 * S;
+  const uint32_t bar_cfree = bar_cfull + 8 * SC;
+  const uint32_t bar_xf = bar_cfree + 8 * SC;
   const uint32_t bar_m1 = bar_xf + 16, bar_m2 = bar_m1 + 16, bar_free = bar_m2 + 16, bar_res = bar_free + 16;
   const uint32_t bar_tab_full = bar_res + 8, bar_tab_free = bar_tab_full + 8;
   const uint32_t tslot = bar_tab_free + 8;
@@ -154,6 +164,10 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     for (int i = 0; i < S; ++i) {
       mbar_init(bar_full + 8 * i, 1);
       mbar_init(bar_out + 8 * i, kTcGroupThreads);
+    }
+    for (int i = 0; i < SC; ++i) {
+      mbar_init(bar_cfull + 8 * i, 1);
+      mbar_init(bar_cfree + 8 * i, kTcGroupThreads);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_xf + 8 * i, kTcGroupThreads);
@@ -189,9 +203,8 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const int idx = it0 + i, tile = idx / gh, h = h0 + (idx - tile * gh);
         const uint32_t st = ring + (i % S) * Cfg::STAGE, bar = bar_full + 8 * (i % S);
         mbar_expect_tx(bar, Cfg::STAGE);
-        tma_load_3d(st + 32768, &map_a, h * R, tile * kTcTile, b, bar);
-        tma_load_3d(st + 16384, &map_y, h * 64, tile * kTcTile, b, bar);
-        tma_load_3d(st, &map_c, p.heads * R + h * 64, tile * kTcTile, b, bar);
+        tma_load_3d(st + 16384, &map_a, h * R, tile * kTcTile, b, bar);
+        tma_load_3d(st, &map_y, h * 64, tile * kTcTile, b, bar);
       };
       // `projected` and the upstream gradient were complete before the kernel ahead of this one started, so
       // a chained launch may fetch them while that kernel (which produces dQ and S') is still draining
@@ -213,8 +226,8 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (!ok) break;
         const int idx = it0 + i, tile = idx / gh, h = h0 + (idx - tile * gh);
         const uint32_t st = ring + (i % S) * Cfg::STAGE;
-        tma_store_3d(&map_oc, p.heads * R + h * 64, tile * kTcTile, b, st + 16384);
-        tma_store_3d(&map_oa, h * R, tile * kTcTile, b, st + 32768);
+        tma_store_3d(&map_oc, p.heads * R + h * 64, tile * kTcTile, b, st);
+        tma_store_3d(&map_oa, h * R, tile * kTcTile, b, st + 16384);
         tma_store_commit();
         if (i + S < n_items) {
           tma_store_wait_read<0>();   // the stage is read by the stores just issued
@@ -222,6 +235,20 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         }
       }
       tma_store_wait_all<0>();
+      if (!ok) atomicExch(p.error, kErrBarrierTimeout);
+    }
+  } else if (warp == kContentWarp) {
+    // ---------------------------------------------------------------- content boxes, a ring of their own
+    if (lane == 0) {
+      for (int j = 0; j < n_items; ++j) {
+        if (j >= SC) {
+          ok = mbar_wait(bar_cfree + 8 * (j % SC), ((j / SC) - 1) & 1);   // item j - SC no longer reads the box
+          if (!ok) break;
+        }
+        const int idx = it0 + j, tile = idx / gh, h = h0 + (idx - tile * gh);
+        mbar_expect_tx(bar_cfull + 8 * (j % SC), Cfg::C_STAGE);
+        tma_load_3d(c_ring + (j % SC) * Cfg::C_STAGE, &map_c, p.heads * R + h * 64, tile * kTcTile, b, bar_cfull + 8 * (j % SC));
+      }
       if (!ok) atomicExch(p.error, kErrBarrierTimeout);
     }
   } else if (warp == kTableWarp) {
@@ -249,6 +276,7 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     ok = wait_uniform(bar_res, 0);
     const uint32_t res_lo = tc::desc_lo_k_major(res_base);   // leading-offset field of the contraction-major form
     const uint32_t ring_lo = tc::desc_lo_k_major(ring);
+    const uint32_t cring_lo = tc::desc_lo_k_major(c_ring);
     constexpr uint32_t N_MAJOR_LBO = ((1024u >> 4) - 1u) << 16;   // added to a contraction-major low word
     auto item_words = [&](int i, uint32_t& st_lo, uint32_t& hb_lo) {
       const int idx = it0 + i, tile = idx / gh;
@@ -265,7 +293,7 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tc::fence_after_sync();
       uint32_t st_lo, hb_lo;
       item_words(i, st_lo, hb_lo);
-      const uint32_t a_lo = st_lo + (32768 >> 4), tb = tmem + slot * Cfg::SLOT_COLS;
+      const uint32_t a_lo = st_lo + (16384 >> 4), tb = tmem + slot * Cfg::SLOT_COLS;
       const uint32_t qh = hb_lo + ((2 * Cfg::W_BYTES) >> 4) + N_MAJOR_LBO, ql = qh + (Cfg::W_BYTES >> 4);
       const uint32_t sh = hb_lo + ((4 * Cfg::W_BYTES) >> 4), sl = sh + (Cfg::S_BYTES >> 4);
       if (tc::elect_one()) {
@@ -288,7 +316,9 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       __syncwarp();
     };
     // products with the (rotated) content and gradient rows: dA += rot(dY) W^T + rot(C) dQ^T
-    auto ready_b = [&](int i) { return !ROT || mbar_test(bar_xf + 8 * (i & 1), (i >> 1) & 1); };
+    auto ready_b = [&](int i) {
+      return ROT ? mbar_test(bar_xf + 8 * (i & 1), (i >> 1) & 1) : mbar_test(bar_cfull + 8 * (i % SC), (i / SC) & 1);
+    };
     auto phase_b = [&](int i) {
       const int slot = i & 1;
       tc::fence_after_sync();
@@ -307,7 +337,7 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             tc::mma_ts_raw<HI_K, IDESC_A>(tb + Cfg::COL_DA, tb + Cfg::COL_CH + ks * 8, ql + ks * 2, 1);
             tc::mma_ts_raw<HI_K, IDESC_A>(tb + Cfg::COL_DA, tb + Cfg::COL_CH + ks * 8, qh + ks * 2, 1);
           } else {
-            const uint32_t y_lo = st_lo + (16384 >> 4) + ks * 2, c_lo = st_lo + ks * 2;
+            const uint32_t y_lo = st_lo + ks * 2, c_lo = cring_lo + (uint32_t)((i % SC) * (Cfg::C_STAGE >> 4)) + ks * 2;
             tc::mma_ss_raw<HI_K, HI_K, IDESC_A>(tb + Cfg::COL_DA, y_lo, wl + ks * 2, 1);
             tc::mma_ss_raw<HI_K, HI_K, IDESC_A>(tb + Cfg::COL_DA, y_lo, wh + ks * 2, 1);
             tc::mma_ss_raw<HI_K, HI_K, IDESC_A>(tb + Cfg::COL_DA, c_lo, ql + ks * 2, 1);
@@ -333,8 +363,12 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         phase_b(next_b++);
         progressed = true;
       }
-      idle = progressed ? 0 : idle + 1;
-      if (idle > kWaitLimit) ok = false;
+      if (progressed) {
+        idle = 0;
+      } else {
+        __nanosleep(40);   // leave the issue slots to the compute warps of this scheduler
+        if (++idle > kWaitLimit) ok = false;
+      }
     }
     if (!ok && lane == 0) atomicExch(p.error, kErrBarrierTimeout);
   } else {
@@ -374,7 +408,7 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int stage = i % S;
       const int idx = it0 + i, tile = idx / gh, h = h0 + (idx - tile * gh);
       const uint32_t st = ring + stage * Cfg::STAGE;
-      const uint32_t c_tile = st, y_tile = st + 16384, a_tile = st + 32768;
+      const uint32_t y_tile = st, a_tile = st + 16384, c_tile = c_ring + (i % SC) * Cfg::C_STAGE;
       const int tok = tile * kTcTile + row;
       const bool valid = tok < p.tokens;
       const float eta = __ldg(p.eta + h);
@@ -391,8 +425,11 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       if (ROT) {
         rotate_half_row_to_tmem(y_tile, row, half, cs, sn, lane_base + Cfg::COL_YH + half * 16,
                                 lane_base + Cfg::COL_YL + half * 16);
+        ok = wait_uniform(bar_cfull + 8 * (i % SC), (i / SC) & 1);
+        if (!ok) break;
         rotate_half_row_to_tmem(c_tile, row, half, cs, sn, lane_base + Cfg::COL_CH + half * 16,
                                 lane_base + Cfg::COL_CL + half * 16);
+        mbar_arrive(bar_cfree + 8 * (i % SC));   // the content box is in registers / tensor memory now
         tc::wait_st();
         tc::fence_before_sync();
         mbar_arrive(bar_xf + 8 * g);
@@ -403,7 +440,8 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       ok = wait_uniform((ROT ? bar_m1 : bar_m2) + 8 * g, par);
       if (!ok) break;
       tc::fence_after_sync();
-      float* dbg = (p.debug && valid) ? p.debug + ((size_t)b * p.tokens + tok) * width : nullptr;
+      if (!ROT) mbar_arrive(bar_cfree + 8 * (i % SC));   // the MMAs that read the content box have completed
+      float* dbg = (DEBUG && valid) ? p.debug + ((size_t)b * p.tokens + tok) * width : nullptr;
       {
         uint32_t acc[32];
         tc::tmem_ld16(lane_base + Cfg::COL_DC + half * 32, *reinterpret_cast<uint32_t(*)[16]>(&acc[0]));
@@ -424,7 +462,7 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const float2 yy = bf2_to_f2(yw[k]);
             const float o0 = fmaf(corr.x, inv_s, eta * yy.x), o1 = fmaf(corr.y, inv_s, eta * yy.y);
             ow[k] = f2_to_bf2(o0, o1);
-            if (dbg) {
+            if (DEBUG && dbg) {
               dbg[p.heads * R + h * 64 + half * 32 + 2 * j] = o0;
               dbg[p.heads * R + h * 64 + half * 32 + 2 * j + 1] = o1;
             }
@@ -458,7 +496,7 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           for (int k = 0; k < 4; ++k) {
             const float o0 = __uint_as_float(acc[src + 2 * k]) * inv_s, o1 = __uint_as_float(acc[src + 2 * k + 1]) * inv_s;
             ow[k] = f2_to_bf2(o0, o1);
-            if (dbg) {
+            if (DEBUG && dbg) {
               dbg[h * R + half * COLS + 8 * c + 2 * k] = o0;
               dbg[h * R + half * COLS + 8 * c + 2 * k + 1] = o1;
             }
@@ -562,18 +600,16 @@ static int launch_token_bwd_tc_r(const ms_shape& s, const Plan& plan, const void
   p.work_ctas = (int)ctas;
   p.core_ctas = core_ctas > 0 ? core_ctas : 1;
   dim3 grid((unsigned)ctas + core_ctas, s.batch, groups);
-  int smem_bytes = 1024 + group * Cfg::HEAD_BYTES + Cfg::STAGES * Cfg::STAGE + Cfg::TABLE_BYTES + Cfg::BAR_BYTES;
+  int smem_bytes = 1024 + group * Cfg::HEAD_BYTES + Cfg::RING_BYTES + Cfg::TABLE_BYTES + Cfg::BAR_BYTES;
   const int core_bytes = (int)core_backward_smem_bytes(R) + 1024;
   if (core && smem_bytes < core_bytes) smem_bytes = core_bytes;
-  if (s.rotary_rows > 0) {
-    auto kern = token_backward_tc_kernel<R, true>;
-    if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
-    launch_kernel(kern, grid, dim3(kTcThreads), smem_bytes, st, map_a, map_c, map_y, map_w, map_q, map_s, map_oa, map_oc, map_cos, map_sin, p);
-  } else {
-    auto kern = token_backward_tc_kernel<R, false>;
-    if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
-    launch_kernel(kern, grid, dim3(kTcThreads), smem_bytes, st, map_a, map_c, map_y, map_w, map_q, map_s, map_oa, map_oc, map_cos, map_sin, p);
-  }
+  void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap,
+               CUtensorMap, CUtensorMap, TokenBwdTcParams);
+  if (s.rotary_rows > 0) kern = debug ? token_backward_tc_kernel<R, true, true> : token_backward_tc_kernel<R, true, false>;
+  else kern = debug ? token_backward_tc_kernel<R, false, true> : token_backward_tc_kernel<R, false, false>;
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) return MS_ERR_LAUNCH;
+  launch_kernel(kern, grid, dim3(kTcThreads), smem_bytes, st, map_a, map_c, map_y, map_w, map_q, map_s, map_oa, map_oc,
+                map_cos, map_sin, p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
 

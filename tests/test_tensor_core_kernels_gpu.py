@@ -95,6 +95,38 @@ def test_token_backward_fp32_before_rounding(cuda_mod, rank, rot, length):
         assert rel_l2(again, out16) <= 4e-3   # short samples take the mma.sync kernel: same values to BF16 rounding
 
 
+@pytest.mark.parametrize("rank,rot,length,comp", [(32, True, 2300, False), (64, True, 1024, False), (16, False, 1500, False),
+                                                  (32, False, 300, True), (64, True, 777, True)])
+def test_readout_fp32_before_rounding(cuda_mod, rank, rot, length, comp):
+    """The readout kernel's own FP32 values (two-word coefficients, FP32 accumulation, inverse rotation and
+    eta*C in FP32) against the reference's frame formulation in FP64 on the identical BF16 projection:
+    <= 1e-4, the FP32 criterion; the BF16 tensor beside them is their rounding."""
+    lib = cuda_mod._LIB
+    heads, batch = 3, 2
+    proj, base, eta_raw, counts, cos, sin, dy = _random_case(720 + rank, batch, length, heads, rank, 64, rot=rot, comp=comp)
+    dp, db, de = proj.cuda(), base.cuda(), eta_raw.cuda()
+    dcos, dsin = _dev(cos), _dev(sin)
+    mixed, tape, dims = cuda_mod._mix_forward(dp, db, de, None, None, dcos, dsin)
+    shape = cuda_mod._Shape(*dims, 0)
+    tape_c = tape.as_struct()
+    ptr = cuda_mod._ptr
+    out16 = torch.empty_like(mixed)
+    out32 = torch.full(mixed.shape, float("nan"), device="cuda", dtype=torch.float32)
+    assert lib.ms_readout_debug(ctypes.byref(shape), dp.data_ptr(), ptr(dcos), ptr(dsin), None, ctypes.byref(tape_c),
+                                out16.data_ptr(), out32.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert lib.ms_device_error() == 0
+    want = O.fast_mix_frame(proj, base, eta_raw, None, cos, sin)
+    err32, err16 = rel_l2(out32, want), rel_l2(out16, want)
+    print(f"readout r{rank} rot={rot} N{length} comp={comp}: FP32 {err32:.2e}, BF16 {err16:.2e}")
+    assert err32 <= 1e-4 and err16 <= 5e-3
+    assert torch.equal(out32.bfloat16(), out16)
+    if length >= 512:
+        assert torch.equal(out16, mixed)
+    else:
+        assert rel_l2(out16, mixed) <= 4e-3
+
+
 def test_debug_entry_rejects_other_shapes(cuda_mod):
     lib = cuda_mod._LIB
     proj, base, eta_raw, counts, cos, sin, dy = _random_case(5, 1, 600, 2, 48, 64)
