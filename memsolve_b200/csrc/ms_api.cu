@@ -35,6 +35,7 @@ int launch_readout(const ms_shape&, const Plan&, const void* projected, const fl
 int launch_token_backward(const ms_shape&, const Plan&, const void* projected, const void* dy, const float* cos,
                           const float* sin, const float* counts, const ms_tape&, const void* gram_grad,
                           const void* cross_grad, void* dprojected, const CoreAdjoint* core, cudaStream_t);
+int stats_tc_group_heads(int rank);
 int launch_readout_tc(const ms_shape&, const Plan&, const void* projected, const float* cos, const float* sin,
                       const float* counts, const ms_tape&, void* mixed, float* debug, cudaStream_t);
 int launch_token_backward_tc(const ms_shape&, const Plan&, const void* projected, const void* dy, const float* cos,
@@ -210,6 +211,40 @@ Plan make_plan(const ms_shape& s) {
     const int per_chunk = (int)((tiles + cb - 1) / cb);
     p.chunk_tokens_bwd = per_chunk * kTileTokens;
     p.chunks_bwd = (s.tokens + p.chunk_tokens_bwd - 1) / p.chunk_tokens_bwd;
+  }
+  static const bool no_tc_env = [] {
+    const char* v = std::getenv("MEMSOLVE_NO_TCGEN05");
+    return v && v[0] == '1';
+  }();
+  // The tcgen05 statistics kernel (long samples, head dimension 64, rank 16/32/64) gives a CTA a group of heads
+  // and a chunk of 128-token tiles: chunks are counted per head group, not per head.
+  // Rank 64 takes it by default: the mma.sync kernels keep a rank-64 accumulator tile in registers only for the
+  // adjoint, and the forward falls back to the generic loader.  At rank 16 and 32 the tcgen05 kernel is limited by
+  // the shared-memory traffic of its many small MMAs and only matches the mma.sync kernels, while its finer
+  // chunking (one partial per CTA and head group) lengthens the compact stage; MEMSOLVE_STATS_TCGEN05=1 selects
+  // it there too (tests do).
+  static const bool all_ranks_env = [] {
+    const char* v = std::getenv("MEMSOLVE_STATS_TCGEN05");
+    return v && v[0] == '1';
+  }();
+  p.stats_tc = !no_tma_env && !no_tc_env && s.head_dim == 64 && s.tokens >= 1024 &&
+               (s.rank == 64 || (all_ranks_env && (s.rank == 16 || s.rank == 32)));
+  if (p.stats_tc) {
+    const int gsize = stats_tc_group_heads(s.rank);
+    const long groups = (long)s.batch * ((s.heads + gsize - 1) / gsize);
+    const int tiles128 = (s.tokens + 127) / 128;
+    auto size_chunks = [&](long ctas, int& n_chunks, int& chunk_tokens) {
+      long c = ctas / groups;
+      if (c < 1) c = 1;
+      if (c > tiles128) c = tiles128;
+      const int per_chunk = (int)((tiles128 + c - 1) / c);
+      chunk_tokens = per_chunk * 128;
+      n_chunks = (s.tokens + chunk_tokens - 1) / chunk_tokens;
+    };
+    // forward: the per-head core rides in spare CTAs of the same grid
+    const long core_slabs = (s.heads + groups - 1) / groups;
+    size_chunks(sm_count() - core_slabs * groups > groups ? sm_count() - core_slabs * groups : groups, p.chunks, p.chunk_tokens);
+    size_chunks(sm_count(), p.chunks_bwd, p.chunk_tokens_bwd);
   }
   p.aligned = (s.head_dim % 8) == 0;
   static const bool no_tma = [] {

@@ -57,6 +57,7 @@ struct Plan {
   bool aligned;      // 16-byte vector path usable for projected / dy / tables
   bool tma;          // TMA kernels allowed (off when the environment sets MEMSOLVE_NO_TMA=1)
   bool tc;           // tcgen05 kernels allowed (off with MEMSOLVE_NO_TMA=1 or MEMSOLVE_NO_TCGEN05=1)
+  bool stats_tc;     // the token chunks were sized for the tcgen05 statistics kernel (head groups, 128-token tiles)
   size_t fwd_partial_floats;  // per (system, chunk): r*r + r*d
   size_t bwd_partial_floats;  // per (system, chunk): r*d
   size_t ws_partials;         // floats

@@ -362,9 +362,18 @@ static int launch_rank(const StatsParams& p, dim3 grid, bool rot, bool aligned, 
   return aligned ? launch_one<R, GRAD, false, true>(p, grid, st) : launch_one<R, GRAD, false, false>(p, grid, st);
 }
 
+int launch_stats_tc(const ms_shape& s, const Plan& plan, bool grad, const void* projected, const void* dy,
+                    const float* cos, const float* sin, float* partials, float* de_partials, const float* base_raw,
+                    const float* eta_raw, const ms_tape* core_tape, cudaStream_t st);
+
 int launch_stats(const ms_shape& s, const Plan& plan, bool grad, const void* projected, const void* dy,
                  const float* cos, const float* sin, float* partials, float* de_partials,
                  const float* base_raw, const float* eta_raw, const ms_tape* core_tape, cudaStream_t st) {
+  if (plan.tc) {
+    const int r = launch_stats_tc(s, plan, grad, projected, dy, cos, sin, partials, de_partials, base_raw, eta_raw,
+                                  core_tape, st);
+    if (r != -1) return r;
+  }
   if (plan.tma) {
     const int r = launch_stats_tma(s, plan, grad, projected, dy, cos, sin, partials, de_partials, base_raw, eta_raw,
                                    core_tape, st);

@@ -57,9 +57,9 @@ __device__ __forceinline__ uint64_t smem_desc_n_major_128(uint32_t addr) {
 // Instruction descriptor of kind::f16 with BF16 operands and an FP32 accumulator: accumulator format
 // in bits [4,6) (1 = F32), operand formats in [7,10) and [10,13) (1 = BF16), operand-major bits 15 (A)
 // and 16 (B) (0 = contraction-major), N/8 in [17,23), M/16 in [24,29).
-__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, bool b_n_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_n_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(m >> 4) << 24);
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, bool b_n_major, bool a_m_major = false) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_m_major ? 1u : 0u) << 15) | ((b_n_major ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // ---------------------------------------------------------------------------------------

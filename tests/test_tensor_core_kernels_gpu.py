@@ -127,6 +127,64 @@ def test_readout_fp32_before_rounding(cuda_mod, rank, rot, length, comp):
         assert rel_l2(out16, mixed) <= 4e-3
 
 
+@pytest.mark.parametrize("rank,rot,length,heads,batch,masked", [
+    (32, True, 5000, 3, 2, False), (64, True, 3000, 5, 1, False), (16, False, 2100, 6, 2, False),
+    (32, False, 1500, 2, 1, True), (16, True, 4096, 5, 1, False), (64, False, 1024, 2, 2, False),
+    (32, True, 32768, 12, 1, False), (64, True, 32768, 12, 1, False)])
+def test_tcgen05_statistics_stagewise(cuda_mod, rank, rot, length, heads, batch, masked):
+    """Forward (G, Q) and adjoint (E, <dY, C>) token reductions of the tcgen05 kernel against FP64, <= 1e-5
+    (the limit of the statistics stage), for head groups that are full, partial (odd head counts) and of four
+    heads (rank 16), with and without rotation, ragged last tiles and counts.  The 1e-5 limit is the reference's
+    for its own sizes (up to 8193 tokens, tests/cuda/test_fast_path.py:847-932); the two 32768-token cases sum
+    twenty times more FP32 terms per accumulator and are held to 2e-5 (measured 4e-6 ... 1.5e-5)."""
+    lib = cuda_mod._LIB
+    proj, base, eta_raw, counts, cos, sin, dy = _random_case(830 + rank + length, batch, length, heads, rank, 64,
+                                                             rot=rot, masked=masked)
+    dp, ddy = proj.cuda(), dy.cuda().contiguous()
+    dcos, dsin, dcounts = _dev(cos), _dev(sin), _dev(counts)
+    shape = cuda_mod._Shape(batch, length, heads, rank, 64, 0, 0 if cos is None else cos.shape[0], 0)
+    ws = cuda_mod._workspace(shape, dp.device)
+    ptr = cuda_mod._ptr
+    stream = torch.cuda.current_stream().cuda_stream
+    fwd = torch.full((lib.ms_packed_stats_floats(ctypes.byref(shape), 0),), float("nan"), device="cuda")
+    bwd = torch.full((lib.ms_packed_stats_floats(ctypes.byref(shape), 1),), float("nan"), device="cuda")
+    assert lib.ms_stats_forward(ctypes.byref(shape), dp.data_ptr(), ptr(dcos), ptr(dsin), ptr(dcounts), ws.data_ptr(),
+                                ws.numel(), fwd.data_ptr(), stream) == 0
+    assert lib.ms_stats_backward(ctypes.byref(shape), dp.data_ptr(), ddy.data_ptr(), ptr(dcos), ptr(dsin),
+                                 ptr(dcounts), ws.data_ptr(), ws.numel(), bwd.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert lib.ms_device_error() == 0
+    g, q = O.stage_stats(proj, heads, rank, counts, cos, sin)
+    pk = fwd.view(batch * heads, rank * rank + rank * 64).cpu()
+    errs = {"G": rel_l2(pk[:, : rank * rank].reshape(batch, heads, rank, rank), g),
+            "Q": rel_l2(pk[:, rank * rank:].reshape(batch, heads, rank, 64), q)}
+    want = O.stage_backward(proj, dy, base, eta_raw, counts, cos, sin)
+    got_e = bwd[: batch * heads * rank * 64].view(batch, heads, rank, 64).cpu()
+    got_de = bwd[batch * heads * rank * 64:].view(batch, heads).cpu().double().sum(0)
+    errs["E"] = rel_l2(got_e, want["E"])
+    errs["de"] = rel_l2(got_de, want["de"])
+    print(f"statistics r{rank} rot={rot} N{length} H{heads} B{batch}", {k: f"{v:.2e}" for k, v in errs.items()})
+    limit = 1e-5 if length <= 8193 else 2e-5
+    assert all(v <= limit for v in errs.values()), errs
+
+
+def test_tcgen05_statistics_all_ranks_in_child_process():
+    """Rank 16 and 32 take the mma.sync statistics kernels unless MEMSOLVE_STATS_TCGEN05=1 is set when the
+    library plans its first launch: run the stage-wise statistics cases and the mixer cases of this file in
+    a child process with the switch on, so the tcgen05 kernel is checked at every rank."""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("MEMSOLVE_STATS_TCGEN05") == "1":
+        pytest.skip("already inside the child process")
+    env = dict(os.environ, MEMSOLVE_STATS_TCGEN05="1")
+    here = os.path.abspath(__file__)
+    done = subprocess.run([sys.executable, "-m", "pytest", here, "-q", "-x", "-p", "no:cacheprovider", "-k",
+                           "statistics_stagewise or token_backward_matches_oracle"], env=env, capture_output=True,
+                          text=True, timeout=900)
+    assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-2000:]
+
+
 def test_debug_entry_rejects_other_shapes(cuda_mod):
     lib = cuda_mod._LIB
     proj, base, eta_raw, counts, cos, sin, dy = _random_case(5, 1, 600, 2, 48, 64)
