@@ -3,18 +3,21 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c5|c2|c4]
 
-Workload (default, "c3"): BASELINE configuration 3 -- one MemSolve layer, dim 768, 12 heads
-(head dim 64), rank 32, rotary on, BF16, x = [1, 32768, 768] ~ N(0,1), upstream gradient
-~ N(0,1), seeded random-init weights (core_base_raw ~ N(0, 0.1^2) so the core is exercised),
-recompute_readout=False.  With N > 1 GPUs every rank holds 32768 local tokens of one
-sequence of 32768*N tokens (sequence parallel, weak scaling).  "c5" is BASELINE configuration 5:
-rank 64, one sequence of 262144 tokens split evenly over the ranks (strong scaling).
+Workload on one GPU ("c3"): one MemSolve layer, dim 768, 12 heads (head dim 64), rank 32, rotary on,
+BF16, x = [1, 32768, 768] ~ N(0,1), upstream gradient ~ N(0,1), seeded random-init weights
+(core_base_raw ~ N(0, 0.1^2) so the core is exercised), recompute_readout=False -- the long-sequence
+single-layer shape the headline metric is quoted on.  On N > 1 GPUs ("c5"): rank 64, one sequence of
+262144 tokens split evenly over the ranks (sequence parallel, strong scaling) -- the reference's
+multi-GPU shape; `--workload c3 --gpus N` instead gives every rank 32768 tokens of a 32768*N-token
+sequence (weak scaling).
 
-A step is layer forward + backward (+ the sequence-parallel gradient SUM when N > 1).
-`value` is tokens/s of the whole job with inputs resident in HBM; `e2e` repeats the step
-through the same public call with the inputs in pinned host memory (copied in every step) and
-a scalar result read back.  `roofline` is measured live: each mixer kernel is timed alone with
-CUDA events on the launching stream after an L2 flush.
+A step is layer forward + backward (+ the sequence-parallel gradient SUM when N > 1).  The timed region is
+`--blocks` blocks of `--steps` steps each, every block bracketed by a barrier and a device synchronisation;
+the median block is reported.  `value` is tokens/s of the whole job with inputs resident in HBM; `e2e`
+repeats the step through the same public call with the inputs in pinned host memory (copied in every step)
+and the output and the input gradient copied back to pinned host memory.  `roofline` is measured live: each
+mixer kernel is timed alone with CUDA events on the launching stream after an L2 flush.  `--sweep` prints
+one line per sequence length 128 ... 32768 (tokens/s of the layer and of the mix core).
 """
 from __future__ import annotations
 
@@ -111,8 +114,46 @@ def build_layer(cfg, device, seed=0):
 # ---------------------------------------------------------------------------------------
 # reference arm / CPU baseline: the oracle port of the reference's pure-PyTorch CPU path
 # ---------------------------------------------------------------------------------------
+REF_DIR = os.path.join(ROOT, "oracle", "_ref")
+
+
+def reference_available() -> bool:
+    return os.path.exists(os.path.join(REF_DIR, "memsolve", "__init__.py"))
+
+
+def reference_layer_step(cfg, tokens, seed=0):
+    """One forward+backward of the reference's own layer (`layer(x, implementation="reference")`, its pure
+    PyTorch CPU path) on `tokens` tokens; the package is the copy that oracle/build_ref.py placed in oracle/_ref."""
+    if REF_DIR not in sys.path:
+        sys.path.insert(0, REF_DIR)
+    from memsolve import MemSolve as RefLayer, MemSolveConfig as RefConfig
+    torch.manual_seed(seed)
+    layer = RefLayer(RefConfig(dim=cfg["dim"], num_heads=cfg["heads"], rank=cfg["rank"], rotary=True))
+    with torch.no_grad():
+        layer.core_base_raw.normal_(std=0.1)
+    x = torch.randn(1, tokens, cfg["dim"]).bfloat16().requires_grad_()
+    dout = torch.randn(1, tokens, cfg["dim"]).bfloat16()
+
+    def step():
+        layer.zero_grad(set_to_none=True)
+        x.grad = None
+        y = layer(x, implementation="reference")
+        y.backward(dout)
+        return y
+
+    return step
+
+
 def cpu_layer_step(cfg, tokens, seed=0):
-    """Returns a closure running one oracle layer forward+backward on `tokens` tokens."""
+    """Returns (closure running one CPU layer forward+backward on `tokens` tokens, kind): the reference's own
+    package when it is present, else the oracle port of it."""
+    if reference_available():
+        return reference_layer_step(cfg, tokens, seed), "reference"
+    return port_layer_step(cfg, tokens, seed), "port"
+
+
+def port_layer_step(cfg, tokens, seed=0):
+    """One oracle layer forward+backward on `tokens` tokens."""
     from oracle import memsolve_oracle as O
     from memsolve_b200 import MemSolve, MemSolveConfig
     torch.manual_seed(seed)
@@ -141,7 +182,8 @@ def cpu_layer_step(cfg, tokens, seed=0):
 
 
 def time_cpu(cfg, tokens, steps, warmup):
-    step = cpu_layer_step(cfg, tokens)
+    """(seconds per step, kind) of the CPU layer on `tokens` tokens."""
+    step, kind = cpu_layer_step(cfg, tokens)
     for _ in range(warmup):
         step()
     times = []
@@ -149,7 +191,11 @@ def time_cpu(cfg, tokens, steps, warmup):
         t0 = time.perf_counter()
         step()
         times.append(time.perf_counter() - t0)
-    return sum(times) / len(times)
+    return sum(times) / len(times), kind
+
+
+CPU_KIND_TEXT = {"reference": "the reference's own pure-PyTorch CPU layer (layer(x, implementation=\"reference\"))",
+                 "port": "oracle port of the reference's pure-PyTorch CPU layer"}
 
 
 def run_reference(args, cfg):
@@ -163,22 +209,24 @@ def run_reference(args, cfg):
         pass
     full = cfg.get("local_tokens", cfg.get("global_tokens"))
     # bounded sample: pick the largest token count whose (steps+warmup) run stays near two minutes
-    probe = time_cpu(cfg, 2048, 1, 1)
-    budget = 120.0 / max(1, args.steps + args.warmup)
+    probe, _ = time_cpu(cfg, 2048, 1, 1)
+    steps = min(args.steps, 10)          # the CPU arm needs no more repetitions than that for a stable mean
+    warmup = min(args.warmup, 2)
+    budget = 150.0 / max(1, steps + warmup)
     tokens = full
     while tokens > 2048 and probe * (tokens / 2048.0) > budget:
         tokens //= 2
-    dt = time_cpu(cfg, tokens, args.steps, args.warmup)
+    dt, kind = time_cpu(cfg, tokens, steps, warmup)
     value = tokens / dt
     cores = torch.get_num_threads()
     line = {
         "impl": "reference", "metric": "layer_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "strong" if cfg["strong"] else "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args, cfg, 1),
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
-                         "sample": f"{tokens} of {full} tokens per step, oracle port of the reference CPU path"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": kind,
+                         "sample": f"{tokens} of {full} tokens per step, {CPU_KIND_TEXT[kind]}"},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -303,16 +351,96 @@ def time_kernels(layer, cfg, tokens, device, reps=10, warm=3, with_graph=True, b
     return out
 
 
-# DRAM bytes (read + write) of one launch at 32768 tokens, rank 32, from the ncu capture summarised in
-# profiles/ (full ncu capture of the mixer kernels).  Traffic of these streaming kernels grows in proportion to tokens.
-_NCU_DRAM_BYTES_C3 = {"stats_forward": 87.4e6, "readout": 104.4e6, "stats_backward": 137.9e6,
-                      "token_backward": 176.8e6}
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "dram_traffic_per_launch.md")
 
 
 def _ncu_traffic(workload, kernel, tokens):
-    if workload != "c3" or kernel not in _NCU_DRAM_BYTES_C3:
-        return None
-    return _NCU_DRAM_BYTES_C3[kernel] * tokens / 32768
+    """DRAM bytes (read + write) of one launch of `kernel`, from the ncu captures summarised in
+    profiles/dram_traffic_per_launch.md (lines `workload kernel tokens bytes`); the traffic of these streaming
+    kernels grows in proportion to the tokens of a launch.  None when the file has no line for the kernel."""
+    try:
+        with open(TRAFFIC_FILE) as f:
+            for line in f:
+                parts = line.split()
+                if len(parts) >= 4 and parts[0] == workload and parts[1] == kernel:
+                    return float(parts[3]) * tokens / float(parts[2])
+    except (OSError, ValueError):
+        pass
+    return None
+
+
+def time_one_gpu(cfg, device, steps=10):
+    """tokens/s of the whole `cfg` workload (all its tokens) on one GPU without sequence parallelism: CUDA-graph
+    replays, median of three blocks."""
+    tokens = cfg.get("global_tokens", cfg.get("local_tokens"))
+    layer = build_layer(cfg, device)
+    gen = torch.Generator().manual_seed(99)
+    x = torch.randn(1, tokens, cfg["dim"], generator=gen).bfloat16().to(device).requires_grad_()
+    dout = torch.randn(1, tokens, cfg["dim"], generator=gen).bfloat16().to(device)
+
+    def step():
+        layer.zero_grad(set_to_none=True)
+        x.grad = None
+        layer(x, implementation="cuda").backward(dout)
+
+    for _ in range(3):
+        step()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for _ in range(3):
+        graph.replay()
+    blocks = []
+    for _ in range(3):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        e1.synchronize()
+        blocks.append(e0.elapsed_time(e1) * 1e-3 / steps)
+    dt = statistics.median(blocks)
+    graph.reset()
+    del graph, x, dout, layer
+    torch.cuda.empty_cache()
+    return {"value": tokens / dt, "unit": "tokens/s", "ms_per_step": dt * 1e3, "n_gpus": 1,
+            "note": "same workload on rank 0's GPU alone, measured in this run before the ranks join"}
+
+
+def run_sweep(args):
+    """One line per sequence length 128 ... 32768 (the reference benchmark's sweep, benchmarks/benchmark_ball.py:
+    20-66): layer forward+backward as CUDA-graph replays, and the mix core (fast_mix forward + backward, six
+    launches) alone with its fraction of the HBM roofline."""
+    from memsolve_b200.ball import cuda as C
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    C.load(device=device)
+    cfg = CONFIGS["c3"]
+    hbm, _tc, which = _peaks()
+    width = cfg["heads"] * cfg["rank"] + cfg["dim"]
+    rows = []
+    tokens = 128
+    while tokens <= 32768:
+        one = time_one_gpu(dict(cfg, local_tokens=tokens), device, steps=50)
+        kern = time_kernels(build_layer(cfg, device), cfg, tokens, device, reps=3, warm=2, with_graph=True)
+        core_s = kern["mix_core_graph"]["s"]
+        core_bytes = 2 * (5 * width + 3 * cfg["dim"]) * tokens
+        rows.append({"tokens": tokens, "layer_us": round(one["ms_per_step"] * 1e3, 2),
+                     "layer_tokens_per_s": one["value"], "mix_core_us": round(core_s * 1e6, 2),
+                     "mix_core_tokens_per_s": tokens / core_s,
+                     "mix_core_frac_of_hbm": core_bytes / core_s / 1e9 / hbm})
+        tokens *= 2
+    print(json.dumps({"metric": "layer_fwd_bwd_tokens_per_s", "unit": "tokens/s", "sweep": rows, "dtype": "bf16",
+                      "data": "synthetic", "peak_source": f"of {which}", "timing": "cuda_graph_replay",
+                      "config": {"workload": "MemSolve layer fwd+bwd, dim 768, 12 heads, rank 32, rotary, B=1, "
+                                             "N = 128 ... 32768"}}))
 
 
 def run_ours(args, cfg):
@@ -339,6 +467,12 @@ def run_ours(args, cfg):
     x = x_host.to(device).requires_grad_()
     dout = d_host.to(device)
     sp = counts = None
+    peer_path = False
+    one_gpu = None
+    if world > 1 and cfg["strong"] and rank == 0 and not args.no_one_gpu:
+        # the same strong-scaling workload on this GPU alone (no sequence parallelism), as the reference point of
+        # the multi-GPU figure: measured before the ranks start working together
+        one_gpu = time_one_gpu(cfg, device)
     if world > 1:
         sp = SequenceParallel.create(tokens)
         counts = sp.valid_counts(None, batch_size=1, device=device)
@@ -347,6 +481,7 @@ def run_ours(args, cfg):
         # path on 2, 4 and 8 GPUs); MEMSOLVE_BENCH_PEER_EXCHANGE=0 selects NCCL for both instead
         if os.environ.get("MEMSOLVE_BENCH_PEER_EXCHANGE", "") != "0":
             sp.use_peer_exchange()
+            peer_path = True
 
     def step(xin, grad_out):
         layer.zero_grad(set_to_none=True)
@@ -365,20 +500,25 @@ def run_ours(args, cfg):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, finish=None):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        if finish is not None:
-            finish()
-        e1.record()
-        barrier()
-        t = torch.tensor([e0.elapsed_time(e1) * 1e-3], device=device, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    def timed(fn, steps, finish=None, blocks=1):
+        """Median over `blocks` blocks of `steps` calls; every block is bracketed by a barrier and a device
+        synchronisation, timed with CUDA events on this rank and reduced with MAX over the ranks."""
+        totals = []
+        for _ in range(blocks):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            if finish is not None:
+                finish()
+            e1.record()
+            barrier()
+            t = torch.tensor([e0.elapsed_time(e1) * 1e-3], device=device, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            totals.append(float(t.item()))
+        return statistics.median(totals)
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -409,7 +549,8 @@ def run_ours(args, cfg):
             graph = None
             torch.cuda.synchronize()
     eager_total = timed(lambda: step(x, dout), args.steps)
-    total = timed(graph.replay, args.steps) if graph is not None else eager_total
+    total = timed(graph.replay, args.steps, blocks=args.blocks) if graph is not None else \
+        timed(lambda: step(x, dout), args.steps, blocks=args.blocks)
     # nvidia-smi samples every 100 ms and the timed region lasts milliseconds: keep the same step
     # running (untimed) for about a second so that the clock record covers this load
     t_end = time.perf_counter() + 1.2
@@ -421,10 +562,18 @@ def run_ours(args, cfg):
     if clocks is not None:
         clocks["window"] = "warm-up + timed steps + 1.2 s of the same step"
 
-    # end to end: inputs start in pinned host memory every step, a scalar result comes back
+    # end to end: inputs start in pinned host memory every step; the layer output and the input gradient go back
+    # to pinned host memory every step
     x_dev = torch.empty_like(x_host, device=device).requires_grad_()
     d_dev = torch.empty_like(d_host, device=device)
-    result = torch.zeros(1, dtype=torch.float32).pin_memory()
+    y_host = torch.empty_like(x_host).pin_memory()
+    dx_host = torch.empty_like(x_host).pin_memory()
+    y_stage = torch.empty_like(x_host, device=device)
+    dx_stage = torch.empty_like(x_host, device=device)
+    back_stream = torch.cuda.Stream(device)
+    results_staged = torch.cuda.Event()
+    results_copied = torch.cuda.Event()
+    results_copied.record()
 
     # The copies of step k+1 run on a copy stream into staging buffers while step k computes (what a
     # training loop with a prefetching loader does); the step then takes its inputs from the staging
@@ -463,13 +612,27 @@ def run_ours(args, cfg):
             y = step(x_dev, d_dev)
             dx = x_dev.grad
         with torch.no_grad():
-            result.copy_((y[0, :8].float().sum() + dx[0, :8].float().sum()).reshape(1), non_blocking=True)
+            # results leave through staging buffers on a copy stream of their own (PCIe is full duplex), while
+            # the next step already computes
+            main.wait_event(results_copied)           # the staging buffers of the step before have been read
+            y_stage.copy_(y)
+            dx_stage.copy_(dx)
+            results_staged.record(main)
+            with torch.cuda.stream(back_stream):
+                back_stream.wait_event(results_staged)
+                y_host.copy_(y_stage, non_blocking=True)
+                dx_host.copy_(dx_stage, non_blocking=True)
+                results_copied.record(back_stream)
 
     prefetch()
     for _ in range(2):
         e2e_step()
     # the timed region ends after the copy stream has drained too (steps + 1 input copies for `steps` steps)
-    e2e_total = timed(e2e_step, args.steps, finish=lambda: torch.cuda.current_stream().wait_stream(copy_stream))
+    def drain():
+        torch.cuda.current_stream().wait_stream(copy_stream)
+        torch.cuda.current_stream().wait_stream(back_stream)
+
+    e2e_total = timed(e2e_step, args.steps, finish=drain, blocks=min(args.blocks, 3))
 
     timing_mode = "cuda_graph_replay" if graph is not None else "eager"
     # a captured graph keeps references to the NCCL communicator: release it before the group goes away
@@ -504,17 +667,26 @@ def run_ours(args, cfg):
         "scaling": "strong" if cfg["strong"] else "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(args, cfg, world), "clocks": clocks,
         "e2e": {"value": global_tokens / (e2e_total / args.steps), "unit": "tokens/s",
-                "h2d_bytes_per_step": (x_host.numel() + d_host.numel()) * 2 * world, "d2h_bytes_per_step": 4 * world},
+                "h2d_bytes_per_step": (x_host.numel() + d_host.numel()) * 2 * world,
+                "d2h_bytes_per_step": (y_host.numel() + dx_host.numel()) * 2 * world},
         # own kernels per step: statistics (+ per-head core), compact, readout, and their three adjoints;
         # the sequence-parallel path adds a pack kernel per direction (the buffer that is all-reduced)
-        "gpu_launches": (6 if world == 1 else 8) * args.steps,
-        "timing": timing_mode,
+        # statistics (+ per-head core), compact, readout and their three adjoints; sequence parallel with the
+        # peer-memory exchange adds one exchange kernel per direction and one SUM kernel per weight matrix
+        "gpu_launches": (6 if world == 1 else (10 if peer_path else 8)) * args.steps * args.blocks,
+        "timing": f"{timing_mode}, median of {args.blocks} blocks of {args.steps} steps",
         "eager_ms_per_step": eager_total / args.steps * 1e3,
+        "collective": None if world == 1 else (
+            "statistics: one kernel over NVLink peer memory per direction; weight gradients: peer-memory SUM kernel "
+            "overlapped with backward; small gradients: NCCL all-reduce" if peer_path else
+            "NCCL all-reduce of the packed statistics per direction; NCCL all-reduce of the gradients overlapped "
+            "with backward"),
+        "one_gpu_same_workload": one_gpu,
         "roofline": {
             "bound": "hbm", "kernel": name, "achieved": achieved, "peak": hbm, "unit": "GB/s",
             "frac": achieved / hbm, "traffic": _ncu_traffic(args.workload, name, tokens),
-            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 32768 tokens "
-                              "(summary under profiles/), scaled by tokens",
+            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch "
+                              "(profiles/dram_traffic_per_launch.md names the capture), scaled by tokens",
             "peak_source": f"of {which}",
             "per_kernel_us": {k: round(v["s"] * 1e6, 2) for k, v in kern.items()},
             "per_kernel_gbs": {k: round(v["bytes"] / v["s"] / 1e9, 1) for k, v in kern.items() if v["bytes"]},
@@ -530,12 +702,16 @@ def run_ours(args, cfg):
         },
     }
     if world == 1 and not args.no_cpu:
-        n_cpu = 8192
-        t_cpu = time_cpu(cfg, n_cpu, 2, 1)
+        try:
+            torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+        except (AttributeError, RuntimeError):
+            pass
+        n_cpu = tokens   # the whole workload: about half a second per step on the box's cores
+        t_cpu, kind = time_cpu(cfg, n_cpu, 3, 1)
         line["cpu_baseline"] = {"value": n_cpu / t_cpu, "unit": "tokens/s", "cores": torch.get_num_threads(),
-                                "kind": "port",
-                                "sample": f"{n_cpu}-token slice of the workload, 2 timed steps, oracle port of the "
-                                          "reference's pure-PyTorch CPU layer forward+backward"}
+                                "kind": kind,
+                                "sample": f"all {n_cpu} tokens of the workload, 3 timed steps after 1 warm-up, "
+                                          f"{CPU_KIND_TEXT[kind]} forward+backward"}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -680,10 +856,15 @@ def run_scaffold(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--blocks", type=int, default=7, help="timed blocks of --steps steps; the median is reported")
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    ap.add_argument("--workload", choices=tuple(CONFIGS) + tuple(SCAFFOLDS), default="c3")
+    ap.add_argument("--workload", choices=tuple(CONFIGS) + tuple(SCAFFOLDS), default=None,
+                    help="default: c3 on one GPU, c5 (strong scaling) on several")
+    ap.add_argument("--sweep", action="store_true", help="sequence lengths 128 ... 32768 on one GPU")
+    ap.add_argument("--no-one-gpu", action="store_true",
+                    help="skip the one-GPU measurement of the same workload in a multi-GPU strong-scaling run")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
     ap.add_argument("--kernels-only", action="store_true",
@@ -692,6 +873,11 @@ def main():
     ap.add_argument("--kernel-warmup", type=int, default=3)
     ap.add_argument("--tokens", type=int, default=0, help="with --kernels-only: tokens per launch instead of the workload's")
     args = ap.parse_args()
+    if args.workload is None:
+        args.workload = "c3" if args.gpus <= 1 else "c5"
+    if args.sweep:
+        run_sweep(args)
+        return
     if args.workload in SCAFFOLDS:
         if args.impl != "ours" or args.gpus != 1:
             raise SystemExit("the scaffold workloads run the CUDA arm on one GPU")
