@@ -718,7 +718,7 @@ def run_ours(args, cfg):
 
 
 # ---------------------------------------------------------------------------------------
-# encoder scaffolds (configurations 2 and 4): many short sequences, one GPU
+# encoder scaffolds (ViT-Small-shaped "c2", BERT-base-shaped "c4"): many short sequences, one GPU
 # ---------------------------------------------------------------------------------------
 SCAFFOLDS = {
     "c2": dict(kind="vision", batch=256, tokens=197, dim=384, heads=6, rank=32, depth=12),
@@ -840,7 +840,7 @@ def run_scaffold(args):
         "metric": f"scaffold_fwd_bwd_{unit.split('/')[0]}_per_s", "value": units / dt, "unit": unit, "n_gpus": 1,
         "steps": args.steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "timing": "eager, BF16 autocast",
-        "config": {"workload": f"configuration {args.workload[1]}: {spec['kind']} scaffold, {spec['depth']} layers, "
+        "config": {"workload": f"{args.workload}: {spec['kind']} scaffold, {spec['depth']} layers, "
                                f"dim {spec['dim']}, {spec['heads']} heads, rank {spec['rank']}, batch {spec['batch']}"
                                f" x {spec['tokens']} tokens", "parallelism": "sp1"},
         "clocks": clocks, "gpu_launches": 6 * spec["depth"] * args.steps,

@@ -10,33 +10,6 @@
 
 #include "../../include/memsolve_b200.h"
 
-// Phase time stamps for development builds (-DMS_PROFILE_TICKS); compiled out of the library.
-#ifdef MS_PROFILE_TICKS
-static __device__ long long g_ms_ticks[64];
-#define MS_TICK(i)                                                                   \
-  do {                                                                               \
-    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)   \
-      g_ms_ticks[i] = clock64();                                                     \
-  } while (0)
-// per-warp start / end times in nanoseconds (slot = any index below 8192)
-static __device__ unsigned long long g_ms_stamps[8192][2];
-#define MS_STAMP(slot, which)                                                          \
-  do {                                                                                 \
-    if ((threadIdx.x & 31) == 0) {                                                     \
-      unsigned long long t_;                                                           \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                           \
-      g_ms_stamps[(slot) & 8191][which] = t_;                                          \
-    }                                                                                  \
-  } while (0)
-#else
-#define MS_TICK(i) \
-  do {             \
-  } while (0)
-#define MS_STAMP(slot, which) \
-  do {                        \
-  } while (0)
-#endif
-
 namespace ms {
 
 constexpr int kTileTokens = 64;   // token rows per shared-memory tile

@@ -295,7 +295,6 @@ compact_forward_kernel(const CompactFwdParams p) {
   const float eta = p.eta[h];
   const int d = p.head_dim;
   const bool staged = p.staged != 0;
-  MS_TICK(0);
 
   if (staged) {
     const uint32_t bar_addr = smem_u32(bar);
@@ -335,11 +334,9 @@ compact_forward_kernel(const CompactFwdParams p) {
       if (valid[e]) gs[off[e]] = acc[e] * inv_n;
   }
   __syncthreads();
-  MS_TICK(1);
   cholesky_inverse_cta<R>(gs, ts, tT, rowbuf, colbuf, dscale, tid);
   __syncthreads();
   grid_launch_dependents();
-  MS_TICK(2);
   for (int i = tid; i < R * R; i += kCompactThreads) {
     const int row = i / R, col = i - row * R;
     p.inverse[(size_t)sys * R * R + i] = ts[row * RP + col];
@@ -348,9 +345,7 @@ compact_forward_kernel(const CompactFwdParams p) {
   constexpr int TILES = (R / 4) * 32;   // 4 x 2 tiles of an r x 64 block
   for (int jb = 0; jb < p.dblocks; ++jb) {
     const int d0 = jb * 64, dv = min(64, d - d0);
-    MS_TICK(30);
     if (staged && jb == 0) ok = mbar_wait(smem_u32(bar) + 8, 0) && ok;
-    MS_TICK(31);
     for (int i0 = tid; i0 < R * 64; i0 += 4 * kCompactThreads) {
       int off[4];
       bool valid[4];
@@ -370,7 +365,6 @@ compact_forward_kernel(const CompactFwdParams p) {
       }
     }
     __syncthreads();
-    MS_TICK(3);
     // Z = T Q   (T lower triangular: the inner index stops at the row)
     for (int tile = tid; tile < TILES; tile += kCompactThreads) {
       const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
@@ -386,7 +380,6 @@ compact_forward_kernel(const CompactFwdParams p) {
       }
     }
     __syncthreads();
-    MS_TICK(4);
     // (F - eta I) Z -> qs
     for (int tile = tid; tile < TILES; tile += kCompactThreads) {
       const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
@@ -398,7 +391,6 @@ compact_forward_kernel(const CompactFwdParams p) {
         *reinterpret_cast<float2*>(qs + (i0 + r) * kQP + j0) = make_float2(acc[r][0], acc[r][1]);
     }
     __syncthreads();
-    MS_TICK(7);
     // W = T^T (F - eta I) Z   (the inner index starts at the row), two BF16 words
     __nv_bfloat16* hi = p.coeff + (size_t)sys * 2 * R * p.dpad;
     __nv_bfloat16* lo = hi + (size_t)R * p.dpad;
@@ -423,9 +415,7 @@ compact_forward_kernel(const CompactFwdParams p) {
       }
     }
     __syncthreads();
-    MS_TICK(5);
   }
-  MS_TICK(6);
   if (!ok && tid == 0) atomicExch(p.error, kErrBarrierTimeout);
 }
 
@@ -483,7 +473,6 @@ compact_backward_kernel(const CompactBwdParams p) {
   const float eta = p.eta[h];
   const int d = p.head_dim;
   const bool staged = p.staged != 0;
-  MS_TICK(9);
 
   if (staged) {
     const uint32_t bar_addr = smem_u32(bar);
@@ -519,7 +508,6 @@ compact_backward_kernel(const CompactBwdParams p) {
   }
   bool ok = true;
   if (staged) ok = mbar_wait(smem_u32(bar), 0);
-  MS_TICK(10);
 
   constexpr int TILES = (R / 4) * 32;          // 4 x 2 tiles of an r x 64 block
   constexpr int RTILES = (R / 4) * (R / 2);    // 4 x 2 tiles of an r x r matrix, columns j and j + r/2
@@ -551,7 +539,6 @@ compact_backward_kernel(const CompactBwdParams p) {
       }
     }
     __syncthreads();
-    MS_TICK(11);
     // U = T E
     for (int tile = tid; tile < TILES; tile += kCompactThreads) {
       const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
@@ -563,7 +550,6 @@ compact_backward_kernel(const CompactBwdParams p) {
         *reinterpret_cast<float2*>(us + (i0 + r) * kQP + j0) = make_float2(acc[r][0], acc[r][1]);
     }
     __syncthreads();
-    MS_TICK(12);
     // H += U Z^T   (r x r, contraction over the 64 channels)
 #pragma unroll
     for (int e = 0; e < RT_PER; ++e) {
@@ -573,7 +559,6 @@ compact_backward_kernel(const CompactBwdParams p) {
         mm_nt<64>(hacc[e], us, kQP, zs, kQP, i0, j0, j0 + R / 2);
       }
     }
-    MS_TICK(13);
     // dZ = M^T U -> es
     for (int tile = tid; tile < TILES; tile += kCompactThreads) {
       const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
@@ -585,7 +570,6 @@ compact_backward_kernel(const CompactBwdParams p) {
         *reinterpret_cast<float2*>(es + (i0 + r) * kQP + j0) = make_float2(acc[r][0], acc[r][1]);
     }
     __syncthreads();
-    MS_TICK(14);
     // dQ = T^T dZ, two BF16 words
     __nv_bfloat16* hi = p.cross_grad + (size_t)sys * 2 * R * p.dpad;
     __nv_bfloat16* lo = hi + (size_t)R * p.dpad;
@@ -612,7 +596,6 @@ compact_backward_kernel(const CompactBwdParams p) {
     __syncthreads();
   }
 
-  MS_TICK(16);
   grid_launch_dependents();
   // H to shared memory and to global (for the per-head sum over the batch)
 #pragma unroll
@@ -648,7 +631,6 @@ compact_backward_kernel(const CompactBwdParams p) {
     }
   }
   __syncthreads();
-  MS_TICK(17);
   // Y = sym T  (T lower triangular: row k of T is zero beyond column k)
   for (int tile = tid; tile < RTILES; tile += kCompactThreads) {
     const int i0 = (tile / (R / 2)) * 4, j0 = tile % (R / 2), j1 = j0 + R / 2;
@@ -662,7 +644,6 @@ compact_backward_kernel(const CompactBwdParams p) {
     }
   }
   __syncthreads();
-  MS_TICK(18);
   // dG = T^T Y ;  stored as s (dG + dG^T) (dG is symmetric, s = 1/sqrt(n): the factor the token pass would
   // otherwise apply to the product A (dG + dG^T) before adding the other two products) in two BF16 words
   const float s_tok = inv_sqrt_rn(n);
@@ -680,7 +661,6 @@ compact_backward_kernel(const CompactBwdParams p) {
       store_split(ghi, glo, (size_t)(i0 + r) * R + j1, acc[r][1] * s_tok);
     }
   }
-  MS_TICK(19);
   if (!ok && tid == 0) atomicExch(p.error, kErrBarrierTimeout);
 }
 

@@ -172,7 +172,6 @@ __device__ __forceinline__ void core_forward_device(const float* __restrict__ ba
   float* rowbuf = xt + R * RP;                    // 2 * (R + 4)
   int* zero_pivot = reinterpret_cast<int*>(rowbuf + 2 * (R + 4));
   const float* base = base_raw + (size_t)h * R * R;
-  MS_TICK(20);
 
   // L = tril(U,-1) + diag(softplus(diag U + c0))
   for (int idx = tid; idx < R * R; idx += NT) {
@@ -207,7 +206,6 @@ __device__ __forceinline__ void core_forward_device(const float* __restrict__ ba
     }
   }
   __syncthreads();
-  MS_TICK(21);
 
   // FP32 inverse
   {
@@ -222,7 +220,6 @@ __device__ __forceinline__ void core_forward_device(const float* __restrict__ ba
     }
   }
   __syncthreads();
-  MS_TICK(22);
 
   // one Newton-Schulz step in FP64:  X <- X + X (I - A X)
   for (int tile = tid; tile < RTILES; tile += NT) {
@@ -250,7 +247,6 @@ __device__ __forceinline__ void core_forward_device(const float* __restrict__ ba
       }
     }
   }
-  MS_TICK(23);
   if (tid == 0) core_info[h] = *zero_pivot <= R ? *zero_pivot : 0;
 }
 

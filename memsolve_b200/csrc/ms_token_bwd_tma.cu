@@ -182,7 +182,6 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     tma_load_3d(st + 4096, &map_a, h * R, c.slice * 16, b, bar);
   };
 
-  MS_STAMP((blockIdx.z * gridDim.x + blockIdx.x) * WARPS + warp, 0);
   for (int k = 0; k < PRE && k < n_items; ++k) {
     if (lane == 0) issue(ahead);
     advance(ahead);
@@ -329,7 +328,6 @@ token_backward_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     tma_store_wait_all<0>();
     if (!ok) atomicExch(p.error, kErrBarrierTimeout);
   }
-  MS_STAMP((blockIdx.z * gridDim.x + blockIdx.x) * WARPS + warp, 1);
 }
 
 template <int R, class Cfg>

@@ -146,7 +146,7 @@ def layer_cases(ref):
               meta=np.array([dim, heads, rank, b, n, int(mode == "complement"), int(rot), int(bias)], dtype=np.int64),
               **params, **out)
 
-    # BASELINE config 1: dim 384, 6 heads, rank 32, x [4,196,384] fp32, seed 0, default init.
+    # the CPU-runnable small case: dim 384, 6 heads, rank 32, x [4,196,384] fp32, seed 0, default init.
     torch.manual_seed(0)
     layer = MemSolve(MemSolveConfig(dim=384, num_heads=6, rank=32))
     x = torch.randn(4, 196, 384)

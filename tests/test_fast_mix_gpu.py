@@ -199,6 +199,21 @@ def test_numerical_boundaries(cuda_mod, rel_scale, eta_value, base_scale):
         assert errs["deta"] <= 3e-2, errs
 
 
+@pytest.mark.parametrize("length", [1, 2, 7, 16])
+@pytest.mark.parametrize("rank", [16, 64])
+@pytest.mark.parametrize("rel_scale", [1.0, 32.0])
+def test_fewer_tokens_than_rank(cuda_mod, length, rank, rel_scale):
+    """N <= r, where the reference switches to a token-space system (memsolve/ball/cuda.py:3230-3926; its tests
+    use N = 1 and 7, tests/cuda/test_fast_path.py:1805-1838).  Here the rank-space kernels serve every length:
+    the Gram matrix then has rank N < r and I + G stays well conditioned (eigenvalues 1 and 1 + sigma^2), also
+    under strong relations (entries of A up to ~100), which is what this case pins down: forward 5e-3,
+    gradients 3e-2, both core modes' shared path, rotary on."""
+    case = _random_case(3300 + 7 * length + rank, 2, length, 2, rank, 64, rot=True, rel_scale=rel_scale,
+                        base_scale=0.3)
+    _assert_case(cuda_mod, *case, gproj=5e-3 if rel_scale == 1.0 else 3e-2, gpar=3e-2,
+                 tag=f"short N={length} r{rank} relations x{rel_scale}")
+
+
 def test_correction_term_alone(cuda_mod):
     """mixed - eta*C isolates the compact path, which is only a few percent of `mixed`
     at default initialisation."""

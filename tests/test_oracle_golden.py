@@ -114,7 +114,7 @@ def test_layer_matches_reference_module(name, tag):
 
 
 def test_layer_config1_matches_reference_module():
-    """BASELINE configuration 1: dim 384, 6 heads, rank 32, x [4,196,384] FP32, seed 0."""
+    """The reference's CPU-runnable small case: dim 384, 6 heads, rank 32, x [4,196,384] FP32, seed 0."""
     from memsolve_b200 import MemSolve, MemSolveConfig
 
     g = load_golden("layer_config1.npz")
