@@ -49,7 +49,8 @@ typedef enum ms_status {
   MS_ERR_DEVICE = 5,           /* current device is not sm_100-class                            */
   MS_ERR_ODD_HEAD_DIM = 6,     /* rotary tables given with an odd head dimension                */
   MS_ERR_STATIC_SCRATCH = 7,   /* shape too large for the built-in scratch of ms_stats_forward_static */
-  MS_ERR_DEBUG_SHAPE = 8       /* an FP32 debug entry point was called with a shape its kernel does not take */
+  MS_ERR_DEBUG_SHAPE = 8,      /* an FP32 debug entry point was called with a shape its kernel does not take */
+  MS_ERR_LINEAR_SHAPE = 9      /* ms_linear_forward: in_features % 64, out_features % 128 or alignment not met  */
 } ms_status;
 
 /* Capacity, in floats, of the scratch buffer compiled into the library for
@@ -118,6 +119,20 @@ int ms_device_error(void);
  * NCCL all-reduce this path replaces (integrations/distributed.py:47-50 of the reference) waits
  * without a limit; a kernel that spins forever would hang the GPU for every other user of it. */
 int ms_set_peer_wait_ms(int milliseconds);
+
+/*
+ * Projection with the reference's fused epilogue (memsolve/ball/cuda.py:418-708 `_biased_gemm` / `_wide_gemm`,
+ * forward of `tensor_core_linear`, memsolve/ball/reference.py:191-269):
+ *   out[m, n] = output_mask[m] ? (input_mask[m] ? sum_k x[m, k] weight[n, k] : 0) + bias[n] : 0
+ * x bf16 [rows, in_features], weight bf16 [out_features, in_features] (row-major, as nn.Linear stores it),
+ * bias f32 [out_features] or NULL, masks one byte per row (0 = masked) or NULL, out bf16 [rows, out_features].
+ * BF16 products, FP32 accumulation, FP32 bias, one BF16 rounding; masked input rows may hold anything (NaN
+ * included), masked output rows are exactly zero.  tcgen05 GEMM (TMA-staged operands, accumulators in tensor
+ * memory); returns MS_ERR_LINEAR_SHAPE for shapes it does not take.
+ */
+int ms_linear_forward(int64_t rows, int32_t in_features, int32_t out_features, const void* x, const void* weight,
+                      const float* bias, const uint8_t* input_mask, const uint8_t* output_mask, void* out,
+                      void* stream);
 
 /* Bytes of scratch the stats/compact calls need for this shape (partials of the token
  * reduction and backward intermediates).  Same workspace serves forward and backward; it must be

@@ -36,6 +36,8 @@ int launch_token_backward(const ms_shape&, const Plan&, const void* projected, c
                           const float* sin, const float* counts, const ms_tape&, const void* gram_grad,
                           const void* cross_grad, void* dprojected, const CoreAdjoint* core, cudaStream_t);
 int stats_tc_group_heads(int rank);
+int launch_linear_tc(long rows, int in_features, int out_features, const void* x, const void* weight, const float* bias,
+                     const unsigned char* input_mask, const unsigned char* output_mask, void* out, cudaStream_t);
 int launch_readout_tc(const ms_shape&, const Plan&, const void* projected, const float* cos, const float* sin,
                       const float* counts, const ms_tape&, void* mixed, float* debug, cudaStream_t);
 int launch_token_backward_tc(const ms_shape&, const Plan&, const void* projected, const void* dy, const float* cos,
@@ -316,6 +318,9 @@ const char* ms_status_string(int status) {
     case MS_ERR_LAUNCH: return "a CUDA kernel launch failed";
     case MS_ERR_DEVICE: return "the current CUDA device is not an sm_100-class GPU";
     case MS_ERR_ODD_HEAD_DIM: return "rotary content requires an even head dimension";
+    case MS_ERR_LINEAR_SHAPE:
+      return "ms_linear_forward takes in_features a multiple of 64, out_features a multiple of 128 and 16-byte aligned "
+             "pointers";
     case MS_ERR_DEBUG_SHAPE:
       return "the FP32 debug entry points cover the tensor-core (tcgen05) kernels only: head dimension 64, rank 16, "
              "32 or 64, 16-byte aligned pointers";
@@ -335,6 +340,16 @@ int ms_device_error(void) {
   if (cudaMemcpy(&value, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
   if (value != 0) cudaMemset(word, 0, sizeof(int));
   return value;
+}
+
+int ms_linear_forward(int64_t rows, int32_t in_features, int32_t out_features, const void* x, const void* weight,
+                      const float* bias, const uint8_t* input_mask, const uint8_t* output_mask, void* out,
+                      void* stream) {
+  MS_TRY(device_status());
+  if (!x || !weight || !out || rows <= 0 || in_features <= 0 || out_features <= 0) return MS_ERR_INVALID_ARGUMENT;
+  const int r = launch_linear_tc((long)rows, in_features, out_features, x, weight, bias, input_mask, output_mask, out,
+                                 static_cast<cudaStream_t>(stream));
+  return r == -1 ? MS_ERR_LINEAR_SHAPE : r;
 }
 
 int ms_set_peer_wait_ms(int milliseconds) {

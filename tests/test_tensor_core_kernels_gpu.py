@@ -185,6 +185,51 @@ def test_tcgen05_statistics_all_ranks_in_child_process():
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-2000:]
 
 
+@pytest.mark.parametrize("rows,in_features,out_features,bias,masks", [
+    (4096, 768, 1152, False, False), (1000, 768, 768, True, True), (130, 128, 128, True, False),
+    (777, 256, 384, False, True), (32768, 768, 1152, True, True)])
+def test_tcgen05_linear_forward(cuda_mod, rows, in_features, out_features, bias, masks):
+    """`ms_linear_forward` against the same contraction in FP32 on the BF16 operands: products and bias in FP32,
+    one BF16 rounding (<= 1 BF16 ulp apart from the FP32 result rounded once: relative L2 <= 2e-3, which is the
+    rounding itself), masked output rows exactly zero, masked input rows give exactly the rounded bias even when
+    they hold NaN."""
+    lib = cuda_mod._LIB
+    gen = torch.Generator().manual_seed(rows + out_features)
+    x = torch.randn(rows, in_features, generator=gen).bfloat16().cuda()
+    w = (torch.randn(out_features, in_features, generator=gen) * 0.05).bfloat16().cuda()
+    b = torch.randn(out_features, generator=gen).cuda() if bias else None
+    in_mask = out_mask = None
+    if masks:
+        in_mask = (torch.rand(rows, generator=gen) > 0.2).cuda()
+        out_mask = (torch.rand(rows, generator=gen) > 0.2).cuda()
+        x[~in_mask] = float("nan")
+    out = torch.full((rows, out_features), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ptr = cuda_mod._ptr
+    status = lib.ms_linear_forward(rows, in_features, out_features, x.data_ptr(), w.data_ptr(), ptr(b), ptr(in_mask),
+                                   ptr(out_mask), out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert status == 0
+    torch.cuda.synchronize()
+    assert lib.ms_device_error() == 0
+    xin = x.float() if in_mask is None else torch.where(in_mask[:, None], x.float(), torch.zeros((), device="cuda"))
+    want = xin @ w.float().t()
+    if b is not None:
+        want = want + b
+    if out_mask is not None:
+        want = torch.where(out_mask[:, None], want, torch.zeros((), device="cuda"))
+    assert torch.isfinite(out.float()).all()
+    err = rel_l2(out, want)
+    print(f"linear {rows}x{in_features}x{out_features}: {err:.2e}")
+    assert err <= 2e-3
+    assert float((out.float() - want.bfloat16().float()).abs().max()) <= 2.0 ** -6 * float(want.abs().max())
+    if masks:
+        assert torch.count_nonzero(out[~out_mask]) == 0
+        only_bias = out_mask & ~in_mask
+        expect = torch.zeros(out_features, device="cuda") if b is None else b
+        assert torch.equal(out[only_bias], expect.bfloat16().expand(int(only_bias.sum()), -1))
+    assert lib.ms_linear_forward(rows, in_features + 8, out_features, x.data_ptr(), w.data_ptr(), None, None, None,
+                                 out.data_ptr(), None) == 9
+
+
 def test_debug_entry_rejects_other_shapes(cuda_mod):
     lib = cuda_mod._LIB
     proj, base, eta_raw, counts, cos, sin, dy = _random_case(5, 1, 600, 2, 48, 64)
