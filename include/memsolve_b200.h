@@ -209,7 +209,22 @@ int ms_readout(const ms_shape* shape, const void* projected, const float* cos, c
 int ms_readout_debug(const ms_shape* shape, const void* projected, const float* cos, const float* sin,
                      const float* counts, const ms_tape* tape, void* mixed, float* mixed_f32, void* stream);
 
-/* Whole forward on one rank: core + stats + compact + readout (no collective). */
+/*
+ * Readout for a sequence with no more tokens than the rank (N <= r), after ms_mix_forward on the same shape:
+ * mixed = rot^-1(eta S^-1 rot(C) + A_raw Wc / sqrt(n)) with S = I_N + A_raw A_raw^T / n, the token-space form of
+ * the eta term (reference: memsolve/ball/cuda.py:3230-3926, its `short_*` kernels).  For such shapes
+ * ms_mix_forward leaves the core part Wc = T^T F Z in tape->coeff (not T^T (F - eta I) Z), which is what this
+ * entry point and ms_mix_backward expect; ms_readout on that tape would miss the eta term.  Other shapes:
+ * MS_ERR_INVALID_ARGUMENT.
+ */
+int ms_readout_short(const ms_shape* shape, const void* projected, const float* cos, const float* sin,
+                     const float* counts, const ms_tape* tape, void* mixed, void* stream);
+
+/*
+ * Whole forward on one rank: core + stats + compact + readout (no collective).  With tokens <= rank the eta
+ * term is evaluated in token space (see ms_readout_short): in rank space it is a difference of nearly equal
+ * quantities when the relations are strong.
+ */
 int ms_mix_forward(const ms_shape* shape, const void* projected, const float* base_raw,
                    const float* eta_raw, const float* cos, const float* sin, const float* counts,
                    void* workspace, size_t workspace_bytes, const ms_tape* tape, void* mixed,

@@ -68,6 +68,7 @@ _SIGNATURES = {
     "ms_compact_forward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, ctypes.c_size_t, _P,
                                           ctypes.POINTER(_Tape), _P]),
     "ms_readout": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, ctypes.POINTER(_Tape), _P, _P]),
+    "ms_readout_short": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, ctypes.POINTER(_Tape), _P, _P]),
     "ms_mix_forward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t,
                                       ctypes.POINTER(_Tape), _P, _P]),
     "ms_stats_backward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, _P, _P, _P, _P, ctypes.c_size_t, _P, _P]),
@@ -240,6 +241,7 @@ class _RecomputeSpec(NamedTuple):
     rotary_cos: torch.Tensor | None
     rotary_sin: torch.Tensor | None
     shape: tuple
+    short: bool = False   # single-rank forward over no more tokens than the rank (token-space eta term)
 
 
 class _RecomputeScopeState:
@@ -372,14 +374,17 @@ def _mix_forward(projected, base, raw, counts, sequence_parallel, cos, sin):
     return mixed, tape, dims
 
 
-def _readout(projected, tape: _TapeTensors, dims, counts, cos, sin) -> torch.Tensor:
+def _readout(projected, tape: _TapeTensors, dims, counts, cos, sin, short: bool = False) -> torch.Tensor:
+    """Rebuild ``mixed`` from the compact tape.  ``short``: the tape comes from a single-rank forward over no more
+    tokens than the rank, whose coefficient tensor holds the core part only (``ms_readout_short``)."""
     batch, length, heads, rank, head_dim, comp, rows = dims
     shape = _Shape(*dims, 0)
     device = projected.device
     with torch.cuda.device(device):
         mixed = torch.empty(batch, length, heads * head_dim, device=device, dtype=torch.bfloat16)
         tape_c = tape.as_struct()
-        _check(_LIB.ms_readout(ctypes.byref(shape), projected.data_ptr(), _ptr(cos), _ptr(sin), _ptr(counts),
+        entry = _LIB.ms_readout_short if short else _LIB.ms_readout
+        _check(entry(ctypes.byref(shape), projected.data_ptr(), _ptr(cos), _ptr(sin), _ptr(counts),
                                ctypes.byref(tape_c), mixed.data_ptr(), _stream(device)), "readout")
     return mixed
 
@@ -451,7 +456,8 @@ class _NoFrameMix(torch.autograd.Function):
         scope = getattr(_RECOMPUTE_LOCAL, "active", None)
         if scope is not None and (scope.policy is True or (scope.policy == "auto" and projected.shape[1] > 512)):
             scope.spec = _RecomputeSpec(
-                projected.detach(), _TapeTensors(*(t.detach() for t in tape)), counts, rotary_cos, rotary_sin, dims)
+                projected.detach(), _TapeTensors(*(t.detach() for t in tape)), counts, rotary_cos, rotary_sin, dims,
+                not _sp_active(sequence_parallel) and dims[1] <= dims[3])
         return mixed
 
     @staticmethod
@@ -815,6 +821,7 @@ class _RecomputeOutputLinear(torch.autograd.Function):
         ctx.save_for_backward(weight_bf16, output_mask, bias, spec.projected, *spec.tape, *extra)
         ctx.flags = (spec.counts is not None, spec.rotary_cos is not None)
         ctx.dims = spec.shape
+        ctx.short = spec.short
         ctx.value_dtype, ctx.weight_dtype = mixed.dtype, weight.dtype
         return _linear_forward(mixed, weight_bf16, bias, output_dtype, output_mask, None)
 
@@ -828,7 +835,7 @@ class _RecomputeOutputLinear(torch.autograd.Function):
         counts = rest.pop(0) if ctx.flags[0] else None
         cos, sin = (rest[0], rest[1]) if ctx.flags[1] else (None, None)
         need_dw = ctx.needs_input_grad[1]
-        mixed = _readout(projected, tape, ctx.dims, counts, cos, sin) if need_dw else None
+        mixed = _readout(projected, tape, ctx.dims, counts, cos, sin, ctx.short) if need_dw else None
         needs = (ctx.needs_input_grad[0], need_dw, bias is not None and ctx.needs_input_grad[2])
         gv, gw, gb = _linear_backward(grad_output, mixed, weight_bf16, output_mask, None, needs,
                                       ctx.value_dtype, ctx.weight_dtype, bias)

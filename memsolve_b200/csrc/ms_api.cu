@@ -38,6 +38,12 @@ int launch_token_backward(const ms_shape&, const Plan&, const void* projected, c
 int stats_tc_group_heads(int rank);
 int launch_linear_tc(long rows, int in_features, int out_features, const void* x, const void* weight, const float* bias,
                      const unsigned char* input_mask, const unsigned char* output_mask, void* out, cudaStream_t);
+int launch_short_readout(const ms_shape&, const Plan&, const void* projected, const float* cos, const float* sin,
+                         const float* counts, const ms_tape&, void* mixed, cudaStream_t);
+int launch_short_backward(const ms_shape&, const Plan&, const void* projected, const void* dy, const float* cos,
+                          const float* sin, const float* counts, const ms_tape&, const void* gram_grad,
+                          const void* cross_grad, void* dprojected, float* de_short, float grad_scale, float* d_eta_raw,
+                          cudaStream_t);
 int launch_readout_tc(const ms_shape&, const Plan&, const void* projected, const float* cos, const float* sin,
                       const float* counts, const ms_tape&, void* mixed, float* debug, cudaStream_t);
 int launch_token_backward_tc(const ms_shape&, const Plan&, const void* projected, const void* dy, const float* cos,
@@ -289,6 +295,8 @@ static Workspace carve(void* ws, const Plan& p) {
 }
 
 static bool is16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+// no more tokens than the rank: ms_mix_forward / ms_mix_backward evaluate the eta term in token space
+static bool short_sequence(const ms_shape& s) { return s.tokens <= s.rank; }
 
 }  // namespace ms
 
@@ -463,6 +471,18 @@ int ms_readout(const ms_shape* shape, const void* projected, const float* cos, c
   return launch_readout(*shape, plan, projected, cos, sin, counts, *tape, mixed, static_cast<cudaStream_t>(stream));
 }
 
+int ms_readout_short(const ms_shape* shape, const void* projected, const float* cos, const float* sin,
+                     const float* counts, const ms_tape* tape, void* mixed, void* stream) {
+  MS_TRY(check_shape(shape));
+  MS_TRY(device_status());
+  if (!projected || !mixed || !tape || !tape->eta || !tape->coeff) return MS_ERR_INVALID_ARGUMENT;
+  if (shape->rotary_rows && (!cos || !sin)) return MS_ERR_INVALID_ARGUMENT;
+  if (!short_sequence(*shape)) return MS_ERR_INVALID_ARGUMENT;
+  const Plan plan = make_plan(*shape);
+  return launch_short_readout(*shape, plan, projected, cos, sin, counts, *tape, mixed,
+                              static_cast<cudaStream_t>(stream));
+}
+
 int ms_readout_debug(const ms_shape* shape, const void* projected, const float* cos, const float* sin,
                      const float* counts, const ms_tape* tape, void* mixed, float* mixed_f32, void* stream) {
   MS_TRY(check_shape(shape));
@@ -496,6 +516,14 @@ int ms_mix_forward(const ms_shape* shape, const void* projected, const float* ba
   // the per-head core (eta, F) is computed by spare CTAs of the statistics grid
   MS_TRY(launch_stats(*shape, stats_plan, false, projected, nullptr, cos, sin, w.partials, nullptr, base_raw,
                       eta_raw, tape, st));
+  if (short_sequence(*shape)) {
+    // no more tokens than the rank: the compact stage keeps the core part only (eta = 0) and the eta term is
+    // evaluated in token space, where it does not cancel (see ms_short.cu)
+    ms_tape core_only = *tape;
+    core_only.eta = nullptr;
+    MS_TRY(launch_compact_forward(*shape, plan, counts, w.partials, false, core_only, st));
+    return launch_short_readout(*shape, plan, projected, cos, sin, counts, *tape, mixed, st);
+  }
   // the two launches below start while the kernel ahead of them drains (see launch_kernel)
   ChainScope chain(chaining_allowed());
   MS_TRY(launch_compact_forward(*shape, plan, counts, w.partials, false, *tape, st));
@@ -664,6 +692,17 @@ int ms_mix_backward(const ms_shape* shape, const void* projected, const void* dy
   const Plan plan = backward_plan(make_plan(*shape));
   const Workspace w = carve(workspace, plan);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (short_sequence(*shape)) {
+    if (!projected || !dy || !dprojected || !tape->coeff) return MS_ERR_INVALID_ARGUMENT;
+    ms_tape core_only = *tape;
+    core_only.eta = nullptr;
+    MS_TRY(launch_compact_backward(*shape, plan, counts, w.partials, w.de_partials, false, core_only, w.hmat,
+                                   w.de_sys, gram_grad, cross_grad, st));
+    // d_base from the core part; its d_eta_raw is replaced by the token-space one below
+    MS_TRY(launch_core_backward(*shape, base_raw, w.hmat, w.de_sys, *tape, 1.0f, d_base_raw, d_eta_raw, st));
+    return launch_short_backward(*shape, plan, projected, dy, cos, sin, counts, *tape, gram_grad, cross_grad,
+                                 dprojected, w.de_partials, 1.0f, d_eta_raw, st);
+  }
   ChainScope chain(chaining_allowed());
   MS_TRY(launch_compact_backward(*shape, plan, counts, w.partials, w.de_partials, false, *tape, w.hmat,
                                  w.de_sys, gram_grad, cross_grad, st));

@@ -292,7 +292,7 @@ compact_forward_kernel(const CompactFwdParams p) {
   const float inv_n = packed ? 1.f : inv_rn(n);
   const float inv_s = packed ? 1.f : inv_sqrt_rn(n);
   const float* src = p.partials + (size_t)sys * nch * p.pf;
-  const float eta = p.eta[h];
+  const float eta = p.eta ? p.eta[h] : 0.f;   // null: the short-sequence path adds the eta term in token space
   const int d = p.head_dim;
   const bool staged = p.staged != 0;
 
@@ -470,7 +470,7 @@ compact_backward_kernel(const CompactBwdParams p) {
   const float n = p.counts ? p.counts[b] : (float)p.tokens;
   const float inv_s = packed ? 1.f : inv_sqrt_rn(n);
   const float* src = p.partials + (size_t)sys * nch * p.pf;
-  const float eta = p.eta[h];
+  const float eta = p.eta ? p.eta[h] : 0.f;   // null: the short-sequence path adds the eta term in token space
   const int d = p.head_dim;
   const bool staged = p.staged != 0;
 

@@ -199,22 +199,37 @@ def test_numerical_boundaries(cuda_mod, rel_scale, eta_value, base_scale):
         assert errs["deta"] <= 3e-2, errs
 
 
-@pytest.mark.parametrize("length", [1, 2, 7, 16])
+@pytest.mark.parametrize("length", [1, 2, 7, 16, 17])
 @pytest.mark.parametrize("rank", [16, 64])
 @pytest.mark.parametrize("rel_scale", [1.0, 32.0])
 def test_fewer_tokens_than_rank(cuda_mod, length, rank, rel_scale):
     """N <= r, where the reference switches to a token-space system (memsolve/ball/cuda.py:3230-3926; its tests
-    use N = 1 and 7, tests/cuda/test_fast_path.py:1805-1838).  Here the rank-space kernels serve every length:
-    the Gram matrix then has rank N < r and I + G stays well conditioned (eigenvalues 1 and 1 + sigma^2), also
-    under strong relations (entries of A up to ~100), which is what this case pins down: forward 5e-3,
-    gradients 3e-2, both core modes' shared path, rotary on."""
+    use N = 1 and 7, tests/cuda/test_fast_path.py:1805-1838).  Under strong relations (entries of A up to ~100)
+    and N < r the rank-space form eta (C - P P^T C) of the output is a small difference of large terms, and so is
+    d_eta = <dY, C> - tr dF (the rank-space kernels lose d_eta_raw there: 8e-2 at N = 2, rank 64, relations x 32).
+    The library evaluates the eta term in token space for N <= r, so every gradient holds the same limits as at
+    long lengths: forward 5e-3, dprojected 5e-3 (3e-2 under strong relations, BF16 storage of large values),
+    parameters 3e-2.  N = 17 at rank 16 is the first length of the rank-space path."""
     case = _random_case(3300 + 7 * length + rank, 2, length, 2, rank, 64, rot=True, rel_scale=rel_scale,
                         base_scale=0.3)
-    # Under strong relations and N < r the output eta (C - P P^T C) is a small difference of large terms, and so is
-    # d_eta = <dY, C> - tr dF: the rank-space kernels then lose d_eta_raw (8e-2 at N = 2, rank 64, relations x 32),
-    # while output, dprojected and d_core_base_raw hold their limits.  That one gradient is checked at 2e-1 there.
-    _assert_case(cuda_mod, *case, gproj=5e-3 if rel_scale == 1.0 else 3e-2, gpar=3e-2 if rel_scale == 1.0 else 2e-1,
+    _assert_case(cuda_mod, *case, gproj=5e-3 if rel_scale == 1.0 else 3e-2, gpar=3e-2,
                  tag=f"short N={length} r{rank} relations x{rel_scale}")
+
+
+@pytest.mark.parametrize("rank,d,length,rot,complement,masked", [
+    (32, 64, 32, True, False, False),    # N = r exactly
+    (64, 64, 64, True, False, True),     # N = r = 64, padded samples
+    (48, 72, 5, False, False, False),    # rank 48, two channel blocks (64 + 8), no rotary
+    (16, 130, 9, True, False, True),     # three channel blocks, the last of 2 channels
+    (32, 64, 3, True, True, False),      # complement mode: F = 0, the eta term is all there is
+    (64, 128, 40, True, True, True),
+])
+def test_short_sequences_shapes(cuda_mod, rank, d, length, rot, complement, masked):
+    """The token-space kernels over the shape envelope of the library: all ranks, head widths that are not a
+    multiple of 64, padded samples (counts), complement mode, with and without rotary tables."""
+    case = list(_random_case(4100 + rank + d + length, 3, length, 2, rank, d, rot=rot, rel_scale=8.0,
+                             base_scale=0.3, comp=complement, masked=masked))
+    _assert_case(cuda_mod, *case, gproj=2e-2, gpar=3e-2, tag=f"short shapes r{rank} d{d} N={length}")
 
 
 def test_correction_term_alone(cuda_mod):

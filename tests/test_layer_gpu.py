@@ -123,16 +123,18 @@ def test_layer_config1_shape_matches_reference_module(mods):
     assert all(errs[k] <= 3e-2 for k in ("dx", "dw_bc", "dw_o", "deta")), errs
 
 
-def test_recompute_policies_give_identical_results(mods):
+@pytest.mark.parametrize("length", [700, 9])
+def test_recompute_policies_give_identical_results(mods, length):
     """Dropping and rebuilding the mixed readout leaves outputs and gradients bit-identical
-    (tests/cuda/test_fast_path.py:2130-2202)."""
+    (tests/cuda/test_fast_path.py:2130-2202); 9 tokens take the token-space kernels for N <= rank, whose
+    rebuilt readout is a separate entry point (ms_readout_short)."""
     MemSolve, MemSolveConfig, _, _ = mods
     torch.manual_seed(5)
     base = MemSolve(MemSolveConfig(dim=128, num_heads=2, rank=32, rotary=True, bias=True)).cuda()
     with torch.no_grad():
         base.core_base_raw.normal_(std=0.1)
-    x0 = torch.randn(2, 700, 128, device="cuda").bfloat16()
-    dout = torch.randn(2, 700, 128, device="cuda").bfloat16()
+    x0 = torch.randn(2, length, 128, device="cuda").bfloat16()
+    dout = torch.randn(2, length, 128, device="cuda").bfloat16()
     results = []
     for policy in (False, True, "auto"):
         layer = copy.deepcopy(base)
