@@ -50,7 +50,7 @@ typedef enum ms_status {
   MS_ERR_ODD_HEAD_DIM = 6,     /* rotary tables given with an odd head dimension                */
   MS_ERR_STATIC_SCRATCH = 7,   /* shape too large for the built-in scratch of ms_stats_forward_static */
   MS_ERR_DEBUG_SHAPE = 8,      /* an FP32 debug entry point was called with a shape its kernel does not take */
-  MS_ERR_LINEAR_SHAPE = 9      /* ms_linear_forward: in_features % 64, out_features % 128 or alignment not met  */
+  MS_ERR_LINEAR_SHAPE = 9      /* ms_linear_*: feature counts or alignment outside the tcgen05 kernels' envelope */
 } ms_status;
 
 /* Capacity, in floats, of the scratch buffer compiled into the library for
@@ -133,6 +133,30 @@ int ms_set_peer_wait_ms(int milliseconds);
 int ms_linear_forward(int64_t rows, int32_t in_features, int32_t out_features, const void* x, const void* weight,
                       const float* bias, const uint8_t* input_mask, const uint8_t* output_mask, void* out,
                       void* stream);
+
+/*
+ * Input gradient of the projection (memsolve/ball/cuda.py:959-1041, backward of `tensor_core_linear`):
+ *   dx[m, k] = (input_mask[m] && output_mask[m]) ? sum_n dy[m, n] weight[n, k] : 0        (one BF16 rounding)
+ * dy bf16 [rows, out_features], weight bf16 [out_features, in_features] as in ms_linear_forward (read in place, no
+ * transposed copy), masks as there or NULL, dx bf16 [rows, in_features].  Envelope: out_features a multiple of 64,
+ * in_features a multiple of 128, 16-byte aligned pointers; otherwise MS_ERR_LINEAR_SHAPE.
+ */
+int ms_linear_input_grad(int64_t rows, int32_t in_features, int32_t out_features, const void* dy, const void* weight,
+                         const uint8_t* input_mask, const uint8_t* output_mask, void* dx, void* stream);
+
+/*
+ * Weight and bias gradients of the projection in one pass over dy and x (the reference's fused dW + db GEMM,
+ * csrc/ball/binding.cpp:114-196):
+ *   dweight[n, k] = sum_m dy[m, n] x[m, k]        dbias[n] = sum_m dy[m, n]        (FP32 sums and results)
+ * x bf16 [rows, in_features], dy bf16 [rows, out_features], dweight f32 [out_features, in_features], dbias f32
+ * [out_features] or NULL.  The rows are split over several CTAs per output tile; the partial tiles go through
+ * `workspace` (ms_linear_weight_grad_workspace bytes, 16-byte aligned) and are added in a fixed order, so the result
+ * is the same bits on every run.  No row masks: mask the operands first.  Envelope: in_features and out_features
+ * multiples of 128; otherwise MS_ERR_LINEAR_SHAPE (and a workspace size of 0).
+ */
+size_t ms_linear_weight_grad_workspace(int64_t rows, int32_t in_features, int32_t out_features);
+int ms_linear_weight_grad(int64_t rows, int32_t in_features, int32_t out_features, const void* x, const void* dy,
+                          float* dweight, float* dbias, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Bytes of scratch the stats/compact calls need for this shape (partials of the token
  * reduction and backward intermediates).  Same workspace serves forward and backward; it must be

@@ -60,6 +60,10 @@ _SIGNATURES = {
     "ms_device_error": (ctypes.c_int, []),
     "ms_set_peer_wait_ms": (ctypes.c_int, [ctypes.c_int]),
     "ms_linear_forward": (ctypes.c_int, [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, _P, _P, _P, _P, _P, _P, _P]),
+    "ms_linear_input_grad": (ctypes.c_int, [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, _P, _P, _P, _P, _P, _P]),
+    "ms_linear_weight_grad_workspace": (ctypes.c_size_t, [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32]),
+    "ms_linear_weight_grad": (ctypes.c_int, [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, _P, _P, _P, _P, _P,
+                                             ctypes.c_size_t, _P]),
     "ms_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(_Shape)]),
     "ms_packed_stats_floats": (ctypes.c_size_t, [ctypes.POINTER(_Shape), ctypes.c_int]),
     "ms_core_forward": (ctypes.c_int, [ctypes.POINTER(_Shape), _P, _P, ctypes.POINTER(_Tape), _P]),
@@ -702,6 +706,52 @@ def _fused_linear_forward(flat, weight_bf16, bias, output_mask, input_mask):
     return out
 
 
+def _fused_linear_input_grad(flat_g, weight_bf16, output_mask, input_mask):
+    """dx = masks * (flat_g @ weight) as one tcgen05 kernel (the weight is read in place as an N-major operand), or
+    None when the shape is not one the kernel takes."""
+    rows, out_features = flat_g.shape
+    in_features = weight_bf16.shape[1]
+    if (_LIB is None or not flat_g.is_cuda or flat_g.dtype != torch.bfloat16 or not flat_g.is_contiguous()
+            or not weight_bf16.is_contiguous() or out_features % 64 or in_features % 128 or rows == 0):
+        return None
+    masks = []
+    for mask in (input_mask, output_mask):
+        masks.append(None if mask is None else mask.reshape(-1).to(torch.bool).contiguous())
+    dx = torch.empty(rows, in_features, device=flat_g.device, dtype=torch.bfloat16)
+    with torch.cuda.device(flat_g.device):
+        status = _LIB.ms_linear_input_grad(rows, in_features, out_features, flat_g.data_ptr(), weight_bf16.data_ptr(),
+                                           _ptr(masks[0]), _ptr(masks[1]), dx.data_ptr(), _stream(flat_g.device))
+    if status == 9:      # MS_ERR_LINEAR_SHAPE
+        return None
+    _check(status, "linear input gradient")
+    return dx
+
+
+def _fused_linear_weight_grad(flat_g, flat_v, need_db):
+    """(dW, db) = (flat_g^T @ flat_v, column sums of flat_g) in FP32 by one tcgen05 kernel with a fixed summation
+    order, or None when the shape is not one the kernel takes.  No row masks."""
+    rows, out_features = flat_g.shape
+    in_features = flat_v.shape[1]
+    if (_LIB is None or not flat_g.is_cuda or flat_g.dtype != torch.bfloat16 or flat_v.dtype != torch.bfloat16
+            or not flat_g.is_contiguous() or not flat_v.is_contiguous() or out_features % 128 or in_features % 128
+            or rows == 0):
+        return None
+    nbytes = int(_LIB.ms_linear_weight_grad_workspace(rows, in_features, out_features))
+    if nbytes == 0:
+        return None
+    device = flat_g.device
+    ws = torch.empty(nbytes, device=device, dtype=torch.uint8)
+    dw = torch.empty(out_features, in_features, device=device, dtype=torch.float32)
+    db = torch.empty(out_features, device=device, dtype=torch.float32) if need_db else None
+    with torch.cuda.device(device):
+        status = _LIB.ms_linear_weight_grad(rows, in_features, out_features, flat_v.data_ptr(), flat_g.data_ptr(),
+                                            dw.data_ptr(), _ptr(db), ws.data_ptr(), nbytes, _stream(device))
+    if status == 9:
+        return None
+    _check(status, "linear weight gradient")
+    return dw, db
+
+
 def _linear_forward(value, weight_bf16, bias, output_dtype, output_mask, input_mask):
     """BF16 x BF16 with FP32 accumulation, FP32 bias, row masks, one rounding."""
     wanted = _OWN_LINEAR == "1" or (_OWN_LINEAR != "0" and (bias is not None or output_mask is not None
@@ -727,13 +777,37 @@ def _linear_forward(value, weight_bf16, bias, output_dtype, output_mask, input_m
 
 def _linear_backward(grad_output, value, weight_bf16, output_mask, input_mask, needs, value_dtype,
                      weight_dtype, bias, out_features=None):
+    """Gradients of the projection.  The library's tcgen05 kernels are taken where they fuse passes that would
+    otherwise run separately (measured at 32768 rows on one B200, L2 flushed): the input gradient when row masks are
+    present (57 against 50 us of cuBLAS for the bare product, but the masks are then free), and dW + db in one pass
+    when a bias gradient is wanted and there are no masks (80 / 104 us against 91 / 110 us of cuBLAS plus the column
+    sums; without a bias cuBLAS' bare dW is faster at 48 / 69 us).  MEMSOLVE_TCGEN05_LINEAR=1 takes them whenever the
+    shape allows, =0 never."""
     need_dx, need_dw, need_db = needs
     if out_features is None:
         out_features = weight_bf16.shape[0]
     flat_g = grad_output.reshape(-1, out_features)
+    grad_value = grad_weight = grad_bias = None
+    masked = output_mask is not None or input_mask is not None
+    own = _OWN_LINEAR != "0" and flat_g.dtype == torch.bfloat16
+    if need_dx and own and value_dtype == torch.bfloat16 and (masked or _OWN_LINEAR == "1"):
+        dx = _fused_linear_input_grad(flat_g.contiguous(), weight_bf16, output_mask, input_mask)
+        if dx is not None:
+            grad_value = dx.reshape(grad_output.shape[:-1] + (weight_bf16.shape[1],))
+            need_dx = False
+    if (need_dw or need_db) and own and not masked and (need_db or _OWN_LINEAR == "1") and value is not None \
+            and value.dtype == torch.bfloat16:
+        fused = _fused_linear_weight_grad(flat_g.contiguous(), value.reshape(-1, value.shape[-1]).contiguous(), need_db)
+        if fused is not None:
+            if need_dw:
+                grad_weight = fused[0].to(weight_dtype)
+            if need_db:
+                grad_bias = fused[1].to(device=bias.device, dtype=bias.dtype)
+            need_dw = need_db = False
+    if not (need_dx or need_dw or need_db):
+        return grad_value, grad_weight, grad_bias
     flat_g = _masked_rows(flat_g, None if output_mask is None else output_mask.reshape(-1))
     g_bf16 = flat_g if flat_g.dtype == torch.bfloat16 else flat_g.to(torch.bfloat16)
-    grad_value = grad_weight = grad_bias = None
     if need_dw:
         flat_v = value.reshape(-1, value.shape[-1])
         flat_v = _masked_rows(flat_v, None if input_mask is None else input_mask.reshape(-1)).to(torch.bfloat16)
@@ -803,11 +877,186 @@ def tensor_core_linear(value, weight, bias=None, *, output_dtype=None, fuse_weig
     if value.shape[-1] != weight.shape[-1]:
         raise ValueError(
             f"tensor_core_linear input and weight features must agree, got {value.shape[-1]} and {weight.shape[-1]}")
+    if torch.compiler.is_compiling():
+        # traced: one registered operator per direction (the kernels are reached through ctypes, which a tracer
+        # cannot follow)
+        flat = torch.ops.memsolve_b200.tensor_core_linear(
+            value.reshape(-1, value.shape[-1]), weight, bias, None if output_mask is None else output_mask.reshape(-1),
+            None if input_mask is None else input_mask.reshape(-1), _DTYPE_CODES[output_dtype])
+        return flat.reshape(value.shape[:-1] + (weight.shape[0],))
     out = _TensorCoreLinear.apply(value, weight.detach(), None if bias is None else bias.detach(), output_dtype,
                                   output_mask, input_mask)
     if torch.is_grad_enabled() and (weight.requires_grad or (bias is not None and bias.requires_grad)):
         out = _ParameterGradients.apply(out, value.detach(), weight, bias, output_mask, input_mask)
     return out
+
+
+# --------------------------------------------------------------------------------------
+# registered operators of the projections and of the output projection with readout recompute
+# (memsolve/ball/cuda.py:1104-1304 `memsolve::tensor_core_linear[_backward]`, :4422-4882
+# `memsolve::fast_mix_output_linear_fwd/_bwd`): what a traced layer calls, one opaque node per direction
+# --------------------------------------------------------------------------------------
+_DTYPE_CODES = {None: 0, torch.float32: 1, torch.bfloat16: 2, torch.float16: 3}
+_CODE_DTYPES = {code: dtype for dtype, code in _DTYPE_CODES.items()}
+
+
+@torch.library.custom_op("memsolve_b200::tensor_core_linear", mutates_args=(), device_types="cuda")
+def _tensor_core_linear_op(flat_value: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                           output_mask: Optional[torch.Tensor], input_mask: Optional[torch.Tensor],
+                           out_dtype_code: int) -> torch.Tensor:
+    """out = output_mask * (input_mask * flat_value @ weight^T + bias): BF16 multiplicands, FP32 sums, one rounding."""
+    weight_bf16 = weight if weight.dtype == torch.bfloat16 else weight.detach().to(torch.bfloat16)
+    return _linear_forward(flat_value, weight_bf16, bias, _CODE_DTYPES[out_dtype_code], output_mask,
+                           input_mask).contiguous()
+
+
+@_tensor_core_linear_op.register_fake
+def _tensor_core_linear_fake(flat_value, weight, bias, output_mask, input_mask, out_dtype_code):
+    dtype = _CODE_DTYPES[out_dtype_code] or torch.float32
+    return flat_value.new_empty((flat_value.shape[0], weight.shape[0]), dtype=dtype)
+
+
+@torch.library.custom_op("memsolve_b200::tensor_core_linear_backward", mutates_args=(), device_types="cuda")
+def _tensor_core_linear_bwd_op(grad_output: torch.Tensor, flat_value: torch.Tensor, weight: torch.Tensor,
+                               bias: Optional[torch.Tensor], output_mask: Optional[torch.Tensor],
+                               input_mask: Optional[torch.Tensor], need_dx: bool, need_dw: bool,
+                               need_db: bool) -> List[torch.Tensor]:
+    """[d flat_value, d weight, d bias]; a gradient that is not needed comes back as an empty tensor."""
+    weight_bf16 = weight if weight.dtype == torch.bfloat16 else weight.detach().to(torch.bfloat16)
+    gv, gw, gb = _linear_backward(grad_output.contiguous(), flat_value, weight_bf16, output_mask, input_mask,
+                                  (need_dx, need_dw, need_db and bias is not None), flat_value.dtype, weight.dtype,
+                                  bias)
+    empty = lambda: grad_output.new_empty((0,))   # noqa: E731  (outputs of an operator may not alias each other)
+    return [empty() if gv is None else gv.contiguous(), empty() if gw is None else gw.contiguous(),
+            empty() if gb is None else gb.contiguous()]
+
+
+@_tensor_core_linear_bwd_op.register_fake
+def _tensor_core_linear_bwd_fake(grad_output, flat_value, weight, bias, output_mask, input_mask, need_dx, need_dw,
+                                 need_db):
+    empty = lambda: grad_output.new_empty((0,))   # noqa: E731
+    return [torch.empty_like(flat_value) if need_dx else empty(),
+            torch.empty_like(weight) if need_dw else empty(),
+            torch.empty_like(bias) if need_db and bias is not None else empty()]
+
+
+def _tensor_core_linear_setup(ctx, inputs, output):
+    flat_value, weight, bias, output_mask, input_mask, _code = inputs
+    ctx.save_for_backward(flat_value, weight, bias, output_mask, input_mask)
+
+
+def _tensor_core_linear_autograd(ctx, grad_output):
+    flat_value, weight, bias, output_mask, input_mask = ctx.saved_tensors
+    needs = ctx.needs_input_grad
+    gv, gw, gb = torch.ops.memsolve_b200.tensor_core_linear_backward(
+        grad_output, flat_value, weight, bias, output_mask, input_mask, needs[0], needs[1],
+        bias is not None and needs[2])
+    return (gv if needs[0] else None, gw if needs[1] else None, gb if bias is not None and needs[2] else None,
+            None, None, None)
+
+
+torch.library.register_autograd("memsolve_b200::tensor_core_linear", _tensor_core_linear_autograd,
+                                setup_context=_tensor_core_linear_setup)
+
+
+@torch.library.custom_op("memsolve_b200::fast_mix_output_linear_fwd", mutates_args=(), device_types="cuda")
+def _fast_mix_out_linear_fwd_op(projected: torch.Tensor, core_base_raw: torch.Tensor, eta_raw: torch.Tensor,
+                                valid_counts: Optional[torch.Tensor], rotary_cos: Optional[torch.Tensor],
+                                rotary_sin: Optional[torch.Tensor], weight: torch.Tensor,
+                                bias: Optional[torch.Tensor], output_mask: Optional[torch.Tensor],
+                                out_dtype_code: int) -> List[torch.Tensor]:
+    """Mixer and output projection as one node that keeps the compact tape instead of `mixed`: returns the
+    projected output and the tape (eta, eta_slope, core_map, core_info, inverse, state, coeff)."""
+    require_available()
+    _validate_no_frame_inputs(projected, core_base_raw, eta_raw, valid_counts)
+    mixed, tape, _ = _mix_forward(projected, core_base_raw, eta_raw, valid_counts, None, rotary_cos, rotary_sin)
+    weight_bf16 = weight if weight.dtype == torch.bfloat16 else weight.detach().to(torch.bfloat16)
+    out = _linear_forward(mixed, weight_bf16, bias, _CODE_DTYPES[out_dtype_code], output_mask, None)
+    return [out.contiguous(), *tape]
+
+
+@_fast_mix_out_linear_fwd_op.register_fake
+def _fast_mix_out_linear_fwd_fake(projected, core_base_raw, eta_raw, valid_counts, rotary_cos, rotary_sin, weight,
+                                  bias, output_mask, out_dtype_code):
+    fake = _fast_mix_fwd_fake(projected, core_base_raw, eta_raw, valid_counts, rotary_cos, rotary_sin)
+    dtype = _CODE_DTYPES[out_dtype_code] or torch.float32
+    out = projected.new_empty((projected.shape[0], projected.shape[1], weight.shape[0]), dtype=dtype)
+    return [out, *fake[1:]]
+
+
+@torch.library.custom_op("memsolve_b200::fast_mix_output_linear_bwd", mutates_args=(), device_types="cuda")
+def _fast_mix_out_linear_bwd_op(grad_output: torch.Tensor, projected: torch.Tensor, core_base_raw: torch.Tensor,
+                                eta_raw: torch.Tensor, valid_counts: Optional[torch.Tensor],
+                                rotary_cos: Optional[torch.Tensor], rotary_sin: Optional[torch.Tensor],
+                                weight: torch.Tensor, bias: Optional[torch.Tensor],
+                                output_mask: Optional[torch.Tensor], tape: List[torch.Tensor], need_dw: bool,
+                                need_db: bool) -> List[torch.Tensor]:
+    """[d projected, d core_base_raw, d eta_raw, d weight, d bias]: the readout is rebuilt from the tape for the
+    weight gradient, then the mixer's backward runs on d mixed = grad_output @ weight."""
+    dims = _dims_of(projected, core_base_raw, rotary_cos)
+    tape_t = _TapeTensors(*tape)
+    weight_bf16 = weight if weight.dtype == torch.bfloat16 else weight.detach().to(torch.bfloat16)
+    short = dims[1] <= dims[3]
+    mixed = _readout(projected, tape_t, dims, valid_counts, rotary_cos, rotary_sin, short) if need_dw else None
+    d_mixed, gw, gb = _linear_backward(grad_output.contiguous(), mixed, weight_bf16, output_mask, None,
+                                       (True, need_dw, need_db and bias is not None), torch.bfloat16, weight.dtype,
+                                       bias)
+    del mixed
+    d_mixed = d_mixed.contiguous()
+    d_projected, d_base, d_raw = _mix_backward(projected, d_mixed, core_base_raw, eta_raw, valid_counts, None,
+                                               rotary_cos, rotary_sin, tape_t, dims)
+    if d_base is None:
+        d_base = torch.zeros_like(core_base_raw)
+    empty = lambda: grad_output.new_empty((0,))   # noqa: E731
+    return [d_projected, d_base, d_raw, empty() if gw is None else gw.contiguous(),
+            empty() if gb is None else gb.contiguous()]
+
+
+@_fast_mix_out_linear_bwd_op.register_fake
+def _fast_mix_out_linear_bwd_fake(grad_output, projected, core_base_raw, eta_raw, valid_counts, rotary_cos, rotary_sin,
+                                  weight, bias, output_mask, tape, need_dw, need_db):
+    empty = lambda: grad_output.new_empty((0,))   # noqa: E731
+    return [torch.empty_like(projected), torch.empty_like(core_base_raw), torch.empty_like(eta_raw),
+            torch.empty_like(weight) if need_dw else empty(),
+            torch.empty_like(bias) if need_db and bias is not None else empty()]
+
+
+def _fast_mix_out_linear_setup(ctx, inputs, output):
+    projected, base, raw, counts, cos, sin, weight, bias, output_mask, _code = inputs
+    ctx.flags = (counts is not None, cos is not None, bias is not None, output_mask is not None)
+    extra = [t for t in (counts, cos, sin, bias, output_mask) if t is not None]
+    ctx.save_for_backward(projected, base, raw, weight, *output[1:], *extra)
+
+
+def _fast_mix_out_linear_autograd(ctx, grads):
+    saved = list(ctx.saved_tensors)
+    projected, base, raw, weight = saved[:4]
+    tape, rest = saved[4:11], saved[11:]
+    has_counts, has_rotary, has_bias, has_mask = ctx.flags
+    counts = rest.pop(0) if has_counts else None
+    cos, sin = (rest.pop(0), rest.pop(0)) if has_rotary else (None, None)
+    bias = rest.pop(0) if has_bias else None
+    output_mask = rest.pop(0) if has_mask else None
+    needs = ctx.needs_input_grad
+    d_projected, d_base, d_raw, gw, gb = torch.ops.memsolve_b200.fast_mix_output_linear_bwd(
+        grads[0], projected, base, raw, counts, cos, sin, weight, bias, output_mask, tape, needs[6],
+        has_bias and needs[7])
+    return (d_projected, d_base, d_raw, None, None, None, gw if needs[6] else None,
+            gb if has_bias and needs[7] else None, None, None)
+
+
+torch.library.register_autograd("memsolve_b200::fast_mix_output_linear_fwd", _fast_mix_out_linear_autograd,
+                                setup_context=_fast_mix_out_linear_setup)
+
+
+def _traced_mix_output_linear(projected, core_base_raw, eta_raw, valid_counts, rotary_cos, rotary_sin, weight, bias,
+                              output_dtype, output_mask):
+    """The mixer followed by the output projection for a traced layer that recomputes the readout in backward."""
+    mask = None if output_mask is None else output_mask.reshape(-1)
+    return torch.ops.memsolve_b200.fast_mix_output_linear_fwd(
+        projected, core_base_raw, eta_raw, valid_counts, rotary_cos, rotary_sin, weight, bias, mask,
+        _DTYPE_CODES[output_dtype])[0]
+
 
 
 class _RecomputeOutputLinear(torch.autograd.Function):

@@ -260,15 +260,20 @@ class MemSolve(nn.Module):
             x, self.w_bc.weight, self.w_bc.bias, output_dtype=torch.bfloat16,
             fuse_weight_bias_grad=True, output_mask=mask, input_mask=mask,
         )
+        core_base = (self.core_base_raw if self.core_base_raw is not None
+                     else self.eta_raw.new_empty((config.num_heads, config.rank, 0)))
         policy: Literal["auto"] | bool = (
             self._recompute_readout if torch.is_grad_enabled() and self.w_o.weight.requires_grad else False
         )
         if policy == "auto":
             policy = length > 512
-        if torch.compiler.is_compiling():
-            policy = False   # traced graphs keep `mixed`; the readout is recomputed on the eager path only
-        core_base = (self.core_base_raw if self.core_base_raw is not None
-                     else self.eta_raw.new_empty((config.num_heads, config.rank, 0)))
+        if torch.compiler.is_compiling() and policy is not False:
+            if sequence_parallel is None:
+                # traced: mixer + output projection as one registered operator that keeps the compact tape
+                return cuda_backend._traced_mix_output_linear(
+                    projected, core_base, self.eta_raw, valid_counts, rotary_cos, rotary_sin, self.w_o.weight,
+                    self.w_o.bias, x.dtype, mask)
+            policy = False
         mix_kwargs = dict(sequence_parallel=sequence_parallel, rotary_cos=rotary_cos, rotary_sin=rotary_sin)
         if policy is False:
             mixed = cuda_backend.fast_mix(projected, core_base, self.eta_raw, valid_counts, **mix_kwargs)

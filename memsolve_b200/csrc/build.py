@@ -21,7 +21,7 @@ OBJ_DIR = os.path.join(LIB_DIR, "obj")
 LIB_NAME = "memsolve_equilibrium_sm100.so"
 SOURCES = ["ms_api.cu", "ms_stats.cu", "ms_compact.cu", "ms_token.cu", "ms_readout_tma.cu", "ms_token_bwd_tma.cu",
            "ms_stats_tma.cu", "ms_exchange.cu", "ms_token_bwd_tc.cu", "ms_readout_tc.cu", "ms_stats_tc.cu", "ms_linear_tc.cu",
-           "ms_short.cu"]
+           "ms_short.cu", "ms_linear_wgrad_tc.cu"]
 HEADERS = ["ms_common.cuh", "ms_core.cuh", "ms_tma.cuh", "ms_frag.cuh", "ms_tc.cuh", os.path.join("..", "..", "include", "memsolve_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -44,6 +44,11 @@ int launch_short_backward(const ms_shape&, const Plan&, const void* projected, c
                           const float* sin, const float* counts, const ms_tape&, const void* gram_grad,
                           const void* cross_grad, void* dprojected, float* de_short, float grad_scale, float* d_eta_raw,
                           cudaStream_t);
+int launch_linear_input_grad_tc(long rows, int in_features, int out_features, const void* dy, const void* weight,
+                                const unsigned char* input_mask, const unsigned char* output_mask, void* dx, cudaStream_t);
+size_t linear_wgrad_workspace_bytes(long rows, int in_features, int out_features);
+int launch_linear_wgrad_tc(long rows, int in_features, int out_features, const void* x, const void* dy, float* dw, float* db,
+                           void* workspace, size_t workspace_bytes, cudaStream_t);
 int launch_readout_tc(const ms_shape&, const Plan&, const void* projected, const float* cos, const float* sin,
                       const float* counts, const ms_tape&, void* mixed, float* debug, cudaStream_t);
 int launch_token_backward_tc(const ms_shape&, const Plan&, const void* projected, const void* dy, const float* cos,
@@ -327,8 +332,8 @@ const char* ms_status_string(int status) {
     case MS_ERR_DEVICE: return "the current CUDA device is not an sm_100-class GPU";
     case MS_ERR_ODD_HEAD_DIM: return "rotary content requires an even head dimension";
     case MS_ERR_LINEAR_SHAPE:
-      return "ms_linear_forward takes in_features a multiple of 64, out_features a multiple of 128 and 16-byte aligned "
-             "pointers";
+      return "the tcgen05 projection kernels take in_features a multiple of 64 (128 for the gradients), out_features a "
+             "multiple of 128 (64 for the input gradient) and 16-byte aligned pointers";
     case MS_ERR_DEBUG_SHAPE:
       return "the FP32 debug entry points cover the tensor-core (tcgen05) kernels only: head dimension 64, rank 16, "
              "32 or 64, 16-byte aligned pointers";
@@ -357,6 +362,28 @@ int ms_linear_forward(int64_t rows, int32_t in_features, int32_t out_features, c
   if (!x || !weight || !out || rows <= 0 || in_features <= 0 || out_features <= 0) return MS_ERR_INVALID_ARGUMENT;
   const int r = launch_linear_tc((long)rows, in_features, out_features, x, weight, bias, input_mask, output_mask, out,
                                  static_cast<cudaStream_t>(stream));
+  return r == -1 ? MS_ERR_LINEAR_SHAPE : r;
+}
+
+int ms_linear_input_grad(int64_t rows, int32_t in_features, int32_t out_features, const void* dy, const void* weight,
+                         const uint8_t* input_mask, const uint8_t* output_mask, void* dx, void* stream) {
+  MS_TRY(device_status());
+  if (!dy || !weight || !dx || rows <= 0 || in_features <= 0 || out_features <= 0) return MS_ERR_INVALID_ARGUMENT;
+  const int r = launch_linear_input_grad_tc((long)rows, in_features, out_features, dy, weight, input_mask, output_mask, dx,
+                                            static_cast<cudaStream_t>(stream));
+  return r == -1 ? MS_ERR_LINEAR_SHAPE : r;
+}
+
+size_t ms_linear_weight_grad_workspace(int64_t rows, int32_t in_features, int32_t out_features) {
+  return linear_wgrad_workspace_bytes((long)rows, in_features, out_features);
+}
+
+int ms_linear_weight_grad(int64_t rows, int32_t in_features, int32_t out_features, const void* x, const void* dy,
+                          float* dweight, float* dbias, void* workspace, size_t workspace_bytes, void* stream) {
+  MS_TRY(device_status());
+  if (!x || !dy || !dweight || rows <= 0 || in_features <= 0 || out_features <= 0) return MS_ERR_INVALID_ARGUMENT;
+  const int r = launch_linear_wgrad_tc((long)rows, in_features, out_features, x, dy, dweight, dbias, workspace,
+                                       workspace_bytes, static_cast<cudaStream_t>(stream));
   return r == -1 ? MS_ERR_LINEAR_SHAPE : r;
 }
 

@@ -57,7 +57,9 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int
                : "memory");
 }
 
-template <int BN>
+// BNM: the second operand is stored [k][n] with n contiguous (the input-gradient product dY W, W = [out, in]):
+// its tile is BN / 64 boxes of 64 k-rows x 64 columns, read by the MMA as an N-major operand.
+template <int BN, bool BNM>
 __global__ void __launch_bounds__(kLinThreads, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_out, const LinearTcParams p) {
@@ -112,15 +114,25 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           const uint32_t st = ring + s * Cfg::STAGE, bar = bar_full + 8 * s;
           mbar_expect_tx(bar, Cfg::STAGE);
           tma_load_2d(st, &map_x, kb * 64, m * 128, bar);
-          tma_load_2d(st + Cfg::A_TILE, &map_w, kb * 64, n * BN, bar);
+          if (BNM) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(st + Cfg::A_TILE + j * 8192, &map_w, n * BN + j * 64, kb * 64, bar);
+          } else {
+            tma_load_2d(st + Cfg::A_TILE, &map_w, kb * 64, n * BN, bar);
+          }
         }
       }
       if (!ok) atomicExch(p.error, kErrBarrierTimeout);
     }
   } else if (warp == 5) {
     // ---------------------------------------------------------------- MMA issuer
-    constexpr uint32_t IDESC = tc::idesc_bf16(128, BN, false);
+    constexpr uint32_t IDESC = tc::idesc_bf16(128, BN, BNM);
     constexpr uint32_t HI = tc::desc_hi_k_major(128);
+    constexpr uint32_t HI_B = BNM ? tc::desc_hi_n_major_128() : HI;
+    // N-major tile: 8192 bytes between its 64-column blocks, 16 k-rows (2048 bytes) per MMA
+    constexpr uint32_t B_FIX = BNM ? (((8192u >> 4) << 16) - (1u << 16)) : 0u;
+    constexpr uint32_t B_STEP = BNM ? 128u : 2u;
     const uint32_t ring_lo = tc::desc_lo_k_major(ring);
     int it = 0, local = 0;
     for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++local) {
@@ -135,10 +147,11 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         ok = lin_wait(bar_full + 8 * s, (it / S) & 1);
         if (!ok) break;
         tc::fence_after_sync();
-        const uint32_t a_lo = ring_lo + (uint32_t)(s * (Cfg::STAGE >> 4)), b_lo = a_lo + (Cfg::A_TILE >> 4);
+        const uint32_t a_lo = ring_lo + (uint32_t)(s * (Cfg::STAGE >> 4)), b_lo = a_lo + (Cfg::A_TILE >> 4) + B_FIX;
         if (tc::elect_one()) {
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) tc::mma_ss_raw<HI, HI, IDESC>(d, a_lo + ks * 2, b_lo + ks * 2, (kb | ks) != 0);
+          for (int ks = 0; ks < 4; ++ks)
+            tc::mma_ss_raw<HI, HI_B, IDESC>(d, a_lo + ks * 2, b_lo + ks * B_STEP, (kb | ks) != 0);
           tc::mma_commit_raw(bar_empty + 8 * s);
           if (kb == p.k_blocks - 1) tc::mma_commit_raw(bar_acc_full + 8 * buf);
         }
@@ -211,7 +224,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   if (warp == 5) tc::tmem_free(tmem, Cfg::TMEM_COLS);
 }
 
-template <int BN>
+// BNM false: out[rows, out_features] = x[rows, in_features] weight[out_features, in_features]^T
+// BNM true:  out[rows, out_features] = x[rows, in_features] weight[in_features, out_features]
+template <int BN, bool BNM>
 static int launch_linear_tc_bn(long rows, int in_features, int out_features, const void* x, const void* weight,
                                const float* bias, const unsigned char* input_mask, const unsigned char* output_mask,
                                void* out, cudaStream_t st) {
@@ -223,7 +238,12 @@ static int launch_linear_tc_bn(long rows, int in_features, int out_features, con
     const uint32_t box[2] = {64, 128};
     if (encode_tensor_map(&map_x, const_cast<void*>(x), 2, 2, dims, str, box, Swizzle::B128)) return MS_ERR_LAUNCH;
   }
-  {
+  if (BNM) {
+    const uint64_t dims[2] = {(uint64_t)out_features, (uint64_t)in_features};
+    const uint64_t str[1] = {(uint64_t)out_features * 2};
+    const uint32_t box[2] = {64, 64};
+    if (encode_tensor_map(&map_w, const_cast<void*>(weight), 2, 2, dims, str, box, Swizzle::B128)) return MS_ERR_LAUNCH;
+  } else {
     const uint64_t dims[2] = {(uint64_t)in_features, (uint64_t)out_features};
     const uint64_t str[1] = {(uint64_t)in_features * 2};
     const uint32_t box[2] = {64, (uint32_t)BN};
@@ -244,7 +264,7 @@ static int launch_linear_tc_bn(long rows, int in_features, int out_features, con
   const long total = (long)p.m_tiles * p.n_tiles;
   long ctas = sm_count();
   if (ctas > total) ctas = total;
-  auto kern = linear_tc_kernel<BN>;
+  auto kern = linear_tc_kernel<BN, BNM>;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Cfg::TOTAL)) return MS_ERR_LAUNCH;
   launch_kernel(kern, dim3((unsigned)ctas), dim3(kLinThreads), Cfg::TOTAL, st, map_x, map_w, map_out, p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
@@ -257,10 +277,28 @@ int launch_linear_tc(long rows, int in_features, int out_features, const void* x
   if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out)) & 15u) != 0)
     return -1;
   if (out_features % 256 == 0)
-    return launch_linear_tc_bn<256>(rows, in_features, out_features, x, weight, bias, input_mask, output_mask, out, st);
+    return launch_linear_tc_bn<256, false>(rows, in_features, out_features, x, weight, bias, input_mask, output_mask, out, st);
   if (out_features % 192 == 0)
-    return launch_linear_tc_bn<192>(rows, in_features, out_features, x, weight, bias, input_mask, output_mask, out, st);
-  return launch_linear_tc_bn<128>(rows, in_features, out_features, x, weight, bias, input_mask, output_mask, out, st);
+    return launch_linear_tc_bn<192, false>(rows, in_features, out_features, x, weight, bias, input_mask, output_mask, out, st);
+  return launch_linear_tc_bn<128, false>(rows, in_features, out_features, x, weight, bias, input_mask, output_mask, out, st);
+}
+
+// dx[rows, in_features] = row masks * (dy[rows, out_features] weight[out_features, in_features]), one BF16 rounding: the
+// input gradient of the projection (memsolve/ball/cuda.py:959-1041).  A row is zero when either mask clears it (a
+// cleared output row had no influence on the loss, a cleared input row was not read).  MS_OK / error, or -1 outside
+// the envelope (out_features a multiple of 64, in_features a multiple of 128, 16-byte aligned pointers).
+int launch_linear_input_grad_tc(long rows, int in_features, int out_features, const void* dy, const void* weight,
+                                const unsigned char* input_mask, const unsigned char* output_mask, void* dx,
+                                cudaStream_t st) {
+  if (rows <= 0 || rows > 0x7fffff00L || out_features <= 0 || (out_features % 64) != 0 || (in_features % 128) != 0) return -1;
+  if (((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(dx)) & 15u) != 0)
+    return -1;
+  // the contraction runs over out_features, the result has in_features columns
+  if (in_features % 256 == 0)
+    return launch_linear_tc_bn<256, true>(rows, out_features, in_features, dy, weight, nullptr, input_mask, output_mask, dx, st);
+  if (in_features % 192 == 0)
+    return launch_linear_tc_bn<192, true>(rows, out_features, in_features, dy, weight, nullptr, input_mask, output_mask, dx, st);
+  return launch_linear_tc_bn<128, true>(rows, out_features, in_features, dy, weight, nullptr, input_mask, output_mask, dx, st);
 }
 
 }  // namespace ms

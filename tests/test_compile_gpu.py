@@ -95,3 +95,86 @@ def test_compile_fullgraph_layer():
     assert torch.equal(y0, y1) and torch.equal(dx0, dx1)
     for a, b in zip(g0, g1):
         assert torch.equal(a, b)
+
+
+def test_projection_operators_opcheck():
+    """`memsolve_b200::tensor_core_linear` and `memsolve_b200::fast_mix_output_linear_fwd` (the reference registers
+    `memsolve::tensor_core_linear[_backward]` and `memsolve::fast_mix_output_linear_fwd/_bwd`,
+    memsolve/ball/cuda.py:1104-1304, 4422-4882): schema, fake kernels and autograd registration."""
+    from memsolve_b200.ball import cuda
+    cuda.load()
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(200, 128, generator=g).bfloat16().cuda().requires_grad_()
+    w = (torch.randn(256, 128, generator=g) * 0.05).cuda().requires_grad_()
+    b = torch.randn(256, generator=g).cuda().requires_grad_()
+    mask = (torch.rand(200, generator=g) > 0.2).cuda()
+    checks = ("test_schema", "test_faketensor", "test_autograd_registration")
+    torch.library.opcheck(torch.ops.memsolve_b200.tensor_core_linear.default, (x, w, b, mask, mask, 2),
+                          test_utils=checks)
+    torch.library.opcheck(torch.ops.memsolve_b200.tensor_core_linear.default, (x, w, None, None, None, 1),
+                          test_utils=checks)
+    projected, base, raw, cos, sin, _ = _inputs(length=96)
+    wo = (torch.randn(128, 3 * 64, generator=g) * 0.05).cuda().requires_grad_()
+    bo = torch.randn(128, generator=g).cuda().requires_grad_()
+    args = (projected.requires_grad_(), base.requires_grad_(), raw.requires_grad_(), None, cos, sin, wo, bo, None, 2)
+    torch.library.opcheck(torch.ops.memsolve_b200.fast_mix_output_linear_fwd.default, args, test_utils=checks)
+
+
+@pytest.mark.parametrize("bias,masked", [(False, False), (True, True)])
+def test_projection_operator_equals_eager_path(bias, masked):
+    """The registered projection against the eager autograd nodes: identical bits for the output and all three
+    gradients, with and without bias and row masks (which select the fused tcgen05 kernels)."""
+    from memsolve_b200.ball import cuda
+    cuda.load()
+    g = torch.Generator().manual_seed(4)
+    x0 = torch.randn(3, 130, 128, generator=g).bfloat16().cuda()
+    w0 = (torch.randn(256, 128, generator=g) * 0.05).cuda()
+    b0 = torch.randn(256, generator=g).cuda() if bias else None
+    mask = (torch.rand(3, 130, generator=g) > 0.2).cuda() if masked else None
+    upstream = torch.randn(3, 130, 256, generator=g).bfloat16().cuda()
+
+    def run(traced):
+        x, w = x0.clone().requires_grad_(), w0.clone().requires_grad_()
+        b = None if b0 is None else b0.clone().requires_grad_()
+        if traced:
+            flat_mask = None if mask is None else mask.reshape(-1)
+            out = torch.ops.memsolve_b200.tensor_core_linear(x.reshape(-1, 128), w, b, flat_mask, flat_mask, 2)
+            out = out.reshape(3, 130, 256)
+        else:
+            out = cuda.tensor_core_linear(x, w, b, output_dtype=torch.bfloat16, output_mask=mask, input_mask=mask)
+        out.backward(upstream)
+        return [out.detach(), x.grad, w.grad] + ([] if b is None else [b.grad])
+
+    for a, c in zip(run(False), run(True)):
+        assert torch.equal(a, c)
+
+
+@pytest.mark.parametrize("length", [700, 9])
+def test_compile_fullgraph_layer_with_readout_recompute(length):
+    """A traced layer with recompute_readout=True runs mixer + output projection as one registered operator that
+    keeps the compact tape; outputs and gradients equal the eager layer's bit for bit.  Bias on: the projections take
+    the fused tcgen05 kernels, which a tracer reaches only through the registered operators."""
+    from memsolve_b200 import MemSolve, MemSolveConfig
+    from memsolve_b200.ball import cuda
+    cuda.load()
+    torch.manual_seed(7)
+    layer = MemSolve(MemSolveConfig(128, 2, rank=16, rotary=True, bias=True, recompute_readout=True)).cuda()
+    with torch.no_grad():
+        layer.core_base_raw.normal_(std=0.1)
+    x = torch.randn(2, length, 128).bfloat16().cuda()
+    upstream = torch.randn(2, length, 128).bfloat16().cuda()
+    factors = layer._rotary_factors(x, None, None, None)
+
+    def run(module):
+        layer.zero_grad(set_to_none=True)
+        xin = x.clone().requires_grad_()
+        out = module(xin, implementation="cuda", rotary_factors=factors)
+        out.backward(upstream)
+        return out.detach(), xin.grad, [p.grad.clone() for p in layer.parameters()]
+
+    y0, dx0, g0 = run(layer)
+    compiled = torch.compile(layer, fullgraph=True, backend="aot_eager")
+    y1, dx1, g1 = run(compiled)
+    assert torch.equal(y0, y1) and torch.equal(dx0, dx1)
+    for a, b in zip(g0, g1):
+        assert torch.equal(a, b)
