@@ -517,6 +517,22 @@ def _fast_mix_fwd_fake(projected, core_base_raw, eta_raw, valid_counts, rotary_c
             projected.new_empty((batch, heads, 2, rank, dpad))]
 
 
+@torch.library.custom_op("memsolve_b200::fast_mix_infer", mutates_args=(), device_types="cuda")
+def _fast_mix_infer_op(projected: torch.Tensor, core_base_raw: torch.Tensor, eta_raw: torch.Tensor,
+                       valid_counts: Optional[torch.Tensor], rotary_cos: Optional[torch.Tensor],
+                       rotary_sin: Optional[torch.Tensor]) -> torch.Tensor:
+    """mixed alone, for graphs traced without gradients (memsolve/ball/cuda.py:4164-4201): the tape is dropped."""
+    require_available()
+    _validate_no_frame_inputs(projected, core_base_raw, eta_raw, valid_counts)
+    return _mix_forward(projected, core_base_raw, eta_raw, valid_counts, None, rotary_cos, rotary_sin)[0]
+
+
+@_fast_mix_infer_op.register_fake
+def _fast_mix_infer_fake(projected, core_base_raw, eta_raw, valid_counts, rotary_cos, rotary_sin):
+    batch, length, heads, _rank, head_dim, _comp, _rows = _dims_of(projected, core_base_raw, rotary_cos)
+    return projected.new_empty((batch, length, heads * head_dim))
+
+
 @torch.library.custom_op("memsolve_b200::fast_mix_bwd", mutates_args=(), device_types="cuda")
 def _fast_mix_bwd_op(projected: torch.Tensor, gradient: torch.Tensor, core_base_raw: torch.Tensor,
                      eta_raw: torch.Tensor, valid_counts: Optional[torch.Tensor],
@@ -610,6 +626,9 @@ def fast_mix(
         raise ValueError("the MemSolve CUDA fast path does not support gradients for valid_counts")
     if torch.compiler.is_compiling() and sequence_parallel is None:
         # traced: one registered operator (its kernel repeats the checks below when it runs)
+        if not (torch.is_grad_enabled() and any(t.requires_grad for t in (projected, core_base_raw, eta_raw))):
+            return torch.ops.memsolve_b200.fast_mix_infer(projected, core_base_raw, eta_raw, valid_counts,
+                                                          rotary_cos, rotary_sin)
         return torch.ops.memsolve_b200.fast_mix_fwd(projected, core_base_raw, eta_raw, valid_counts,
                                                     rotary_cos, rotary_sin)[0]
     require_available()

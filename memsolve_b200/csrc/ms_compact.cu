@@ -194,8 +194,10 @@ __device__ __forceinline__ void stage_partials(uint32_t dst, const float* src, i
 }
 
 // acc[e] = sum over chunks, in chunk order, of src[c * stride + off[e]] for four entries at a time
-// (independent chains, pointers advanced by the stride); entries with ok[e] false give zero
-template <class T>
+// (independent chains, pointers advanced by the stride); entries with ok[e] false give zero.  DEPTH chunks
+// are fetched per round: two from shared memory, eight from global memory, where a round costs a trip to L2
+// and a long sequence leaves some twenty chunks per system (the additions keep their chunk order either way).
+template <int DEPTH, class T>
 __device__ __forceinline__ void sum_chunks4(const T* src, int stride, int nch, const int (&off)[4],
                                             const bool (&ok)[4], float (&acc)[4]) {
   const T* ptr[4];
@@ -205,22 +207,30 @@ __device__ __forceinline__ void sum_chunks4(const T* src, int stride, int nch, c
     acc[e] = 0.f;
   }
   int c = 0;
-  for (; c + 2 <= nch; c += 2) {
-    float v[2][4];
+  for (; c + DEPTH <= nch; c += DEPTH) {
+    float v[DEPTH][4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      v[0][e] = ptr[e][0];
-      v[1][e] = ptr[e][stride];
-      ptr[e] += 2 * stride;
-    }
+    for (int k = 0; k < DEPTH; ++k)
 #pragma unroll
-    for (int k = 0; k < 2; ++k)
+      for (int e = 0; e < 4; ++e) v[k][e] = ptr[e][(size_t)k * stride];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ptr[e] += (size_t)DEPTH * stride;
+#pragma unroll
+    for (int k = 0; k < DEPTH; ++k)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[e] += v[k][e];
   }
   if (c < nch) {
+    float v[DEPTH][4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) acc[e] += ptr[e][0];
+    for (int k = 0; k < DEPTH; ++k)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[k][e] = c + k < nch ? ptr[e][(size_t)k * stride] : 0.f;
+#pragma unroll
+    for (int k = 0; k < DEPTH; ++k)
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (c + k < nch) acc[e] += v[k][e];
   }
 #pragma unroll
   for (int e = 0; e < 4; ++e) acc[e] = ok[e] ? acc[e] : 0.f;
@@ -327,8 +337,8 @@ compact_forward_kernel(const CompactFwdParams p) {
       off[e] = i0 + e * kCompactThreads;
       valid[e] = off[e] < R * R;
     }
-    if (staged) sum_chunks4(stage, p.pf, nch, off, valid, acc);
-    else sum_chunks4(src, p.pf, nch, off, valid, acc);
+    if (staged) sum_chunks4<2>(stage, p.pf, nch, off, valid, acc);
+    else sum_chunks4<8>(src, p.pf, nch, off, valid, acc);
 #pragma unroll
     for (int e = 0; e < 4; ++e)
       if (valid[e]) gs[off[e]] = acc[e] * inv_n;
@@ -356,8 +366,8 @@ compact_forward_kernel(const CompactFwdParams p) {
         valid[e] = c < dv;
         off[e] = R * R + row * d + d0 + (valid[e] ? c : 0);
       }
-      if (staged) sum_chunks4(stage, p.pf, nch, off, valid, acc);
-      else sum_chunks4(src, p.pf, nch, off, valid, acc);
+      if (staged) sum_chunks4<2>(stage, p.pf, nch, off, valid, acc);
+      else sum_chunks4<8>(src, p.pf, nch, off, valid, acc);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = i0 + e * kCompactThreads;
@@ -529,8 +539,8 @@ compact_backward_kernel(const CompactBwdParams p) {
         off[e] = row * d + d0 + (valid[e] ? c : 0);
         zv[e] = valid[e] ? p.state[(size_t)sys * R * d + off[e]] : 0.f;
       }
-      if (staged) sum_chunks4(stage, p.pf, nch, off, valid, acc);
-      else sum_chunks4(src, p.pf, nch, off, valid, acc);
+      if (staged) sum_chunks4<2>(stage, p.pf, nch, off, valid, acc);
+      else sum_chunks4<8>(src, p.pf, nch, off, valid, acc);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = i0 + e * kCompactThreads;

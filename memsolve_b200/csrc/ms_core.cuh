@@ -75,6 +75,25 @@ __device__ __forceinline__ void core_mm_tn(double (&acc)[4][2], const float* At,
   }
 }
 
+// acc[a][b] += sum_{k < r} A(i0 + a, k) B(k, j0 + b js) for FP64 matrices in shared memory with element strides
+// (sai, sak) and (sbk, sbj): either operand may be read transposed
+__device__ __forceinline__ void core_mm44(double (&acc)[4][4], const double* A, int sai, int sak, const double* B,
+                                          int sbk, int sbj, int i0, int j0, int js, int r) {
+#pragma unroll 2
+  for (int k = 0; k < r; ++k) {
+    double a[4], b[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      a[e] = A[(i0 + e) * sai + k * sak];
+      b[e] = B[k * sbk + (j0 + e * js) * sbj];
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+      for (int y = 0; y < 4; ++y) acc[x][y] = fma(a[x], b[y], acc[x][y]);
+  }
+}
+
 // layout of the core forward: NT threads, TPR neighbouring threads share one matrix row
 template <int R, int NT>
 struct CoreDims {
@@ -334,36 +353,57 @@ __device__ __forceinline__ void core_backward_device(const float* __restrict__ b
   }
   if (complement) return;
 
-  // t1 = (F+I)^T dF ;  dJ = -1/2 t1 (F+I)^T
-  for (int i = tid; i < r * r; i += nthreads) {
-    const int row = i / r, col = i - row * r;
-    double acc = 0.0;
-    for (int k = 0; k < r; ++k) acc = fma(pm[k * p + row], dfm[k * p + col], acc);
-    t1[row * p + col] = acc;
+  // t1 = (F+I)^T dF ;  dJ = -1/2 t1 (F+I)^T ;  then L's gradient from S = dJ + dJ^T: FP64 products on 4 x 4
+  // register tiles (rows i0 .. i0 + 3, columns tj + b r/4: the lanes of a warp read neighbouring columns)
+  const int q4 = r / 4, ntiles = q4 * q4;
+  for (int tile = tid; tile < ntiles; tile += nthreads) {
+    const int i0 = (tile / q4) * 4, tj = tile % q4;
+    double acc[4][4] = {};
+    core_mm44(acc, pm, 1, p, dfm, p, 1, i0, tj, q4, r);
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) t1[(i0 + a) * p + tj + b * q4] = acc[a][b];
+  }
+  __syncthreads();
+  for (int tile = tid; tile < ntiles; tile += nthreads) {
+    const int i0 = (tile / q4) * 4, tj = tile % q4;
+    double acc[4][4] = {};
+    core_mm44(acc, t1, p, 1, pm, 1, p, i0, tj, q4, r);
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) dfm[(i0 + a) * p + tj + b * q4] = -0.5 * acc[a][b];   // dJ
   }
   __syncthreads();
   for (int i = tid; i < r * r; i += nthreads) {
     const int row = i / r, col = i - row * r;
-    double acc = 0.0;
-    for (int k = 0; k < r; ++k) acc = fma(t1[row * p + k], pm[col * p + k], acc);
-    dfm[row * p + col] = -0.5 * acc;   // dJ
+    t1[row * p + col] = dfm[row * p + col] + dfm[col * p + row];   // S
   }
   __syncthreads();
-  for (int i = tid; i < r * r; i += nthreads) {
-    const int row = i / r, col = i - row * r;
-    double out;
-    if (row < col) {
-      out = dfm[row * p + col] - dfm[col * p + row];
-    } else {
-      double acc = 0.0;
-      for (int k = col; k < r; ++k) acc = fma(dfm[row * p + k] + dfm[k * p + row], lc[k * p + col], acc);
-      if (row == col) {
-        const float x = base_raw[(size_t)h * r * r + i] + kSoftplusShiftF;
-        acc *= (double)(1.0f / (1.0f + expf(-x)));
+  for (int tile = tid; tile < ntiles; tile += nthreads) {
+    const int i0 = (tile / q4) * 4, tj = tile % q4;
+    double acc[4][4] = {};
+    // L is lower triangular with zeros stored above the diagonal: the full inner range adds nothing for k < col
+    core_mm44(acc, t1, p, 1, lc, p, 1, i0, tj, q4, r);
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int row = i0 + a, col = tj + b * q4;
+        double out;
+        if (row < col) {
+          out = dfm[row * p + col] - dfm[col * p + row];
+        } else {
+          out = acc[a][b];
+          if (row == col) {
+            const float x = base_raw[(size_t)h * r * r + row * r + col] + kSoftplusShiftF;
+            out *= (double)(1.0f / (1.0f + expf(-x)));
+          }
+        }
+        d_base[(size_t)h * r * r + row * r + col] = (float)out * grad_scale;
       }
-      out = acc;
     }
-    d_base[(size_t)h * r * r + i] = (float)out * grad_scale;
   }
 }
 

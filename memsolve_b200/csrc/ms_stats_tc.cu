@@ -48,7 +48,9 @@ struct StatsTcCfg {
   static constexpr int A_TILE = kStTile * ROWS * 2;       // 16 or 32 KB (one or two 64-column tiles)
   static constexpr int A_STAGES = R == 64 ? 2 : 3;
   static constexpr int X_TILE = GRAD ? 32768 : 16384;     // gradient (+ content for <dY, C>) or content
-  static constexpr int X_STAGES = GRAD ? 3 : 4;
+  // an odd ring is shared by the two compute groups, which is only safe together with the low-word ring (see the
+  // waits of the compute warps); without rotation there is none, and room for four stages
+  static constexpr int X_STAGES = (GRAD && ROT) ? 3 : 4;
   // low-word tiles: a deep ring lets a compute group rotate its next unit while the MMAs of its last one run
   static constexpr int LO_STAGES = !ROT ? 0 : (!GRAD ? 4 : (R == 64 ? 2 : 3));
   static constexpr int LO_TILE = 16384;
@@ -272,6 +274,7 @@ stats_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       auto take_tables = [&](int k) {
         bool good = true;
         while (tab_next <= k && good) {
+          uint32_t seen = 0;   // one word of every load below
           good = st_wait(bar_tab_full, tab_next & 1);
           if (good && tab_next == k) {
 #pragma unroll
@@ -280,9 +283,14 @@ stats_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               const float4 cv = ld_shared_f4(tab_buf + off), sv = ld_shared_f4(tab_buf + 16384 + off);
               cs[4 * v] = cv.x; cs[4 * v + 1] = cv.y; cs[4 * v + 2] = cv.z; cs[4 * v + 3] = cv.w;
               sn[4 * v] = sv.x; sn[4 * v + 1] = sv.y; sn[4 * v + 2] = sv.z; sn[4 * v + 3] = sv.w;
+              seen ^= __float_as_uint(cv.w) ^ __float_as_uint(sv.w);
             }
           }
-          if (good) st_arrive(bar_tab_free);
+          if (good) {
+            // the rows must be in registers before the buffer goes back to the table warp's next bulk copy
+            wait_for_loaded(seen, tslot + 8);
+            st_arrive(bar_tab_free);
+          }
           ++tab_next;
         }
         return good;
@@ -295,8 +303,17 @@ stats_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           ok = take_tables(t);
           if (!ok) break;
         }
-        ok = st_wait(bar_xfull + 8 * (j % SX), (j / SX) & 1);
-        if (ok && ROT && j >= SL) ok = st_wait(bar_lofree + 8 * (j % SL), ((j / SL) - 1) & 1);
+        // Order matters.  A parity wait is only meaningful while the waiter is at most one phase behind the
+        // barrier.  With an odd ring the last user of this X slot (unit j - SX) belonged to the OTHER group, so
+        // this group has not observed that phase: were it to test the "full" barrier before that load had landed
+        // (loads complete out of order), the test for unit j would pass at once on the phase before it and the
+        // stale tile would be rotated.  The low-word slot comes back by tcgen05.commit after the MMAs of unit
+        // j - SL, which (MMAs complete in order, SL <= SX) follow the other group's arrival for unit j - SX and
+        // hence its genuine wait for that load: after this wait the barrier cannot be behind.  (Rings whose
+        // length is even are used by one group only and need no such argument.)
+        static_assert(!TRANSFORM || (SX % 2) == 0 || (ROT && SL <= SX), "X ring shared by the two groups");
+        if (ROT && j >= SL) ok = st_wait(bar_lofree + 8 * (j % SL), ((j / SL) - 1) & 1);
+        if (ok) ok = st_wait(bar_xfull + 8 * (j % SX), (j / SX) & 1);
         if (!ok) break;
         float dot = 0.f;
 #pragma unroll

@@ -119,6 +119,23 @@ __device__ __forceinline__ void tma_store_wait_all() {
   asm volatile("cp.async.bulk.wait_group %0;\n" ::"n"(N) : "memory");
 }
 // make generic-proxy writes to shared memory visible to the async proxy (before a TMA store)
+// Make the warp wait until `bits` is in its registers.  ld.shared only ISSUES a read; an mbarrier arrive that follows
+// it in the program can be performed -- and the buffer it releases be overwritten by the producer's next bulk copy --
+// before the data has come back.  (Measured: rotary rows released right after their loads were replaced by the next
+// tile's rows for single threads in about every second launch of 32768 tokens.)  A warp issues in order, so one
+// instruction that consumes a value derived from every load holds back everything after it until the loads have
+// returned.  The store is never taken for real data, and would only touch the scratch word if it were.
+__device__ __forceinline__ void wait_for_loaded(uint32_t bits, uint32_t scratch) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.eq.u32 p, %0, 0x9e3779b9;\n"
+      "@p st.shared.u32 [%1], %0;\n"
+      "}\n" ::"r"(bits),
+      "r"(scratch)
+      : "memory");
+}
+
 __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
 }  // namespace ms

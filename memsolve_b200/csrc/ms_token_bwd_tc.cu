@@ -388,6 +388,7 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     auto take_tables = [&](int k) {
       bool good = true;
       while (tab_next <= k && good) {
+        uint32_t seen = 0;   // one word of every load below
         good = wait_uniform(bar_tab_full, tab_next & 1);
         if (good && tab_next == k) {
 #pragma unroll
@@ -396,9 +397,14 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const float4 cv = ld_shared_f4(tab_buf + off), sv = ld_shared_f4(tab_buf + 16384 + off);
             cs[4 * v] = cv.x; cs[4 * v + 1] = cv.y; cs[4 * v + 2] = cv.z; cs[4 * v + 3] = cv.w;
             sn[4 * v] = sv.x; sn[4 * v + 1] = sv.y; sn[4 * v + 2] = sv.z; sn[4 * v + 3] = sv.w;
+            seen ^= __float_as_uint(cv.w) ^ __float_as_uint(sv.w);
           }
         }
-        if (good) mbar_arrive(bar_tab_free);
+        if (good) {
+          // the rows must be in registers before the buffer goes back to the table warp's next bulk copy
+          wait_for_loaded(seen, tslot + 8);
+          mbar_arrive(bar_tab_free);
+        }
         ++tab_next;
       }
       return good;

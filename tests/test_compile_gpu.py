@@ -52,6 +52,23 @@ def test_opcheck():
                           test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
 
 
+def test_compile_inference_operator():
+    """Traced without gradients the mixer is `memsolve_b200::fast_mix_infer` (no tape kept); same bits as eager."""
+    from memsolve_b200.ball import cuda
+    cuda.load()
+    projected, base, raw, cos, sin, _ = _inputs(length=200)
+    torch.library.opcheck(torch.ops.memsolve_b200.fast_mix_infer.default, (projected, base, raw, None, cos, sin),
+                          test_utils=("test_schema", "test_faketensor"))
+
+    def mix(p, b, r):
+        return cuda.fast_mix(p, b, r, rotary_cos=cos, rotary_sin=sin)
+
+    with torch.no_grad():
+        want = mix(projected, base, raw)
+        got = torch.compile(mix, fullgraph=True, backend="aot_eager")(projected, base, raw)
+    assert torch.equal(want, got)
+
+
 @pytest.mark.parametrize("rotary", [False, True])
 def test_compile_fullgraph_mixer(rotary):
     from memsolve_b200.ball import cuda

@@ -258,6 +258,19 @@ def test_bitwise_repeatability(cuda_mod):
         assert torch.equal(ga, gb)
 
 
+@pytest.mark.parametrize("rank", [32, 64])
+def test_bitwise_repeatability_long_sequence(cuda_mod, rank):
+    """Twelve forward + backward passes over 32768 rotated tokens (the tcgen05 readout, token backward and, at
+    rank 64, statistics kernels, all with TMA-staged rotary rows) give identical bits every time."""
+    case = _random_case(23 + rank, 1, 32768, 12, rank, 64, rot=True)
+    first = _run_fast(cuda_mod, *case)
+    for _ in range(11):
+        again = _run_fast(cuda_mod, *case)
+        assert torch.equal(again[0], first[0])
+        for ga, gb in zip(again[1], first[1]):
+            assert torch.equal(ga, gb)
+
+
 _PLAIN_LAUNCH_CHILD = """
 import sys, torch
 sys.path.insert(0, {root!r}); sys.path.insert(0, {tests!r})

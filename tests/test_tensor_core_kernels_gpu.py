@@ -168,6 +168,34 @@ def test_tcgen05_statistics_stagewise(cuda_mod, rank, rot, length, heads, batch,
     assert all(v <= limit for v in errs.values()), errs
 
 
+@pytest.mark.parametrize("rank", [16, 32, 64])
+def test_tcgen05_statistics_stagewise_repeatable(cuda_mod, rank):
+    """Forty launches of both token reductions over 32768 rotated tokens give the same bits.  The kernels add in a
+    fixed order, so any difference is a synchronisation fault: this is the case that exposed rotary rows handed back
+    to the table warp's next bulk copy while the loads that read them were still in flight (single threads then
+    rotated by the next tile's angles, in about every second launch)."""
+    lib = cuda_mod._LIB
+    proj, base, eta_raw, counts, cos, sin, dy = _random_case(77 + rank, 1, 32768, 12, rank, 64, rot=True)
+    dp, ddy, dcos, dsin = proj.cuda(), dy.cuda().contiguous(), cos.cuda(), sin.cuda()
+    shape = cuda_mod._Shape(1, 32768, 12, rank, 64, 0, 1, 0)
+    ws = cuda_mod._workspace(shape, dp.device)
+    stream = torch.cuda.current_stream().cuda_stream
+    sizes = [lib.ms_packed_stats_floats(ctypes.byref(shape), k) for k in (0, 1)]
+    first = None
+    for _ in range(40):
+        fwd, bwd = (torch.zeros(n, device="cuda") for n in sizes)
+        assert lib.ms_stats_forward(ctypes.byref(shape), dp.data_ptr(), dcos.data_ptr(), dsin.data_ptr(), None,
+                                    ws.data_ptr(), ws.numel(), fwd.data_ptr(), stream) == 0
+        assert lib.ms_stats_backward(ctypes.byref(shape), dp.data_ptr(), ddy.data_ptr(), dcos.data_ptr(),
+                                     dsin.data_ptr(), None, ws.data_ptr(), ws.numel(), bwd.data_ptr(), stream) == 0
+        torch.cuda.synchronize()
+        if first is None:
+            first = (fwd, bwd)
+        else:
+            assert torch.equal(fwd, first[0]) and torch.equal(bwd, first[1])
+    assert lib.ms_device_error() == 0
+
+
 def test_tcgen05_statistics_all_ranks_in_child_process():
     """Rank 16 and 32 take the mma.sync statistics kernels unless MEMSOLVE_STATS_TCGEN05=1 is set when the
     library plans its first launch: run the stage-wise statistics cases and the mixer cases of this file in
