@@ -481,6 +481,8 @@ def run_ours(args, cfg):
         # path on 2, 4 and 8 GPUs); MEMSOLVE_BENCH_PEER_EXCHANGE=0 selects NCCL for both instead
         if os.environ.get("MEMSOLVE_BENCH_PEER_EXCHANGE", "") != "0":
             sp.use_peer_exchange()
+            # both kinds of exchange areas sized for this layer (largest gradient included) before any capture
+            sp.prepare_peer_exchange(layer)
             peer_path = True
 
     def step(xin, grad_out):

@@ -24,12 +24,18 @@ namespace ms {
 constexpr int kCompactThreads = 256;
 constexpr int kQP = 68;   // pitch in floats of the r x 64 blocks: rows 16-byte aligned, 4-bank skew
 
+// Threads per CTA of the compact kernels: rank 64 takes 512 (its 64 x 64 products and the 64 elimination steps are
+// what a sequence-parallel step waits for on every rank; twice the threads halve the work per thread and step).
+template <int R>
+constexpr int compact_threads() { return R == 64 ? 512 : kCompactThreads; }
+
 template <int R>
 struct CompactDims {
-  static constexpr int TPR = R <= 16 ? 16 : (R <= 32 ? 8 : 4);   // threads per matrix row in the factorisation
+  static constexpr int NT = compact_threads<R>();
+  static constexpr int TPR = R <= 16 ? 16 : (R <= 32 || R == 64 ? 8 : 4);   // threads per matrix row in the factorisation
   static constexpr int CPT = R / TPR;                            // columns per thread
   static constexpr int RP = R + 4;                               // pitch in floats of the r x r matrices
-  static_assert(R * TPR <= kCompactThreads && CPT * TPR == R, "factorisation layout");
+  static_assert(R * TPR <= NT && CPT * TPR == R, "factorisation layout");
 };
 
 // ---------------------------------------------------------------------------------------
@@ -275,10 +281,10 @@ constexpr int compact_fwd_fixed_floats() {
 
 // MINB > 1: register budget for that many resident CTAs per SM (many systems: throughput instead of latency)
 template <int R, int MINB = 1>
-__global__ void __launch_bounds__(kCompactThreads, MINB)
+__global__ void __launch_bounds__(compact_threads<R>(), MINB)
 compact_forward_kernel(const CompactFwdParams p) {
   using D = CompactDims<R>;
-  constexpr int RP = D::RP;
+  constexpr int RP = D::RP, NT = D::NT;
   extern __shared__ __align__(16) unsigned char csm[];
   float* gs = reinterpret_cast<float*>(csm);   // R*R      G
   float* ts = gs + R * R;                      // R*RP     T
@@ -320,7 +326,7 @@ compact_forward_kernel(const CompactFwdParams p) {
       stage_partials(smem_u32(stage), src, nch, p.pf, R * R, p.pf - R * R, bar_addr + 8);
     }
   }
-  for (int i = tid; i < R * R; i += kCompactThreads) {
+  for (int i = tid; i < R * R; i += NT) {
     const int row = i / R, col = i - row * R;
     float f = p.complement ? 0.f : p.core_map[(size_t)h * R * R + i];
     if (row == col) f -= eta;
@@ -328,13 +334,13 @@ compact_forward_kernel(const CompactFwdParams p) {
   }
   bool ok = true;
   if (staged) ok = mbar_wait(smem_u32(bar), 0);
-  for (int i0 = tid; i0 < R * R; i0 += 4 * kCompactThreads) {
+  for (int i0 = tid; i0 < R * R; i0 += 4 * NT) {
     int off[4];
     bool valid[4];
     float acc[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      off[e] = i0 + e * kCompactThreads;
+      off[e] = i0 + e * NT;
       valid[e] = off[e] < R * R;
     }
     if (staged) sum_chunks4<2>(stage, p.pf, nch, off, valid, acc);
@@ -347,7 +353,7 @@ compact_forward_kernel(const CompactFwdParams p) {
   cholesky_inverse_cta<R>(gs, ts, tT, rowbuf, colbuf, dscale, tid);
   __syncthreads();
   grid_launch_dependents();
-  for (int i = tid; i < R * R; i += kCompactThreads) {
+  for (int i = tid; i < R * R; i += NT) {
     const int row = i / R, col = i - row * R;
     p.inverse[(size_t)sys * R * R + i] = ts[row * RP + col];
   }
@@ -356,13 +362,13 @@ compact_forward_kernel(const CompactFwdParams p) {
   for (int jb = 0; jb < p.dblocks; ++jb) {
     const int d0 = jb * 64, dv = min(64, d - d0);
     if (staged && jb == 0) ok = mbar_wait(smem_u32(bar) + 8, 0) && ok;
-    for (int i0 = tid; i0 < R * 64; i0 += 4 * kCompactThreads) {
+    for (int i0 = tid; i0 < R * 64; i0 += 4 * NT) {
       int off[4];
       bool valid[4];
       float acc[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int i = i0 + e * kCompactThreads, row = i >> 6, c = i & 63;
+        const int i = i0 + e * NT, row = i >> 6, c = i & 63;
         valid[e] = c < dv;
         off[e] = R * R + row * d + d0 + (valid[e] ? c : 0);
       }
@@ -370,13 +376,13 @@ compact_forward_kernel(const CompactFwdParams p) {
       else sum_chunks4<8>(src, p.pf, nch, off, valid, acc);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int i = i0 + e * kCompactThreads;
+        const int i = i0 + e * NT;
         qs[(i >> 6) * kQP + (i & 63)] = acc[e] * inv_s;
       }
     }
     __syncthreads();
     // Z = T Q   (T lower triangular: the inner index stops at the row)
-    for (int tile = tid; tile < TILES; tile += kCompactThreads) {
+    for (int tile = tid; tile < TILES; tile += NT) {
       const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
       float acc[4][2];
       zero_tile(acc);
@@ -391,7 +397,7 @@ compact_forward_kernel(const CompactFwdParams p) {
     }
     __syncthreads();
     // (F - eta I) Z -> qs
-    for (int tile = tid; tile < TILES; tile += kCompactThreads) {
+    for (int tile = tid; tile < TILES; tile += NT) {
       const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
       float acc[4][2];
       zero_tile(acc);
@@ -405,7 +411,7 @@ compact_forward_kernel(const CompactFwdParams p) {
     __nv_bfloat16* hi = p.coeff + (size_t)sys * 2 * R * p.dpad;
     __nv_bfloat16* lo = hi + (size_t)R * p.dpad;
     const int cend = min(64, p.dpad - d0);
-    for (int tile = tid; tile < TILES; tile += kCompactThreads) {
+    for (int tile = tid; tile < TILES; tile += NT) {
       const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
       float acc[4][2];
       zero_tile(acc);
@@ -455,10 +461,10 @@ constexpr int compact_bwd_fixed_floats() {
 }
 
 template <int R, int MINB = 1>
-__global__ void __launch_bounds__(kCompactThreads, MINB)
+__global__ void __launch_bounds__(compact_threads<R>(), MINB)
 compact_backward_kernel(const CompactBwdParams p) {
   using D = CompactDims<R>;
-  constexpr int RP = D::RP;
+  constexpr int RP = D::RP, NT = D::NT;
   extern __shared__ __align__(16) unsigned char csm[];
   float* ts = reinterpret_cast<float*>(csm);   // T
   float* tT = ts + R * RP;                     // T^T
@@ -493,7 +499,7 @@ compact_backward_kernel(const CompactBwdParams p) {
     __syncthreads();
     if (tid == 0) stage_partials(smem_u32(stage), src, nch, p.pf, 0, p.pf, bar_addr);
   }
-  for (int i = tid; i < R * R; i += kCompactThreads) {
+  for (int i = tid; i < R * R; i += NT) {
     const int row = i / R, col = i - row * R;
     const float t = p.inverse[(size_t)sys * R * R + i];
     ts[row * RP + col] = t;
@@ -521,20 +527,20 @@ compact_backward_kernel(const CompactBwdParams p) {
 
   constexpr int TILES = (R / 4) * 32;          // 4 x 2 tiles of an r x 64 block
   constexpr int RTILES = (R / 4) * (R / 2);    // 4 x 2 tiles of an r x r matrix, columns j and j + r/2
-  constexpr int RT_PER = (RTILES + kCompactThreads - 1) / kCompactThreads;
+  constexpr int RT_PER = (RTILES + NT - 1) / NT;
   float hacc[RT_PER][4][2];                    // H = sum over channel blocks of U Z^T, kept in registers
 #pragma unroll
   for (int e = 0; e < RT_PER; ++e) zero_tile(hacc[e]);
 
   for (int jb = 0; jb < p.dblocks; ++jb) {
     const int d0 = jb * 64, dv = min(64, d - d0);
-    for (int i0 = tid; i0 < R * 64; i0 += 4 * kCompactThreads) {
+    for (int i0 = tid; i0 < R * 64; i0 += 4 * NT) {
       int off[4];
       bool valid[4];
       float acc[4], zv[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int i = i0 + e * kCompactThreads, row = i >> 6, c = i & 63;
+        const int i = i0 + e * NT, row = i >> 6, c = i & 63;
         valid[e] = c < dv;
         off[e] = row * d + d0 + (valid[e] ? c : 0);
         zv[e] = valid[e] ? p.state[(size_t)sys * R * d + off[e]] : 0.f;
@@ -543,14 +549,14 @@ compact_backward_kernel(const CompactBwdParams p) {
       else sum_chunks4<8>(src, p.pf, nch, off, valid, acc);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int i = i0 + e * kCompactThreads;
+        const int i = i0 + e * NT;
         es[(i >> 6) * kQP + (i & 63)] = acc[e] * inv_s;
         zs[(i >> 6) * kQP + (i & 63)] = zv[e];
       }
     }
     __syncthreads();
     // U = T E
-    for (int tile = tid; tile < TILES; tile += kCompactThreads) {
+    for (int tile = tid; tile < TILES; tile += NT) {
       const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
       float acc[4][2];
       zero_tile(acc);
@@ -563,14 +569,14 @@ compact_backward_kernel(const CompactBwdParams p) {
     // H += U Z^T   (r x r, contraction over the 64 channels)
 #pragma unroll
     for (int e = 0; e < RT_PER; ++e) {
-      const int tile = tid + e * kCompactThreads;
+      const int tile = tid + e * NT;
       if (tile < RTILES) {
         const int i0 = (tile / (R / 2)) * 4, j0 = tile % (R / 2);
         mm_nt<64>(hacc[e], us, kQP, zs, kQP, i0, j0, j0 + R / 2);
       }
     }
     // dZ = M^T U -> es
-    for (int tile = tid; tile < TILES; tile += kCompactThreads) {
+    for (int tile = tid; tile < TILES; tile += NT) {
       const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
       float acc[4][2];
       zero_tile(acc);
@@ -584,7 +590,7 @@ compact_backward_kernel(const CompactBwdParams p) {
     __nv_bfloat16* hi = p.cross_grad + (size_t)sys * 2 * R * p.dpad;
     __nv_bfloat16* lo = hi + (size_t)R * p.dpad;
     const int cend = min(64, p.dpad - d0);
-    for (int tile = tid; tile < TILES; tile += kCompactThreads) {
+    for (int tile = tid; tile < TILES; tile += NT) {
       const int i0 = (tile >> 5) * 4, j0 = (tile & 31) * 2;
       float acc[4][2];
       zero_tile(acc);
@@ -610,7 +616,7 @@ compact_backward_kernel(const CompactBwdParams p) {
   // H to shared memory and to global (for the per-head sum over the batch)
 #pragma unroll
   for (int e = 0; e < RT_PER; ++e) {
-    const int tile = tid + e * kCompactThreads;
+    const int tile = tid + e * NT;
     if (tile < RTILES) {
       const int i0 = (tile / (R / 2)) * 4, j0 = tile % (R / 2), j1 = j0 + R / 2;
 #pragma unroll
@@ -627,7 +633,7 @@ compact_backward_kernel(const CompactBwdParams p) {
   // sym[r][k] = X[max(r,k)][min(r,k)] / 2, written to both triangles from the lower one
   float* sym = es;
   float* ys = us;
-  for (int tile = tid; tile < RTILES; tile += kCompactThreads) {
+  for (int tile = tid; tile < RTILES; tile += NT) {
     const int i0 = (tile / (R / 2)) * 4, j0 = tile % (R / 2), j1 = j0 + R / 2;
     float acc[4][2];
     zero_tile(acc);
@@ -642,7 +648,7 @@ compact_backward_kernel(const CompactBwdParams p) {
   }
   __syncthreads();
   // Y = sym T  (T lower triangular: row k of T is zero beyond column k)
-  for (int tile = tid; tile < RTILES; tile += kCompactThreads) {
+  for (int tile = tid; tile < RTILES; tile += NT) {
     const int i0 = (tile / (R / 2)) * 4, j0 = tile % (R / 2), j1 = j0 + R / 2;
     float acc[4][2];
     zero_tile(acc);
@@ -659,7 +665,7 @@ compact_backward_kernel(const CompactBwdParams p) {
   const float s_tok = inv_sqrt_rn(n);
   __nv_bfloat16* ghi = p.gram_grad + (size_t)sys * 2 * R * R;
   __nv_bfloat16* glo = ghi + R * R;
-  for (int tile = tid; tile < RTILES; tile += kCompactThreads) {
+  for (int tile = tid; tile < RTILES; tile += NT) {
     const int i0 = (tile / (R / 2)) * 4, j0 = tile % (R / 2), j1 = j0 + R / 2;
     float acc[4][2];
     zero_tile(acc);
@@ -759,12 +765,12 @@ static int launch_compact_fwd_r(CompactFwdParams& p, int systems, cudaStream_t s
   if constexpr (R <= 32) {
     if (many) {
       if (set_smem(compact_forward_kernel<R, 4>, bytes)) return MS_ERR_LAUNCH;
-      launch_kernel(compact_forward_kernel<R, 4>, dim3(systems), dim3(kCompactThreads), bytes, st, p);
+      launch_kernel(compact_forward_kernel<R, 4>, dim3(systems), dim3(compact_threads<R>()), bytes, st, p);
       return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
     }
   }
   if (set_smem(compact_forward_kernel<R>, bytes)) return MS_ERR_LAUNCH;
-  launch_kernel(compact_forward_kernel<R>, dim3(systems), dim3(kCompactThreads), bytes, st, p);
+  launch_kernel(compact_forward_kernel<R>, dim3(systems), dim3(compact_threads<R>()), bytes, st, p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
 
@@ -800,12 +806,12 @@ static int launch_compact_bwd_r(CompactBwdParams& p, int systems, cudaStream_t s
   if constexpr (R <= 32) {
     if (many) {
       if (set_smem(compact_backward_kernel<R, 4>, bytes)) return MS_ERR_LAUNCH;
-      launch_kernel(compact_backward_kernel<R, 4>, dim3(systems), dim3(kCompactThreads), bytes, st, p);
+      launch_kernel(compact_backward_kernel<R, 4>, dim3(systems), dim3(compact_threads<R>()), bytes, st, p);
       return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
     }
   }
   if (set_smem(compact_backward_kernel<R>, bytes)) return MS_ERR_LAUNCH;
-  launch_kernel(compact_backward_kernel<R>, dim3(systems), dim3(kCompactThreads), bytes, st, p);
+  launch_kernel(compact_backward_kernel<R>, dim3(systems), dim3(compact_threads<R>()), bytes, st, p);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
 

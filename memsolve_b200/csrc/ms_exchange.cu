@@ -28,7 +28,7 @@
 
 namespace ms {
 
-constexpr int kExCtas = 32;          // thread blocks = slices of the value vector
+constexpr int kExCtas = 128;         // thread blocks = slices of the value vector (one vector of four per thread at rank 64)
 constexpr int kExThreads = 256;
 constexpr int kExMaxRanks = 8;
 constexpr int kErrPeerTimeout = 0x200;
@@ -93,20 +93,29 @@ __device__ __forceinline__ float4 reduce_partials4(const ExchangeParams& p, int 
     const float n = p.counts ? p.counts[sys / p.heads] : (float)p.tokens;
     const float4* src = reinterpret_cast<const float4*>(p.partials + (size_t)sys * p.chunks * p.pf + e);
     const int stride4 = p.pf >> 2;
-    // chunk order is kept; four loads are in flight at a time
+    // chunk order is kept; eight loads are in flight at a time (a trip to L2 per round: with the twenty-odd
+    // partials of a long sequence the rounds are what this kernel waits for)
     int k = 0;
-    for (; k + 4 <= p.chunks; k += 4) {
-      float4 t[4];
+    for (; k + 8 <= p.chunks; k += 8) {
+      float4 t[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) t[u] = __ldg(src + (size_t)(k + u) * stride4);
+      for (int u = 0; u < 8; ++u) t[u] = __ldg(src + (size_t)(k + u) * stride4);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         v.x += t[u].x; v.y += t[u].y; v.z += t[u].z; v.w += t[u].w;
       }
     }
-    for (; k < p.chunks; ++k) {
-      const float4 t = __ldg(src + (size_t)k * stride4);
-      v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+    if (k < p.chunks) {
+      float4 t[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        t[u] = k + u < p.chunks ? __ldg(src + (size_t)(k + u) * stride4) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (k + u < p.chunks) {
+          v.x += t[u].x; v.y += t[u].y; v.z += t[u].z; v.w += t[u].w;
+        }
+      }
     }
     const float scale = e < p.gram_floats ? inv_rn(n) : inv_sqrt_rn(n);
     v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;

@@ -115,7 +115,7 @@ class _PeerExchange:
         self.areas(statistics_bytes, device)
         if largest_gradient_numel >= self.SUM_MINIMUM_NUMEL and device.index not in self._sum_areas:
             need = int(backend._LIB.ms_peer_sum_area_bytes(largest_gradient_numel))
-            self._sum_areas[device.index] = self._allocate(max(need, 16 << 20), device)
+            self._sum_areas[device.index] = self._allocate(max(need, 32 << 20), device)
             self._streams[device.index] = torch.cuda.Stream(device)
 
     # ---- in-place SUM of a gradient over the ranks, on a stream of its own
@@ -145,7 +145,7 @@ class _PeerExchange:
         entry = self._sum_areas.get(device.index)
         need = int(lib.ms_peer_sum_area_bytes(tensor.numel()))
         if entry is None:
-            entry = self._sum_areas[device.index] = self._allocate(max(need, 16 << 20), device)
+            entry = self._sum_areas[device.index] = self._allocate(max(need, 32 << 20), device)
             self._streams[device.index] = torch.cuda.Stream(device)
         elif entry[3] < need:
             raise RuntimeError("gradient larger than the peer-memory SUM area; can_sum() routes such tensors to NCCL")
