@@ -59,7 +59,7 @@ typedef enum ms_status {
 
 /* Problem shape shared by every call. */
 typedef struct ms_shape {
-  int32_t batch;       /* B */
+  int32_t batch;       /* B; B*H <= 65535 */
   int32_t tokens;      /* N (local tokens of this rank under sequence parallelism)  */
   int32_t heads;       /* H */
   int32_t rank;        /* r in {16,32,48,64} */

@@ -186,7 +186,9 @@ int check_shape(const ms_shape* s) {
   if (s->rotary_rows != 0 && s->rotary_rows != 1 && s->rotary_rows != s->batch) return MS_ERR_INVALID_ARGUMENT;
   if (s->rotary_rows != 0 && (s->head_dim & 1)) return MS_ERR_ODD_HEAD_DIM;
   if (s->reserved != 0) return MS_ERR_INVALID_ARGUMENT;
-  if ((long long)s->batch * s->heads > 0x3fffffffLL) return MS_ERR_INVALID_ARGUMENT;
+  // the (sample, head) systems ride on gridDim.y of several kernels: refuse what the grid cannot hold instead of
+  // failing at launch
+  if ((long long)s->batch * s->heads > 65535LL) return MS_ERR_INVALID_ARGUMENT;
   return MS_OK;
 }
 
@@ -229,13 +231,11 @@ Plan make_plan(const ms_shape& s) {
     const char* v = std::getenv("MEMSOLVE_NO_TCGEN05");
     return v && v[0] == '1';
   }();
-  // The tcgen05 statistics kernel (long samples, head dimension 64, rank 16/32/64) gives a CTA a group of heads
-  // and a chunk of 128-token tiles: chunks are counted per head group, not per head.
-  // Rank 64 takes it by default: the mma.sync kernels keep a rank-64 accumulator tile in registers only for the
-  // adjoint, and the forward falls back to the generic loader.  At rank 16 and 32 the tcgen05 kernel is limited by
-  // the shared-memory traffic of its many small MMAs and only matches the mma.sync kernels, while its finer
-  // chunking (one partial per CTA and head group) lengthens the compact stage; MEMSOLVE_STATS_TCGEN05=1 selects
-  // it there too (tests do).
+  // The tcgen05 statistics kernel (long samples, head dimension 64, rank 16/32/64) gives a CTA one head and a chunk
+  // of 128-token tiles.  Rank 64 takes it by default: the mma.sync kernels keep a rank-64 accumulator tile in
+  // registers only for the adjoint, and the forward falls back to the generic loader.  At rank 16 and 32 it only
+  // matches the mma.sync kernels inside the chained launches (the cos / sin rows, 32 KB per 24 KB of tokens and one
+  // head, bound both); MEMSOLVE_STATS_TCGEN05=1 selects it there too (tests do).
   static const bool all_ranks_env = [] {
     const char* v = std::getenv("MEMSOLVE_STATS_TCGEN05");
     return v && v[0] == '1';
