@@ -228,10 +228,10 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int dmodel = p.heads * 64;
     float cs[16], sn[16];
     int tab_next = 0;
+    bool owe_table = false;   // this thread holds the rows of a tile and has not yet released the buffer
     auto take_tables = [&](int k) {
       bool good = true;
       while (tab_next <= k && good) {
-        uint32_t seen = 0;   // one word of every load below
         good = ro_wait(bar_tab_full, tab_next & 1);
         if (good && tab_next == k) {
 #pragma unroll
@@ -240,13 +240,13 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const float4 cv = ld_shared_f4(tab_buf + off), sv = ld_shared_f4(tab_buf + 16384 + off);
             cs[4 * v] = cv.x; cs[4 * v + 1] = cv.y; cs[4 * v + 2] = cv.z; cs[4 * v + 3] = cv.w;
             sn[4 * v] = sv.x; sn[4 * v + 1] = sv.y; sn[4 * v + 2] = sv.z; sn[4 * v + 3] = sv.w;
-            seen ^= __float_as_uint(cv.w) ^ __float_as_uint(sv.w);
           }
         }
         if (good) {
-          // the rows must be in registers before the buffer goes back to the table warp's next bulk copy
-          wait_for_loaded(seen, tslot + 8);
-          ro_arrive(bar_tab_free);
+          // A tile whose rows were copied is handed back only after they have been USED (in the epilogue below):
+          // ld.shared merely issues the reads, and an arrive right behind it can let the next bulk copy land first.
+          if (tab_next == k) owe_table = true;
+          else ro_arrive(bar_tab_free);
         }
         ++tab_next;
       }
@@ -296,6 +296,10 @@ readout_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           }
         }
         st_shared_v4(addr, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+      }
+      if (ROT && owe_table) {   // every cos / sin register has been consumed by an instruction issued above
+        ro_arrive(bar_tab_free);
+        owe_table = false;
       }
       fence_async_shared();
       ro_arrive(bar_out + 8 * (i % SC));

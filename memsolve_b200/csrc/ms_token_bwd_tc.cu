@@ -383,12 +383,12 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int width = p.heads * (R + 64);
     float cs[16], sn[16];
     int tab_next = 0;   // ordinal of the next tile whose table rows this thread has not yet passed
+    bool owe_table = false;   // this thread holds the rows of a tile and has not yet released the buffer
     // Copy this thread's 16 cos / sin entries of tile ordinal k from the shared-memory buffer; tiles in between
     // (this group had no item in them) are passed without copying, so that the buffer can be refilled.
     auto take_tables = [&](int k) {
       bool good = true;
       while (tab_next <= k && good) {
-        uint32_t seen = 0;   // one word of every load below
         good = wait_uniform(bar_tab_full, tab_next & 1);
         if (good && tab_next == k) {
 #pragma unroll
@@ -397,13 +397,13 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const float4 cv = ld_shared_f4(tab_buf + off), sv = ld_shared_f4(tab_buf + 16384 + off);
             cs[4 * v] = cv.x; cs[4 * v + 1] = cv.y; cs[4 * v + 2] = cv.z; cs[4 * v + 3] = cv.w;
             sn[4 * v] = sv.x; sn[4 * v + 1] = sv.y; sn[4 * v + 2] = sv.z; sn[4 * v + 3] = sv.w;
-            seen ^= __float_as_uint(cv.w) ^ __float_as_uint(sv.w);
           }
         }
         if (good) {
-          // the rows must be in registers before the buffer goes back to the table warp's next bulk copy
-          wait_for_loaded(seen, tslot + 8);
-          mbar_arrive(bar_tab_free);
+          // A tile whose rows were copied is handed back only after they have been USED (below): ld.shared merely
+          // issues the reads, and an arrive right behind it can let the table warp's next bulk copy land first.
+          if (tab_next == k) owe_table = true;
+          else mbar_arrive(bar_tab_free);
         }
         ++tab_next;
       }
@@ -431,6 +431,10 @@ token_backward_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       if (ROT) {
         rotate_half_row_to_tmem(y_tile, row, half, cs, sn, lane_base + Cfg::COL_YH + half * 16,
                                 lane_base + Cfg::COL_YL + half * 16);
+        if (owe_table) {   // every cos / sin register has been consumed by an instruction issued above
+          mbar_arrive(bar_tab_free);
+          owe_table = false;
+        }
         ok = wait_uniform(bar_cfull + 8 * (i % SC), (i / SC) & 1);
         if (!ok) break;
         rotate_half_row_to_tmem(c_tile, row, half, cs, sn, lane_base + Cfg::COL_CH + half * 16,
