@@ -1,7 +1,8 @@
 """Place the reference's own pure-Python package under oracle/_ref so that the CPU baseline can time the
 reference itself (`layer(x, implementation="reference")`) instead of the oracle port.
 
-    python oracle/build_ref.py [path of the reference checkout, default /root/reference]
+    python oracle/build_ref.py [path of the reference checkout; default: REFERENCE_ROOT below, or the
+                                environment variable MEMSOLVE_REFERENCE_ROOT]
 
 The package (memsolve/: five Python files) is copied as it lies, unmodified, into oracle/_ref/memsolve.  That
 folder is listed in .gitignore: the copy is a build product of this recipe, like a compiled reference library
@@ -16,9 +17,10 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 TARGET = os.path.join(HERE, "_ref")
+REFERENCE_ROOT = os.environ.get("MEMSOLVE_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
 
 
-def build(reference_root: str = "/root/reference") -> bool:
+def build(reference_root: str = REFERENCE_ROOT) -> bool:
     source = os.path.join(reference_root, "memsolve")
     if not os.path.isdir(source):
         return os.path.isdir(os.path.join(TARGET, "memsolve"))   # keep what an earlier build left
@@ -31,5 +33,5 @@ def build(reference_root: str = "/root/reference") -> bool:
 
 
 if __name__ == "__main__":
-    ok = build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ok = build(sys.argv[1] if len(sys.argv) > 1 else REFERENCE_ROOT)
     print("oracle/_ref/memsolve", "ready" if ok else "not available (no reference checkout)")
