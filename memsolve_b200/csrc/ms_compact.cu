@@ -26,13 +26,16 @@ constexpr int kQP = 68;   // pitch in floats of the r x 64 blocks: rows 16-byte 
 
 // Threads per CTA of the compact kernels: rank 64 takes 512 (its 64 x 64 products and the 64 elimination steps are
 // what a sequence-parallel step waits for on every rank; twice the threads halve the work per thread and step).
-template <int R>
-constexpr int compact_threads() { return R == 64 ? 512 : kCompactThreads; }
+// Rank 32 does the same when few systems are in flight (one resident CTA per SM; the four-CTA variant for many
+// systems keeps 256 threads for its register budget).
+template <int R, int MINB = 1>
+constexpr int compact_threads() { return (R == 64 || (R == 32 && MINB == 1)) ? 512 : kCompactThreads; }
 
-template <int R>
+template <int R, int MINB = 1>
 struct CompactDims {
-  static constexpr int NT = compact_threads<R>();
-  static constexpr int TPR = R <= 16 ? 16 : (R <= 32 || R == 64 ? 8 : 4);   // threads per matrix row in the factorisation
+  static constexpr int NT = compact_threads<R, MINB>();
+  // threads per matrix row in the factorisation
+  static constexpr int TPR = R <= 16 ? 16 : (R == 32 ? (NT == 512 ? 16 : 8) : (R == 64 ? 8 : 4));
   static constexpr int CPT = R / TPR;                            // columns per thread
   static constexpr int RP = R + 4;                               // pitch in floats of the r x r matrices
   static_assert(R * TPR <= NT && CPT * TPR == R, "factorisation layout");
@@ -50,10 +53,10 @@ struct CompactDims {
 // the owners of the pivot row and of the pivot column publish them (double buffered) and one
 // CTA barrier separates the steps, so a step costs one barrier, a handful of shared-memory
 // reads and CPT FMAs per thread instead of a whole row per lane.
-template <int R>
+template <int R, int MINB>
 __device__ __forceinline__ void cholesky_inverse_cta(const float* gs, float* ts, float* tT, float* rowbuf,
                                                      float* colbuf, double* dscale, int tid) {
-  using D = CompactDims<R>;
+  using D = CompactDims<R, MINB>;
   constexpr int TPR = D::TPR, CPT = D::CPT, RP = D::RP;
   const int i = tid / TPR, q = tid % TPR;
   const bool active = i < R;
@@ -281,9 +284,9 @@ constexpr int compact_fwd_fixed_floats() {
 
 // MINB > 1: register budget for that many resident CTAs per SM (many systems: throughput instead of latency)
 template <int R, int MINB = 1>
-__global__ void __launch_bounds__(compact_threads<R>(), MINB)
+__global__ void __launch_bounds__(compact_threads<R, MINB>(), MINB)
 compact_forward_kernel(const CompactFwdParams p) {
-  using D = CompactDims<R>;
+  using D = CompactDims<R, MINB>;
   constexpr int RP = D::RP, NT = D::NT;
   extern __shared__ __align__(16) unsigned char csm[];
   float* gs = reinterpret_cast<float*>(csm);   // R*R      G
@@ -350,7 +353,7 @@ compact_forward_kernel(const CompactFwdParams p) {
       if (valid[e]) gs[off[e]] = acc[e] * inv_n;
   }
   __syncthreads();
-  cholesky_inverse_cta<R>(gs, ts, tT, rowbuf, colbuf, dscale, tid);
+  cholesky_inverse_cta<R, MINB>(gs, ts, tT, rowbuf, colbuf, dscale, tid);
   __syncthreads();
   grid_launch_dependents();
   for (int i = tid; i < R * R; i += NT) {
@@ -461,9 +464,9 @@ constexpr int compact_bwd_fixed_floats() {
 }
 
 template <int R, int MINB = 1>
-__global__ void __launch_bounds__(compact_threads<R>(), MINB)
+__global__ void __launch_bounds__(compact_threads<R, MINB>(), MINB)
 compact_backward_kernel(const CompactBwdParams p) {
-  using D = CompactDims<R>;
+  using D = CompactDims<R, MINB>;
   constexpr int RP = D::RP, NT = D::NT;
   extern __shared__ __align__(16) unsigned char csm[];
   float* ts = reinterpret_cast<float*>(csm);   // T
@@ -765,7 +768,7 @@ static int launch_compact_fwd_r(CompactFwdParams& p, int systems, cudaStream_t s
   if constexpr (R <= 32) {
     if (many) {
       if (set_smem(compact_forward_kernel<R, 4>, bytes)) return MS_ERR_LAUNCH;
-      launch_kernel(compact_forward_kernel<R, 4>, dim3(systems), dim3(compact_threads<R>()), bytes, st, p);
+      launch_kernel(compact_forward_kernel<R, 4>, dim3(systems), dim3(compact_threads<R, 4>()), bytes, st, p);
       return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
     }
   }
@@ -806,7 +809,7 @@ static int launch_compact_bwd_r(CompactBwdParams& p, int systems, cudaStream_t s
   if constexpr (R <= 32) {
     if (many) {
       if (set_smem(compact_backward_kernel<R, 4>, bytes)) return MS_ERR_LAUNCH;
-      launch_kernel(compact_backward_kernel<R, 4>, dim3(systems), dim3(compact_threads<R>()), bytes, st, p);
+      launch_kernel(compact_backward_kernel<R, 4>, dim3(systems), dim3(compact_threads<R, 4>()), bytes, st, p);
       return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
     }
   }
