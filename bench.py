@@ -675,7 +675,9 @@ def run_ours(args, cfg):
         # the sequence-parallel path adds a pack kernel per direction (the buffer that is all-reduced)
         # statistics (+ per-head core), compact, readout and their three adjoints; sequence parallel with the
         # peer-memory exchange adds one exchange kernel per direction and one SUM kernel per weight matrix
-        "gpu_launches": (6 if world == 1 else (10 if peer_path else 8)) * args.steps * args.blocks,
+        # (on one GPU rank 64 adds a launch per direction that reduces the statistics' partials)
+        "gpu_launches": ((8 if cfg["rank"] == 64 else 6) if world == 1 else (10 if peer_path else 8))
+                        * args.steps * args.blocks,
         "timing": f"{timing_mode}, median of {args.blocks} blocks of {args.steps} steps",
         "eager_ms_per_step": eager_total / args.steps * 1e3,
         "collective": None if world == 1 else (

@@ -279,7 +279,18 @@ Plan make_plan(const ms_shape& s) {
   }
   p.ws_hmat = round64((size_t)p.systems * s.rank * s.rank);
   p.ws_de_sys = round64((size_t)p.systems);
-  p.ws_total_bytes = (p.ws_partials + p.ws_de + p.ws_hmat + p.ws_de_sys) * sizeof(float);
+  p.ws_packed = round64((size_t)p.systems * (p.fwd_partial_floats + 1));
+  // Rank 64 with the tcgen05 statistics: a system's partials (twelve of 32 KB at 32768 tokens) do not fit the
+  // staging area of the compact kernels, whose twelve CTAs then add them from global memory at ~26 GB/s each
+  // (6.6 + 8.6 us forward, 9.4 us backward); a launch of its own over all SMs does it in ~2 us and the compact
+  // kernels read one reduced vector (mix core at 32768 tokens: 236 -> 220 us).  At rank 16/32 the staged sums are
+  // cheaper than the extra launch (145.7 against 150.4 us).  MEMSOLVE_PACK=1 / 0 forces either.
+  static const int pack_env = [] {
+    const char* v = std::getenv("MEMSOLVE_PACK");
+    return !v ? -1 : (v[0] == '1' ? 1 : 0);
+  }();
+  p.pack = p.stats_tc && (pack_env < 0 ? s.rank == 64 : pack_env == 1);
+  p.ws_total_bytes = (p.ws_partials + p.ws_de + p.ws_hmat + p.ws_de_sys + p.ws_packed) * sizeof(float);
   return p;
 }
 
@@ -288,6 +299,7 @@ struct Workspace {
   float* de_partials;
   float* hmat;
   float* de_sys;
+  float* packed;
 };
 
 static Workspace carve(void* ws, const Plan& p) {
@@ -296,6 +308,7 @@ static Workspace carve(void* ws, const Plan& p) {
   w.de_partials = w.partials + p.ws_partials;
   w.hmat = w.de_partials + p.ws_de;
   w.de_sys = w.hmat + p.ws_hmat;
+  w.packed = w.de_sys + p.ws_de_sys;
   return w;
 }
 
@@ -551,9 +564,14 @@ int ms_mix_forward(const ms_shape* shape, const void* projected, const float* ba
     MS_TRY(launch_compact_forward(*shape, plan, counts, w.partials, false, core_only, st));
     return launch_short_readout(*shape, plan, projected, cos, sin, counts, *tape, mixed, st);
   }
-  // the two launches below start while the kernel ahead of them drains (see launch_kernel)
+  // the launches below start while the kernel ahead of them drains (see launch_kernel)
   ChainScope chain(chaining_allowed());
-  MS_TRY(launch_compact_forward(*shape, plan, counts, w.partials, false, *tape, st));
+  if (plan.pack) {
+    MS_TRY(launch_pack_stats(*shape, plan, false, w.partials, nullptr, counts, w.packed, st));
+    MS_TRY(launch_compact_forward(*shape, plan, counts, w.packed, true, *tape, st));
+  } else {
+    MS_TRY(launch_compact_forward(*shape, plan, counts, w.partials, false, *tape, st));
+  }
   Plan read_plan = plan;
   read_plan.aligned = plan.aligned && is16(projected) && is16(mixed);
   return launch_readout(*shape, read_plan, projected, cos, sin, counts, *tape, mixed, st);
@@ -731,8 +749,14 @@ int ms_mix_backward(const ms_shape* shape, const void* projected, const void* dy
                                  dprojected, w.de_partials, 1.0f, d_eta_raw, st);
   }
   ChainScope chain(chaining_allowed());
-  MS_TRY(launch_compact_backward(*shape, plan, counts, w.partials, w.de_partials, false, *tape, w.hmat,
-                                 w.de_sys, gram_grad, cross_grad, st));
+  if (plan.pack) {
+    MS_TRY(launch_pack_stats(*shape, plan, true, w.partials, w.de_partials, counts, w.packed, st));
+    MS_TRY(launch_compact_backward(*shape, plan, counts, w.packed, nullptr, true, *tape, w.hmat, w.de_sys, gram_grad,
+                                   cross_grad, st));
+  } else {
+    MS_TRY(launch_compact_backward(*shape, plan, counts, w.partials, w.de_partials, false, *tape, w.hmat,
+                                   w.de_sys, gram_grad, cross_grad, st));
+  }
   // the token pass needs only dG and dQ; the per-head core adjoint rides in spare CTAs of its grid
   if (!projected || !dy || !dprojected) return MS_ERR_INVALID_ARGUMENT;
   Plan token_plan = plan;

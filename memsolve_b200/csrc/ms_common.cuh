@@ -31,12 +31,14 @@ struct Plan {
   bool tma;          // TMA kernels allowed (off when the environment sets MEMSOLVE_NO_TMA=1)
   bool tc;           // tcgen05 kernels allowed (off with MEMSOLVE_NO_TMA=1 or MEMSOLVE_NO_TCGEN05=1)
   bool stats_tc;     // the token chunks were sized for the tcgen05 statistics kernel (head groups, 128-token tiles)
+  bool pack;         // ms_mix_forward / ms_mix_backward add the partials in a launch of their own (many chunks)
   size_t fwd_partial_floats;  // per (system, chunk): r*r + r*d
   size_t bwd_partial_floats;  // per (system, chunk): r*d
   size_t ws_partials;         // floats
   size_t ws_de;               // floats: systems * chunks * de_slots
   size_t ws_hmat;             // floats: systems * r * r
   size_t ws_de_sys;           // floats: systems
+  size_t ws_packed;           // floats: reduced statistics of all systems (+ the <dY, C> sums)
   size_t ws_total_bytes;
 };
 

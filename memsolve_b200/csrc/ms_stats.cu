@@ -336,8 +336,17 @@ __global__ void pack_stats_kernel(const float* __restrict__ partials, const floa
   const float inv_n = inv_rn(n), inv_s = inv_sqrt_rn(n);
   const float* src = partials + (size_t)sys * chunks * partial_floats;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < partial_floats; i += gridDim.x * blockDim.x) {
+    // chunk order is kept; eight loads are in flight at a time
     float v = 0.f;
-    for (int c = 0; c < chunks; ++c) v += src[(size_t)c * partial_floats + i];
+    int c = 0;
+    for (; c + 8 <= chunks; c += 8) {
+      float t[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) t[u] = src[(size_t)(c + u) * partial_floats + i];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v += t[u];
+    }
+    for (; c < chunks; ++c) v += src[(size_t)c * partial_floats + i];
     packed[(size_t)sys * partial_floats + i] = v * (i < gram_floats ? inv_n : inv_s);
   }
   if (grad && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -414,9 +423,8 @@ int launch_pack_stats(const ms_shape& s, const Plan& plan, bool grad, const floa
                       const float* de_partials, const float* counts, float* packed, cudaStream_t st) {
   const int pf = (int)(grad ? plan.bwd_partial_floats : plan.fwd_partial_floats);
   dim3 grid((pf + 255) / 256, plan.systems);
-  pack_stats_kernel<<<grid, 256, 0, st>>>(partials, de_partials, counts, packed, s.heads, s.tokens,
-                                          plan.chunks, plan.de_slots, grad ? 0 : s.rank * s.rank, pf,
-                                          plan.systems, grad ? 1 : 0);
+  launch_kernel(pack_stats_kernel, grid, dim3(256), 0, st, partials, de_partials, counts, packed, s.heads, s.tokens,
+                plan.chunks, plan.de_slots, grad ? 0 : s.rank * s.rank, pf, plan.systems, grad ? 1 : 0);
   return cudaGetLastError() == cudaSuccess ? MS_OK : MS_ERR_LAUNCH;
 }
 
