@@ -505,6 +505,40 @@ def test_full_size_long_sequence(cuda_mod, rank):
     assert cuda_mod._LIB.ms_device_error() == 0
 
 
+@pytest.mark.parametrize("rank,length", [(32, 32768), (64, 262144)])
+def test_full_size_properties(cuda_mod, rank, length):
+    """Size-independent properties at the benchmark sizes (32768 tokens at rank 32; the whole 262144-token sequence
+    of the sequence-parallel configuration at rank 64, where an FP64 oracle run would take minutes).  For fixed
+    relations A the mixer is LINEAR in the content: mix(A, C1 + C2) = mix(A, C1) + mix(A, C2), also through the
+    rotation; and with eta -> 1 and a zero core the update vanishes in the limit of weak relations:
+    mix(0, C) = eta C.  Limits are those of the BF16 stores (three roundings in the sum: 8e-3)."""
+    heads, d = 12, 64
+    gen = torch.Generator().manual_seed(length + rank)
+    rel = (torch.randn(1, length, heads * rank, generator=gen) * 0.6).bfloat16()
+    # contents on a coarse grid, so that C1 + C2 is exact in BF16
+    c1 = (torch.randint(-8, 9, (1, length, heads * d), generator=gen).float() / 8).bfloat16()
+    c2 = (torch.randint(-8, 9, (1, length, heads * d), generator=gen).float() / 8).bfloat16()
+    base = (torch.randn(heads, rank, rank, generator=gen) * 0.1).cuda()
+    eta_raw = (torch.full((heads,), 1.4722) + torch.randn(heads, generator=gen) * 0.1).cuda()
+    cos, sin = O.rotary_tables(torch.arange(length)[None], head_dim=d, train_length=128, context_length=length)
+    cos, sin = cos.cuda(), sin.cuda()
+
+    def mix(content, relations=rel):
+        proj = torch.cat([relations, content], dim=-1).cuda().contiguous()
+        with torch.no_grad():
+            return cuda_mod.fast_mix(proj, base, eta_raw, rotary_cos=cos, rotary_sin=sin).float()
+
+    y1, y2, y12 = mix(c1), mix(c2), mix((c1.float() + c2.float()).bfloat16())
+    err = rel_l2(y12, y1 + y2)
+    print(f"linearity at {length} tokens, rank {rank}: {err:.2e}")
+    assert err <= 8e-3
+    y0 = mix(c1, torch.zeros_like(rel))
+    eta = O.bounded_eta(eta_raw.double().cpu())
+    want = (c1.double().reshape(1, length, heads, d) * eta.view(1, 1, heads, 1)).reshape(1, length, heads * d)
+    assert rel_l2(y0.cpu(), want) <= 5e-3
+    assert cuda_mod._LIB.ms_device_error() == 0
+
+
 @pytest.mark.parametrize("batch,length,heads,rank,head_dim,rot", [
     (1, 16 * 37 + 5, 12, 32, 64, True), (3, 197, 6, 32, 64, False), (2, 1000, 3, 64, 128, True),
     (1, 50, 2, 16, 64, True), (2, 4100, 16, 32, 64, True)])
