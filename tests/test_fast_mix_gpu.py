@@ -539,6 +539,30 @@ def test_full_size_properties(cuda_mod, rank, length):
     assert cuda_mod._LIB.ms_device_error() == 0
 
 
+@pytest.mark.parametrize("rank,length", [(32, 32768), (64, 262144)])
+def test_full_size_adjoint_identity(cuda_mod, rank, length):
+    """For fixed relations the mixer is a linear map of the content, so forward and backward must be adjoint:
+    <mix(A, C), dY> = <C, dC>, with dC the content part of the backward pass for the upstream gradient dY.  With
+    dY = mix(A, C) itself both sides are |Y|^2, a sum of 2e7 ... 2e8 positive terms against which the BF16
+    rounding of Y and dC averages out: 2e-4 relative."""
+    heads, d = 12, 64
+    gen = torch.Generator().manual_seed(3 * length + rank)
+    proj = (torch.randn(1, length, heads * (rank + d), generator=gen) * 0.6).bfloat16().cuda().requires_grad_()
+    base = (torch.randn(heads, rank, rank, generator=gen) * 0.1).cuda()
+    eta_raw = (torch.full((heads,), 1.4722) + torch.randn(heads, generator=gen) * 0.1).cuda()
+    cos, sin = O.rotary_tables(torch.arange(length)[None], head_dim=d, train_length=128, context_length=length)
+    y = cuda_mod.fast_mix(proj, base, eta_raw, rotary_cos=cos.cuda(), rotary_sin=sin.cuda())
+    dy = y.detach().clone()
+    y.backward(dy)
+    content = proj.detach()[..., heads * rank:].double()
+    d_content = proj.grad[..., heads * rank:].double()
+    left = float((y.detach().double() * dy.double()).sum())
+    right = float((content * d_content).sum())
+    print(f"adjoint identity at {length} tokens, rank {rank}: {left:.8e} vs {right:.8e} ({abs(left - right) / left:.1e})")
+    assert abs(left - right) <= 2e-4 * left
+    assert cuda_mod._LIB.ms_device_error() == 0
+
+
 @pytest.mark.parametrize("batch,length,heads,rank,head_dim,rot", [
     (1, 16 * 37 + 5, 12, 32, 64, True), (3, 197, 6, 32, 64, False), (2, 1000, 3, 64, 128, True),
     (1, 50, 2, 16, 64, True), (2, 4100, 16, 32, 64, True)])
