@@ -124,8 +124,20 @@ __device__ __forceinline__ float4 reduce_partials4(const ExchangeParams& p, int 
     const int cnt = p.chunks * p.de_slots;
     for (int q = 0; q < 4; ++q) {
       const int sys = i + q - body;
-      if (sys < p.systems)
-        for (int k = 0; k < cnt; ++k) out[q] += p.de_partials[(size_t)sys * cnt + k];
+      if (sys < p.systems) {
+        // index order is kept; eight loads in flight at a time (one thread adds a system's few dozen values, and
+        // one load per trip to L2 made this the longest path of the adjoint exchange)
+        const float* src = p.de_partials + (size_t)sys * cnt;
+        int k = 0;
+        for (; k + 8 <= cnt; k += 8) {
+          float t[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) t[u] = __ldg(src + k + u);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) out[q] += t[u];
+        }
+        for (; k < cnt; ++k) out[q] += __ldg(src + k);
+      }
     }
     v = make_float4(out[0], out[1], out[2], out[3]);
   }
