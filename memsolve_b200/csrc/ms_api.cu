@@ -232,16 +232,17 @@ Plan make_plan(const ms_shape& s) {
     return v && v[0] == '1';
   }();
   // The tcgen05 statistics kernel (long samples, head dimension 64, rank 16/32/64) gives a CTA one head and a chunk
-  // of 128-token tiles.  Rank 64 takes it by default: the mma.sync kernels keep a rank-64 accumulator tile in
-  // registers only for the adjoint, and the forward falls back to the generic loader.  At rank 16 and 32 it only
-  // matches the mma.sync kernels inside the chained launches (the cos / sin rows, 32 KB per 24 KB of tokens and one
-  // head, bound both); MEMSOLVE_STATS_TCGEN05=1 selects it there too (tests do).
-  static const bool all_ranks_env = [] {
+  // of 128-token tiles.  Rank 64 takes it (the mma.sync kernels keep a rank-64 accumulator tile in registers only
+  // for the adjoint, and the forward falls back to the generic loader) and so does rank 32: alone it is faster
+  // there (30.0 / 31.6 us against 31.8 / 35.8 us at 32768 tokens), inside the chained launches the two are level
+  // (145.7 us either way).  At rank 16 the mma.sync kernels stay ahead inside the chain (124.2 against 125.7 us).
+  // MEMSOLVE_STATS_TCGEN05=1 selects the tcgen05 kernel at every rank, =0 at rank 64 only.
+  static const int tc_env = [] {
     const char* v = std::getenv("MEMSOLVE_STATS_TCGEN05");
-    return v && v[0] == '1';
+    return !v ? -1 : (v[0] == '1' ? 1 : 0);
   }();
   p.stats_tc = !no_tma_env && !no_tc_env && s.head_dim == 64 && s.tokens >= 1024 &&
-               (s.rank == 64 || (all_ranks_env && (s.rank == 16 || s.rank == 32)));
+               (s.rank == 64 || (s.rank == 32 && tc_env != 0) || (s.rank == 16 && tc_env == 1));
   if (p.stats_tc) {
     const int gsize = stats_tc_group_heads(s.rank);
     const long groups = (long)s.batch * ((s.heads + gsize - 1) / gsize);
