@@ -197,9 +197,9 @@ def test_tcgen05_statistics_stagewise_repeatable(cuda_mod, rank):
 
 
 def test_tcgen05_statistics_all_ranks_in_child_process():
-    """Rank 16 and 32 take the mma.sync statistics kernels unless MEMSOLVE_STATS_TCGEN05=1 is set when the
-    library plans its first launch: run the stage-wise statistics cases and the mixer cases of this file in
-    a child process with the switch on, so the tcgen05 kernel is checked at every rank."""
+    """Rank 16 takes the mma.sync statistics kernels unless MEMSOLVE_STATS_TCGEN05=1 is set when the library
+    plans its first launch: run the stage-wise statistics cases and the mixer cases of this file in a child
+    process with the switch on, so the tcgen05 kernel is checked at every rank."""
     import os
     import subprocess
     import sys
@@ -209,6 +209,23 @@ def test_tcgen05_statistics_all_ranks_in_child_process():
     here = os.path.abspath(__file__)
     done = subprocess.run([sys.executable, "-m", "pytest", here, "-q", "-x", "-p", "no:cacheprovider", "-k",
                            "statistics_stagewise or token_backward_matches_oracle"], env=env, capture_output=True,
+                          text=True, timeout=900)
+    assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-2000:]
+
+
+def test_mma_sync_statistics_at_rank_32_in_child_process():
+    """The other way round: with MEMSOLVE_STATS_TCGEN05=0 rank 32 takes the mma.sync statistics kernels at every
+    length; the stage-wise cases and the long-sequence mixer case run in a child process with that setting."""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("MEMSOLVE_STATS_TCGEN05") is not None:
+        pytest.skip("already inside a child process")
+    env = dict(os.environ, MEMSOLVE_STATS_TCGEN05="0")
+    here = os.path.dirname(os.path.abspath(__file__))
+    done = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_tensor_core_kernels_gpu.py"),
+                           os.path.join(here, "test_fast_mix_gpu.py"), "-q", "-x", "-p", "no:cacheprovider", "-k",
+                           "statistics_stagewise or full_size_long_sequence"], env=env, capture_output=True,
                           text=True, timeout=900)
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-2000:]
 
