@@ -347,7 +347,7 @@ compact_forward_kernel(const CompactFwdParams p) {
       valid[e] = off[e] < R * R;
     }
     if (staged) sum_chunks4<2>(stage, p.pf, nch, off, valid, acc);
-    else sum_chunks4<8>(src, p.pf, nch, off, valid, acc);
+    else sum_chunks4<(MINB == 1 ? 8 : 1)>(src, p.pf, nch, off, valid, acc);
 #pragma unroll
     for (int e = 0; e < 4; ++e)
       if (valid[e]) gs[off[e]] = acc[e] * inv_n;
@@ -376,7 +376,7 @@ compact_forward_kernel(const CompactFwdParams p) {
         off[e] = R * R + row * d + d0 + (valid[e] ? c : 0);
       }
       if (staged) sum_chunks4<2>(stage, p.pf, nch, off, valid, acc);
-      else sum_chunks4<8>(src, p.pf, nch, off, valid, acc);
+      else sum_chunks4<(MINB == 1 ? 8 : 1)>(src, p.pf, nch, off, valid, acc);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = i0 + e * NT;
@@ -549,7 +549,7 @@ compact_backward_kernel(const CompactBwdParams p) {
         zv[e] = valid[e] ? p.state[(size_t)sys * R * d + off[e]] : 0.f;
       }
       if (staged) sum_chunks4<2>(stage, p.pf, nch, off, valid, acc);
-      else sum_chunks4<8>(src, p.pf, nch, off, valid, acc);
+      else sum_chunks4<(MINB == 1 ? 8 : 1)>(src, p.pf, nch, off, valid, acc);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = i0 + e * NT;
